@@ -1,0 +1,82 @@
+"""ctypes binding of ``libhelion_b200.so`` (the C ABI declared in ``include/helion_b200.h``).
+
+The library is loaded lazily on first use.  There is no fallback: if the shared
+library has not been built (``python -m helion_b200.build``) or cannot be loaded,
+every operator raises ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p
+from ctypes import c_float
+from ctypes import c_int
+from ctypes import c_int64
+from ctypes import c_void_p
+from pathlib import Path
+import threading
+
+LIB_PATH = Path(__file__).resolve().parent / "libhelion_b200.so"
+
+HB200_OK = 0
+ABI_VERSION = 1
+
+_P = c_void_p
+_I64 = c_int64
+
+# name -> argument types (every entry point returns int unless listed in _RESTYPES)
+SIGNATURES: dict[str, list] = {
+    "hb200_abi_version": [],
+    "hb200_error_string": [c_int],
+    "hb200_nvfp4_gemv_bf16in": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
+    "hb200_nvfp4_gemv_bf16in_mma": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
+    "hb200_nvfp4_gemv_fp4in": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P],
+    "hb200_silu_and_mul_per_block_quant": [_P, _P, _P, _I64, _I64, _I64, _I64, c_int, _P, c_int, _P],
+    "hb200_rms_norm_dynamic_per_token_quant": [_P, _P, _P, _P, _I64, _I64, c_float, _P, _P, c_int, c_int, _P],
+    "hb200_per_token_group_fp8_quant": [_P, _P, _P, _I64, _I64, c_int, c_float, c_float, c_float, c_int, c_int, _P],
+    "hb200_nvfp4_quantize": [_P, _P, _P, _P, _I64, _I64, _I64, c_int, _P],
+}
+_RESTYPES = {"hb200_error_string": c_char_p}
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+
+class HelionB200Error(RuntimeError):
+    """A C-ABI entry point returned a non-zero status."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and declare every entry point's signature."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the CUDA extension first (python -m helion_b200.build); "
+                "helion_b200 has no CPU or eager fallback"
+            )
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError here means header and library disagree
+            fn.argtypes = argtypes
+            fn.restype = _RESTYPES.get(name, c_int)
+        version = lib.hb200_abi_version()
+        if version != ABI_VERSION:
+            raise RuntimeError(f"libhelion_b200.so has ABI version {version}, expected {ABI_VERSION}")
+        _lib = lib
+        return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != HB200_OK:
+        msg = load().hb200_error_string(status).decode()
+        raise HelionB200Error(f"{what} failed with status {status}: {msg}")
+
+
+def call(name: str, *args) -> None:
+    """Invoke entry point ``name`` and raise on a non-zero status."""
+    check(getattr(load(), name)(*args), name)

@@ -1,0 +1,376 @@
+"""Operator surface: the reference's Python entry points, backed by the sm_100a C ABI.
+
+Every public function here keeps the call signature, tensor layouts, validation
+order and error messages of the reference entry point named in its docstring, so
+it can be swapped in for it.  The device work is registered as ``torch.library``
+custom ops in the ``helion_b200`` namespace (with fake implementations for
+tracing); the custom ops call ``libhelion_b200.so`` through ctypes on the current
+CUDA stream.  There is no CPU or eager fallback: non-CUDA tensors raise.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .layouts import fp4_storage
+from .layouts import swizzled_scale_numel
+
+_FP8 = torch.float8_e4m3fn
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "helion_b200 operators run on CUDA (sm_100a) tensors only; there is no CPU fallback "
+                f"(got a tensor on {t.device})"
+            )
+
+
+def _ptr(t: Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------ validators
+# Same checks and messages as examples/nvfp4_gemv.py:111-149.
+def _check_swizzled_scales(name: str, scales: Tensor, rows: int, cols: int) -> None:
+    expected = swizzled_scale_numel(rows, cols)
+    if scales.numel() != expected:
+        raise ValueError(
+            f"{name} must contain {expected} SWIZZLE_32_4_4 scale values "
+            f"for logical shape ({rows}, {cols}); got {scales.numel()}"
+        )
+
+
+def _check_contiguous(name: str, t: Tensor) -> None:
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _check_fp4_weight_storage(name: str, storage: Tensor) -> None:
+    if storage.dim() != 2:
+        raise ValueError(f"{name} must be a 2D packed FP4 tensor")
+    if storage.shape[1] % 8 != 0:
+        raise ValueError(f"{name} K bytes must be divisible by 8; got {storage.shape[1]}")
+
+
+def _check_numel(name: str, t: Tensor, expected: int) -> None:
+    if t.numel() != expected:
+        raise ValueError(f"{name} must contain {expected} values; got {t.numel()}")
+
+
+# ------------------------------------------------------------------ custom ops
+@torch.library.custom_op("helion_b200::nvfp4_gemv_bf16in", mutates_args=())
+def _gemv_bf16in_op(weight_bytes: Tensor, x: Tensor, weight_scale: Tensor, alpha: float, use_mma: bool) -> Tensor:
+    _require_cuda(weight_bytes, x, weight_scale)
+    n, k_bytes = weight_bytes.shape
+    k = k_bytes * 2
+    batch = x.numel() // k if k else 1
+    out = torch.empty((batch, n), dtype=torch.bfloat16, device=weight_bytes.device)
+    if n and batch:
+        with torch.cuda.device(weight_bytes.device):
+            _lib.call(
+                "hb200_nvfp4_gemv_bf16in_mma" if use_mma else "hb200_nvfp4_gemv_bf16in",
+                weight_bytes.data_ptr(), x.data_ptr(), weight_scale.data_ptr(), out.data_ptr(),
+                n, k, batch, float(alpha), _stream(),
+            )
+    return out
+
+
+@_gemv_bf16in_op.register_fake
+def _(weight_bytes, x, weight_scale, alpha, use_mma):
+    k = weight_bytes.shape[1] * 2
+    batch = x.numel() // k if k else 1
+    return weight_bytes.new_empty((batch, weight_bytes.shape[0]), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("helion_b200::nvfp4_gemv_fp4in", mutates_args=())
+def _gemv_fp4in_op(weight_bytes: Tensor, x_bytes: Tensor, weight_scale: Tensor, x_scale: Tensor, alpha: float) -> Tensor:
+    _require_cuda(weight_bytes, x_bytes, weight_scale, x_scale)
+    n, k_bytes = weight_bytes.shape
+    out = torch.empty((n,), dtype=torch.bfloat16, device=weight_bytes.device)
+    if n:
+        with torch.cuda.device(weight_bytes.device):
+            _lib.call(
+                "hb200_nvfp4_gemv_fp4in",
+                weight_bytes.data_ptr(), x_bytes.data_ptr(), weight_scale.data_ptr(), x_scale.data_ptr(),
+                out.data_ptr(), n, k_bytes * 2, float(alpha), _stream(),
+            )
+    return out
+
+
+@_gemv_fp4in_op.register_fake
+def _(weight_bytes, x_bytes, weight_scale, x_scale, alpha):
+    return weight_bytes.new_empty((weight_bytes.shape[0],), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("helion_b200::silu_and_mul_per_block_quant", mutates_args=("out", "scales"))
+def _silu_mul_quant_op(out: Tensor, input: Tensor, scales: Tensor, group_size: int, scale_ub: Tensor | None) -> None:  # noqa: A002
+    _require_cuda(out, input, scales, scale_ub)
+    tokens, two_i = input.shape
+    with torch.cuda.device(input.device):
+        _lib.call(
+            "hb200_silu_and_mul_per_block_quant",
+            out.data_ptr(), input.data_ptr(), scales.data_ptr(), tokens, two_i // 2,
+            input.stride(0), out.stride(0), group_size, _ptr(scale_ub), int(out.dtype == torch.int8), _stream(),
+        )
+
+
+@_silu_mul_quant_op.register_fake
+def _(out, input, scales, group_size, scale_ub):  # noqa: A002
+    return None
+
+
+@torch.library.custom_op(
+    "helion_b200::rms_norm_dynamic_per_token_quant", mutates_args=("result", "scale", "residual")
+)
+def _rms_quant_op(
+    result: Tensor, input: Tensor, weight: Tensor, scale: Tensor, epsilon: float,  # noqa: A002
+    scale_ub: Tensor | None, residual: Tensor | None,
+) -> None:
+    _require_cuda(result, input, weight, scale, scale_ub, residual)
+    tokens, hidden = input.shape
+    with torch.cuda.device(input.device):
+        _lib.call(
+            "hb200_rms_norm_dynamic_per_token_quant",
+            result.data_ptr(), input.data_ptr(), weight.data_ptr(), scale.data_ptr(), tokens, hidden,
+            float(epsilon), _ptr(scale_ub), _ptr(residual), int(input.dtype == torch.float16),
+            int(result.dtype == torch.int8), _stream(),
+        )
+
+
+@_rms_quant_op.register_fake
+def _(result, input, weight, scale, epsilon, scale_ub, residual):  # noqa: A002
+    return None
+
+
+@torch.library.custom_op("helion_b200::per_token_group_fp8_quant", mutates_args=("output_q", "output_s"))
+def _group_quant_op(
+    input: Tensor, output_q: Tensor, output_s: Tensor, group_size: int, eps: float,  # noqa: A002
+    fp8_min: float, fp8_max: float, scale_ue8m0: bool,
+) -> None:
+    _require_cuda(input, output_q, output_s)
+    tokens, hidden = input.shape
+    dtype_code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[input.dtype]
+    with torch.cuda.device(input.device):
+        _lib.call(
+            "hb200_per_token_group_fp8_quant",
+            input.data_ptr(), output_q.data_ptr(), output_s.data_ptr(), tokens, hidden, group_size,
+            float(eps), float(fp8_min), float(fp8_max), int(scale_ue8m0), dtype_code, _stream(),
+        )
+
+
+@_group_quant_op.register_fake
+def _(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0):  # noqa: A002
+    return None
+
+
+@torch.library.custom_op("helion_b200::nvfp4_quantize", mutates_args=())
+def _nvfp4_quantize_op(x: Tensor, global_scale: Tensor | None) -> tuple[Tensor, Tensor, Tensor]:
+    _require_cuda(x, global_scale)
+    rows, k = x.shape
+    per_token = global_scale is None
+    codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    numel = swizzled_scale_numel(rows, k // 16)
+    padded = rows % 128 != 0 or (k // 16) % 4 != 0
+    scales = (torch.zeros if padded else torch.empty)(numel, dtype=torch.uint8, device=x.device)
+    g = torch.empty((rows,), dtype=torch.float32, device=x.device) if per_token else global_scale.reshape(1).clone()
+    if rows and k:
+        with torch.cuda.device(x.device):
+            _lib.call(
+                "hb200_nvfp4_quantize", x.data_ptr(), codes.data_ptr(), scales.data_ptr(), g.data_ptr(),
+                rows, k, x.stride(0), int(per_token), _stream(),
+            )
+    return codes, scales.view(_FP8), g
+
+
+@_nvfp4_quantize_op.register_fake
+def _(x, global_scale):
+    rows, k = x.shape
+    g = x.new_empty((rows,) if global_scale is None else (1,), dtype=torch.float32)
+    return (
+        x.new_empty((rows, k // 2), dtype=torch.uint8),
+        x.new_empty((swizzled_scale_numel(rows, k // 16),), dtype=_FP8),
+        g,
+    )
+
+
+# ---------------------------------------------------------------- public entry points
+def nvfp4_gemv_bf16in(
+    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, backend: str | None = None
+) -> Tensor:
+    """``weight_packed @ x_bf16`` for NVFP4 weights and a BF16 vector; returns bf16 ``[N]``.
+
+    Drop-in for ``nvfp4_gemv_bf16in`` (examples/nvfp4_gemv.py:432-476).  ``backend`` is
+    accepted for signature compatibility and ignored: there is one implementation.
+    """
+    _check_contiguous("weight_packed", weight_packed)
+    _check_contiguous("x_bf16", x_bf16)
+    weight_bytes = fp4_storage(weight_packed)
+    _check_fp4_weight_storage("weight_packed", weight_bytes)
+    _check_numel("x_bf16", x_bf16, weight_bytes.shape[1] * 2)
+    _check_swizzled_scales("weight_scale", weight_scale, weight_bytes.shape[0], weight_bytes.shape[1] // 8)
+    if x_bf16.dtype is not torch.bfloat16:
+        raise TypeError(f"x_bf16 must be torch.bfloat16, got {x_bf16.dtype}")
+    out = _gemv_bf16in_op(weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, False)
+    return out.reshape(weight_bytes.shape[0])
+
+
+def nvfp4_gemv_bf16in_batched(
+    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, use_mma: bool | None = None
+) -> Tensor:
+    """Decode-batch extension of :func:`nvfp4_gemv_bf16in`: ``x_bf16`` is ``[M, K]`` with 1 <= M <= 32,
+    the result is bf16 ``[M, N]``.  ``use_mma`` forces the tensor-core formulation for M == 1."""
+    _check_contiguous("weight_packed", weight_packed)
+    _check_contiguous("x_bf16", x_bf16)
+    weight_bytes = fp4_storage(weight_packed)
+    _check_fp4_weight_storage("weight_packed", weight_bytes)
+    if x_bf16.dim() != 2 or x_bf16.shape[1] != weight_bytes.shape[1] * 2:
+        raise ValueError(f"x_bf16 must have shape [M, {weight_bytes.shape[1] * 2}]; got {tuple(x_bf16.shape)}")
+    if not 1 <= x_bf16.shape[0] <= 32:
+        raise ValueError(f"batch must be in 1..32; got {x_bf16.shape[0]}")
+    _check_swizzled_scales("weight_scale", weight_scale, weight_bytes.shape[0], weight_bytes.shape[1] // 8)
+    if x_bf16.dtype is not torch.bfloat16:
+        raise TypeError(f"x_bf16 must be torch.bfloat16, got {x_bf16.dtype}")
+    return _gemv_bf16in_op(
+        weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, bool(use_mma)
+    )
+
+
+def nvfp4_gemv_fp4in(
+    weight_packed: Tensor, x_packed: Tensor, weight_scale: Tensor, x_scale: Tensor, alpha: float = 1.0,
+    *, backend: str | None = None,
+) -> Tensor:
+    """``weight_packed @ x_packed`` for NVFP4 weights and an NVFP4 vector; returns bf16 ``[N]``.
+
+    Drop-in for ``nvfp4_gemv_fp4in`` (examples/nvfp4_gemv.py:479-525).
+    """
+    _check_contiguous("weight_packed", weight_packed)
+    _check_contiguous("x_packed", x_packed)
+    weight_bytes = fp4_storage(weight_packed)
+    x_bytes = fp4_storage(x_packed)
+    _check_fp4_weight_storage("weight_packed", weight_bytes)
+    _check_numel("x_packed", x_bytes, weight_bytes.shape[1])
+    scale_cols = weight_bytes.shape[1] // 8
+    _check_swizzled_scales("weight_scale", weight_scale, weight_bytes.shape[0], scale_cols)
+    _check_swizzled_scales("x_scale", x_scale, 1, scale_cols)
+    return _gemv_fp4in_op(
+        weight_bytes, _aligned(x_bytes), weight_scale.reshape(-1).view(torch.uint8),
+        x_scale.reshape(-1).view(torch.uint8), alpha,
+    )
+
+
+def _aligned(t: Tensor) -> Tensor:
+    """The kernels read activations with 16-byte loads; re-materialise odd views."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
+def silu_and_mul_per_block_quant(
+    out: Tensor, input: Tensor, scales: Tensor, group_size: int,  # noqa: A002
+    scale_ub: Tensor | None = None, is_scale_transposed: bool = False,
+) -> None:
+    """``out, scales <- quant_fp8_per_block(silu(input[:, :d]) * input[:, d:])`` in place.
+
+    Drop-in for ``silu_and_mul_per_block_quant``
+    (pretuned_kernels/silu_and_mul_per_block_quant/silu_and_mul_per_block_quant.py:31-122);
+    the assertions are the reference's.
+    """
+    assert input.ndim == 2
+    num_tokens, two_intermediate_size = input.shape
+    assert two_intermediate_size % 2 == 0
+    intermediate_size = two_intermediate_size // 2
+    assert out.shape[0] == num_tokens
+    assert out.shape[1] == intermediate_size
+    assert out.dtype in [_FP8, torch.int8]
+    if scale_ub is not None:
+        assert out.dtype == _FP8
+        assert scale_ub.dtype == torch.float32
+    assert scales.ndim == 2 and scales.dtype == torch.float32
+    assert scales.shape[0] == num_tokens
+    groups_per_row = scales.shape[1]
+    assert intermediate_size % group_size == 0 and intermediate_size // group_size == groups_per_row
+    assert group_size in [64, 128]
+    assert input.stride()[-1] == 1
+    assert out.stride()[-1] == 1
+    if input.dtype is not torch.bfloat16:
+        raise TypeError(f"input must be torch.bfloat16, got {input.dtype}")
+    if not scales.is_contiguous():
+        raise ValueError("scales must be contiguous")
+    _silu_mul_quant_op(out, input, scales, group_size, scale_ub)
+
+
+def rms_norm_dynamic_per_token_quant(
+    result: Tensor, input: Tensor, weight: Tensor, scale: Tensor, epsilon: float,  # noqa: A002
+    scale_ub: Tensor | None = None, residual: Tensor | None = None,
+) -> None:
+    """RMSNorm(weight) (+ optional residual add, written back) then per-token dynamic quantisation, in place.
+
+    Drop-in for ``rms_norm_dynamic_per_token_quant``
+    (pretuned_kernels/rms_norm_dynamic_per_token_quant/rms_norm_dynamic_per_token_quant.py:40-128).
+    """
+    assert input.ndim == 2
+    num_tokens, hidden_size = input.shape
+    assert result.dtype in [_FP8, torch.int8]
+    assert result.is_contiguous() and input.is_contiguous()
+    if scale_ub is not None:
+        assert result.dtype == _FP8
+        assert scale_ub.dtype == torch.float32
+    assert input.dtype == weight.dtype
+    assert scale.shape[0] == num_tokens
+    assert scale.dtype == torch.float32
+    if residual is not None:
+        assert residual.dtype == input.dtype
+        if not residual.is_contiguous():
+            raise ValueError("residual must be contiguous")
+    if input.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"input must be bfloat16 or float16, got {input.dtype}")
+    if not (scale.is_contiguous() and weight.is_contiguous()):
+        raise ValueError("scale and weight must be contiguous")
+    _rms_quant_op(result, input, weight, scale, epsilon, scale_ub, residual)
+
+
+def per_token_group_fp8_quant(
+    input: Tensor, output_q: Tensor, output_s: Tensor, group_size: int, eps: float,  # noqa: A002
+    fp8_min: float, fp8_max: float, scale_ue8m0: bool,
+    dummy_is_scale_transposed: bool = False, dummy_is_tma_aligned: bool = False,
+) -> None:
+    """Per-(token, group) dynamic FP8 quantisation, in place on ``output_q`` / ``output_s``.
+
+    Drop-in for ``per_token_group_fp8_quant``
+    (pretuned_kernels/per_token_group_fp8_quant/per_token_group_fp8_quant.py:29-74); the arithmetic is
+    the module's fp32 reference ``_per_token_group_fp8_quant_torch`` (:77-97).
+    """
+    assert input.ndim == 2
+    num_tokens, hidden_size = input.shape
+    groups_per_row = output_s.shape[1]
+    assert hidden_size % group_size == 0 and hidden_size // group_size == groups_per_row
+    assert output_s.ndim == 2 and output_s.dtype == torch.float32
+    if not (input.is_contiguous() and output_q.is_contiguous() and output_s.is_contiguous()):
+        raise ValueError("input, output_q and output_s must be contiguous")
+    if output_q.dtype is not _FP8:
+        raise TypeError(f"output_q must be torch.float8_e4m3fn, got {output_q.dtype}")
+    _group_quant_op(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0)
+
+
+def nvfp4_quantize(x: Tensor, global_scale: Tensor | None = None) -> tuple[Tensor, Tensor, Tensor]:
+    """bf16 ``[rows, K]`` -> ``(packed e2m1 [rows, K/2] uint8, swizzled e4m3 scales, global scale)``.
+
+    With ``global_scale`` (0-dim or 1-element fp32 tensor) the whole tensor shares it; with ``None``
+    each row gets its own ``row_amax / (6 * 448)`` (returned as ``[rows]``).  The code rule is the
+    reference's ``quantize_fp4_e2m1`` (examples/nvfp4_gemm.py:368-381).
+    """
+    if x.dim() != 2:
+        raise ValueError("nvfp4_quantize expects a 2D tensor")
+    if x.shape[1] % 16:
+        raise ValueError(f"K must be divisible by 16, got {x.shape[1]}")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError(f"x must be torch.bfloat16, got {x.dtype}")
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return _nvfp4_quantize_op(x, global_scale)

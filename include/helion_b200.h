@@ -1,0 +1,117 @@
+/*
+ * helion_b200 -- C ABI of the sm_100a quantized-inference operators.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, 0 = the legacy default stream), launches asynchronously on
+ * that stream, never synchronises and never throws.  Unless its comment says
+ * otherwise an entry point allocates nothing.  The return value is HB200_OK or
+ * a negative HB200_ERR_* code; hb200_error_string() names it.
+ *
+ * Data formats (shared by all NVFP4 entry points):
+ *   - packed e2m1: two 4-bit codes per byte along K, low nibble = even k
+ *     (examples/nvfp4_gemm.py:396-408, examples/nvfp4_gemv.py:548-556);
+ *   - block scales: one float8_e4m3fn byte per 16 K-elements, stored flat in
+ *     the SWIZZLE_32_4_4 layout for logical shape [rows, K/16], zero padded to
+ *     round_up(rows,128) x round_up(K/16,4) (examples/nvfp4_gemv.py:68-101).
+ *
+ * The reference (pytorch/helion) has no native FFI: its operators are Python
+ * callables that JIT-compile generated kernels.  Each declaration below cites
+ * the Python entry point whose device work it replaces.
+ */
+#ifndef HELION_B200_H_
+#define HELION_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HB200_OK 0
+#define HB200_ERR_INVALID_ARGUMENT (-1) /* null pointer, bad size or alignment   */
+#define HB200_ERR_UNSUPPORTED (-2)      /* valid request outside built variants  */
+#define HB200_ERR_CUDA (-3)             /* a CUDA runtime/driver call failed     */
+#define HB200_ERR_DEVICE_TIMEOUT (-4)   /* a bounded device-side wait ran out    */
+#define HB200_ERR_WORKSPACE (-5)        /* caller workspace missing or too small */
+
+#define HB200_ABI_VERSION 1
+
+int hb200_abi_version(void);
+const char* hb200_error_string(int code);
+
+/* --------------------------------------------------------------- NVFP4 GEMV
+ * out[m, n] = bf16(alpha * sum_g scale[n, g] * sum_{i<16} e2m1(W[n, 16g+i]) * x[m, 16g+i])
+ *
+ * Replaces nvfp4_gemv_bf16in (examples/nvfp4_gemv.py:432-476,
+ * pretuned_kernels/nvfp4_gemv/nvfp4_gemv.py:205-222) for batch == 1 and is its
+ * decode-batch extension for 1 < batch <= 32 (x row-major [batch, K], out
+ * row-major [batch, N]).  K % 16 == 0.  Activations are converted to fp16
+ * before the multiply, as the reference's kernels do, so |x| must stay within
+ * fp16 range.
+ */
+int hb200_nvfp4_gemv_bf16in(const void* weight_packed, /* u8  [N, K/2]            */
+                            const void* x_bf16,        /* bf16 [batch, K]          */
+                            const void* weight_scale,  /* e4m3 swizzled [N, K/16]  */
+                            void* out_bf16,            /* bf16 [batch, N]          */
+                            int64_t n, int64_t k, int64_t batch, float alpha, void* stream);
+
+/* The batched kernel's arithmetic (block scale folded into the fp16 weight,
+ * fp32 accumulation inside warp-level MMAs) for any batch in 1..32, including
+ * batch == 1; exported so the two GEMV formulations can be cross-checked.
+ * Same arguments as hb200_nvfp4_gemv_bf16in. */
+int hb200_nvfp4_gemv_bf16in_mma(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                                void* out_bf16, int64_t n, int64_t k, int64_t batch, float alpha, void* stream);
+
+/* Replaces nvfp4_gemv_fp4in (examples/nvfp4_gemv.py:479-525): the activation is
+ * itself NVFP4 (packed codes [K/2] and swizzled e4m3 scales for logical
+ * [1, K/16]); the block scale applied is weight_scale * x_scale. */
+int hb200_nvfp4_gemv_fp4in(const void* weight_packed, const void* x_packed, const void* weight_scale,
+                           const void* x_scale, void* out_bf16, int64_t n, int64_t k, float alpha,
+                           void* stream);
+
+/* ------------------------------------------------- fused FP8 quant producers
+ * Replaces silu_and_mul_per_block_quant
+ * (pretuned_kernels/silu_and_mul_per_block_quant/silu_and_mul_per_block_quant.py:31-122).
+ * input bf16 [tokens, 2*inter] (gate first, then up), row stride in_stride
+ * elements; out e4m3 (or int8 when out_is_int8) [tokens, inter] with row stride
+ * out_stride bytes; scales fp32 [tokens, inter/group] contiguous;
+ * group in {64, 128}; scale_ub: optional device fp32 scalar (may be null). */
+int hb200_silu_and_mul_per_block_quant(void* out, const void* input, void* scales, int64_t tokens,
+                                       int64_t inter, int64_t in_stride, int64_t out_stride, int group,
+                                       const float* scale_ub, int out_is_int8, void* stream);
+
+/* Replaces rms_norm_dynamic_per_token_quant
+ * (pretuned_kernels/rms_norm_dynamic_per_token_quant/rms_norm_dynamic_per_token_quant.py:40-128).
+ * input/weight/residual bf16 or fp16 (in_is_fp16); result e4m3 or int8
+ * [tokens, hidden] contiguous; scale fp32 [tokens]; residual (nullable) is
+ * added to the input first and overwritten with the sum. */
+int hb200_rms_norm_dynamic_per_token_quant(void* result, const void* input, const void* weight, void* scale,
+                                           int64_t tokens, int64_t hidden, float epsilon,
+                                           const float* scale_ub, void* residual, int in_is_fp16,
+                                           int out_is_int8, void* stream);
+
+/* Replaces per_token_group_fp8_quant
+ * (pretuned_kernels/per_token_group_fp8_quant/per_token_group_fp8_quant.py:29-74);
+ * arithmetic follows the module's fp32 reference (:77-97).
+ * input bf16/fp16/fp32 (in_dtype 0/1/2) [tokens, hidden] contiguous. */
+int hb200_per_token_group_fp8_quant(const void* input, void* output_q, void* output_s, int64_t tokens,
+                                    int64_t hidden, int group, float eps, float fp8_min, float fp8_max,
+                                    int scale_ue8m0, int in_dtype, void* stream);
+
+/* ------------------------------------------------------- NVFP4 quantiser
+ * bf16 [rows, K] (row stride ldx elements) -> packed e2m1 codes [rows, K/2],
+ * e4m3 block scales in SWIZZLE_32_4_4 order for logical [rows, K/16] (only the
+ * logical entries are written: the caller zero-fills the buffer when rows % 128
+ * or (K/16) % 4 is non-zero) and the fp32 global scale g = amax / (6*448):
+ *   per_token == 0: *global_scale is an input, one value for the tensor;
+ *   per_token != 0: global_scale[rows] is an output, one value per row.
+ * Codes follow quantize_fp4_e2m1 (examples/nvfp4_gemm.py:368-381); the
+ * reference has no kernel for this step (it calls vLLM's scaled_fp4_quant,
+ * pretuned_kernels/nvfp4_gemv/nvfp4_gemv.py:241-246). */
+int hb200_nvfp4_quantize(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
+                         int64_t rows, int64_t k, int64_t ldx, int per_token, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELION_B200_H_ */

@@ -1,0 +1,119 @@
+"""Host-side mirror of the reference interface: layouts, validators, error messages, fake tensors."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helion_b200 as hb
+from helion_b200 import layouts as L
+from oracle import oracle as O
+
+
+def test_layout_helpers_match_golden(golden):
+    g = golden("formats.npz")
+    for rows, cols in ((1, 1), (5, 3), (130, 9), (256, 8)):
+        r = torch.arange(rows)[:, None]
+        c = torch.arange(cols)[None, :]
+        assert torch.equal(L.swizzled_scale_offsets(r, c, cols), g.raw(f"swz_off_{rows}x{cols}"))
+        assert L.swizzled_scale_numel(rows, cols) == g.scalar(f"swz_numel_{rows}x{cols}")
+        logical = torch.arange(rows * cols, dtype=torch.int32).remainder(251).to(torch.uint8).reshape(rows, cols)
+        buf = L.swizzle_fp8_scales(logical)
+        assert torch.equal(buf, g.raw(f"swz_buf_{rows}x{cols}"))
+        assert torch.equal(L.unswizzle_fp8_scales(buf, rows, cols), logical)
+    assert L.swizzled_scale_offsets(200, 7, 9) == int(g.raw("swz_off_256x8")[0, 0]) + ((200 // 128) * 3 + 1) * 512 + (200 % 32) * 16 + ((200 % 128) // 32) * 4 + 3
+    assert torch.equal(L.quantize_fp4_e2m1(g.raw("quant_in")), g.raw("quant_codes"))
+    codes = g.raw("pack_codes")
+    assert torch.equal(L.pack_fp4_last_dim(codes), g.raw("pack_last_dim"))
+    assert torch.equal(L.pack_fp4(codes.t().contiguous()), g.raw("pack_dim0"))
+    assert torch.equal(L.unpack_fp4_last_dim(g.raw("pack_last_dim")), codes)
+    assert torch.equal(L.unpack_fp4(g.raw("pack_dim0")), codes.t())
+    assert torch.equal(L.dequantize_fp4_codes(torch.arange(16)), O.dequant_e2m1(torch.arange(16)))
+
+
+def test_swizzle_of_float8_and_1d_input():
+    s = (torch.rand(3, 5) + 0.5).to(torch.float8_e4m3fn)
+    buf = L.swizzle_fp8_scales(s)
+    assert buf.dtype is torch.float8_e4m3fn and buf.numel() == 128 * 8
+    assert torch.equal(L.unswizzle_fp8_scales(buf, 3, 5).view(torch.uint8), s.view(torch.uint8))
+    one = L.swizzle_fp8_scales(s[0])
+    assert torch.equal(one.view(torch.uint8), L.swizzle_fp8_scales(s[:1]).view(torch.uint8))
+    with pytest.raises(ValueError, match="expected 1D or 2D scales"):
+        L.swizzle_fp8_scales(torch.zeros(1, 1, 1))
+
+
+def test_host_quantiser_matches_oracle():
+    torch.manual_seed(3)
+    x = (torch.randn(40, 96) * 0.02).to(torch.bfloat16)
+    for per_token in (False, True):
+        p, s, g = L.nvfp4_quantize_host(x, per_token=per_token)
+        po, so, go = O.nvfp4_quantize(x, per_token=per_token)
+        assert torch.equal(p, po) and torch.equal(s.view(torch.uint8), so.view(torch.uint8)) and torch.equal(g, go)
+        deq = L.nvfp4_dequantize_host(p, s, g)
+        ref = O.dequant_scaled_k_major(po, so) * (go.reshape(-1, 1) if per_token else go)
+        assert torch.equal(deq, ref)
+
+
+def _gemv_inputs(n=64, kb=128):
+    w = torch.randint(0, 256, (n, kb), dtype=torch.uint8)
+    x = torch.randn(kb * 2, dtype=torch.bfloat16)
+    s = L.swizzle_fp8_scales((torch.rand(n, kb // 8) + 0.5).to(torch.float8_e4m3fn))
+    return w, x, s
+
+
+def test_gemv_validators_match_reference_messages():
+    """The error contract of test/test_examples.py:2031-2055."""
+    w, x, s = _gemv_inputs()
+    with pytest.raises(ValueError, match="x_bf16 must contain"):
+        hb.nvfp4_gemv_bf16in(w, x[:-2], s)
+    with pytest.raises(ValueError, match="x_packed must contain"):
+        hb.nvfp4_gemv_fp4in(w, torch.zeros(100, dtype=torch.uint8), s, L.swizzle_fp8_scales(torch.ones(16).to(torch.float8_e4m3fn)))
+    with pytest.raises(ValueError, match="weight_packed must be contiguous"):
+        hb.nvfp4_gemv_bf16in(w.t(), x, s)
+    with pytest.raises(ValueError, match="K bytes must be divisible by 8"):
+        hb.nvfp4_gemv_bf16in(w[:, :4].contiguous(), x[:8], s)
+    with pytest.raises(ValueError, match=r"weight_scale must contain 2048 SWIZZLE_32_4_4 scale values for logical shape \(64, 16\); got 2047"):
+        hb.nvfp4_gemv_bf16in(w, x, s[:-1])
+    with pytest.raises(ValueError, match="must be a 2D packed FP4 tensor"):
+        hb.nvfp4_gemv_bf16in(w.reshape(-1), x, s)
+    with pytest.raises(TypeError, match="expected uint8 or float4_e2m1fn_x2 tensor"):
+        hb.nvfp4_gemv_bf16in(w.to(torch.int32), x, s)
+
+
+def test_no_cpu_fallback():
+    w, x, s = _gemv_inputs()
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        hb.nvfp4_gemv_bf16in(w, x, s)
+    q = torch.empty(4, 128, dtype=torch.float8_e4m3fn)
+    sc = torch.empty(4, 1, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        hb.per_token_group_fp8_quant(torch.randn(4, 128, dtype=torch.bfloat16), q, sc, 128, 1e-10, -448.0, 448.0, False)
+
+
+def test_quant_producer_assertions():
+    x = torch.randn(4, 256, dtype=torch.bfloat16)
+    out = torch.empty(4, 128, dtype=torch.float8_e4m3fn)
+    with pytest.raises(AssertionError):
+        hb.silu_and_mul_per_block_quant(out, x, torch.empty(4, 1), 32)  # group size not in {64, 128}
+    with pytest.raises(AssertionError):
+        hb.silu_and_mul_per_block_quant(out, x, torch.empty(4, 2), 128)  # wrong number of groups
+    with pytest.raises(AssertionError):
+        hb.rms_norm_dynamic_per_token_quant(out, x[:, :128].contiguous(), torch.ones(128), torch.empty(4, 1), 1e-6)  # dtype mismatch
+    with pytest.raises(AssertionError):
+        hb.per_token_group_fp8_quant(x, torch.empty(4, 256, dtype=torch.float8_e4m3fn), torch.empty(4, 3), 128, 1e-10, -448.0, 448.0, False)
+
+
+def test_custom_ops_registered_with_fake_impls():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    assert hasattr(torch.ops.helion_b200, "nvfp4_gemv_bf16in")
+    with FakeTensorMode():
+        w = torch.empty(64, 128, dtype=torch.uint8, device="cuda")
+        x = torch.empty(2, 256, dtype=torch.bfloat16, device="cuda")
+        s = torch.empty(2048, dtype=torch.uint8, device="cuda")
+        y = torch.ops.helion_b200.nvfp4_gemv_bf16in(w, x, s, 1.0, False)
+        assert y.shape == (2, 64) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
+        y = torch.ops.helion_b200.nvfp4_gemv_fp4in(w, torch.empty(128, dtype=torch.uint8, device="cuda"), s, s, 1.0)
+        assert y.shape == (64,)
+        c, sc, g = torch.ops.helion_b200.nvfp4_quantize(x, None)
+        assert c.shape == (2, 128) and sc.numel() == 128 * 16 and g.shape == (2,)
