@@ -16,6 +16,7 @@ from .ops import nvfp4_gemv_bf16in
 from .ops import nvfp4_gemv_bf16in_batched
 from .ops import nvfp4_gemv_fp4in
 from .ops import nvfp4_quantize
+from .ops import nvfp4_scaled_matmul
 from .ops import per_token_group_fp8_quant
 from .ops import rms_norm_dynamic_per_token_quant
 from .ops import silu_and_mul_per_block_quant
@@ -26,6 +27,7 @@ __all__ = [
     "nvfp4_gemv_bf16in_batched",
     "nvfp4_gemv_fp4in",
     "nvfp4_quantize",
+    "nvfp4_scaled_matmul",
     "per_token_group_fp8_quant",
     "rms_norm_dynamic_per_token_quant",
     "silu_and_mul_per_block_quant",

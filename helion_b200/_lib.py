@@ -35,6 +35,8 @@ SIGNATURES: dict[str, list] = {
     "hb200_rms_norm_dynamic_per_token_quant": [_P, _P, _P, _P, _I64, _I64, c_float, _P, _P, c_int, c_int, _P],
     "hb200_per_token_group_fp8_quant": [_P, _P, _P, _I64, _I64, c_int, c_float, c_float, c_float, c_int, c_int, _P],
     "hb200_nvfp4_quantize": [_P, _P, _P, _P, _I64, _I64, _I64, c_int, _P],
+    "hb200_nvfp4_scaled_matmul": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, c_float, c_int, _P],
+    "hb200_device_status": [c_int],
 }
 _RESTYPES = {"hb200_error_string": c_char_p}
 

@@ -1,0 +1,411 @@
+// Block-scaled NVFP4 GEMM for sm_100a:  D[M,N] = alpha * (A[M,K] . B[N,K]^T)
+// with both operands packed e2m1 (K-major) and one e4m3 scale per 16 K-elements
+// in the SWIZZLE_32_4_4 layout.
+//
+// One persistent CTA per SM, six warps with fixed roles:
+//   warp 0   producer : TMA loads of the A and B tiles (128-byte swizzled rows of
+//                       256 K-elements) and plain bulk copies of the scale tiles
+//                       (the swizzled global layout is already the 128x4 atom the
+//                       tensor core wants, 512 contiguous bytes per 64 K-elements)
+//   warp 1   MMA      : tcgen05.cp moves the scale atoms to tensor memory, then
+//                       tcgen05.mma.kind::mxf4nvf4.block_scale accumulates
+//                       128 x BLOCK_N x 64 per instruction into tensor memory
+//   warps 2-5 epilogue: tcgen05.ld of the fp32 accumulator, * alpha, convert, store
+// Stages of the shared-memory ring and of the accumulator ring are handed over
+// with mbarriers; every wait is bounded and a timeout ends the kernel with an
+// error status instead of hanging.  No cluster multicast is used anywhere.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#include <mutex>
+#include <type_traits>
+
+namespace hb200 {
+
+__device__ int g_device_status = 0;
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;   // one swizzle row: 256 e2m1 values
+constexpr int kAtomBytes = 512;     // one 128-row x 4-scale atom (64 K-elements)
+constexpr int kAtomsPerStage = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+
+struct GemmArgs {
+  const uint8_t* sfa;  // swizzled scales of A, logical [M, K/16]
+  const uint8_t* sfb;  // swizzled scales of B, logical [N, K/16]
+  void* out;           // [M, N] row-major, leading dimension ldc elements
+  int64_t ldc;
+  int m, n, k;
+  float alpha;
+  int m_tiles, n_tiles;
+};
+
+template <int BLOCK_N>
+struct StageLayout {
+  static constexpr int kNB = (BLOCK_N + 127) / 128;  // 128-row scale atoms along N
+  static constexpr int kABytes = kBlockM * kBlockKBytes;
+  static constexpr int kBBytes = BLOCK_N * kBlockKBytes;
+  static constexpr int kSfaBytes = kAtomsPerStage * kAtomBytes;
+  static constexpr int kSfbBytes = kNB * kAtomsPerStage * kAtomBytes;
+  static constexpr int kBOff = kABytes;
+  static constexpr int kSfaOff = kBOff + ((kBBytes + 1023) / 1024) * 1024;
+  static constexpr int kSfbOff = kSfaOff + kSfaBytes;
+  static constexpr int kBytes = ((kSfbOff + kSfbBytes + 1023) / 1024) * 1024;
+  // tensor memory: accumulator ring, then the scale columns of one stage
+  static constexpr int kSfCols = kAtomsPerStage * 4 * (1 + kNB);
+  static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= kTmemCols) ? 2 : 1;
+  static constexpr int kSfaCol = kAccStages * BLOCK_N;
+  static constexpr int kSfbCol = kSfaCol + kAtomsPerStage * 4;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const uint32_t (&r)[32], float alpha, int valid, bool vec_ok);
+
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], float alpha,
+                                                               int valid, bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
+                                                       __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha);
+        p[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const uint32_t (&r)[32], float alpha, int valid,
+                                                        bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        p[j] = h2_as_u32(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
+                                           __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha));
+      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __float2half_rn(__uint_as_float(r[j]) * alpha);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* dst, const uint32_t (&r)[32], float alpha, int valid,
+                                                       bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      *reinterpret_cast<float4*>(dst + v * 4) =
+          make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha,
+                      __uint_as_float(r[v * 4 + 2]) * alpha, __uint_as_float(r[v * 4 + 3]) * alpha);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __uint_as_float(r[j]) * alpha;
+  }
+}
+
+template <int BLOCK_N, int STAGES, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const GemmArgs g) {
+  using L = StageLayout<BLOCK_N>;
+  constexpr int ACC = L::kAccStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte aligned bases
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::kBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col_tiles = (g.k / 16 + 3) / 4;                     // 64-element scale atoms along K
+  const int num_kb = (col_tiles + kAtomsPerStage - 1) / kAtomsPerStage;
+  const int num_tiles = g.m_tiles * g.n_tiles;
+  const int n_row_tiles = (g.n + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < ACC; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag)) { ok = false; break; }
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          int sfb_tiles = 0;
+#pragma unroll
+          for (int nb = 0; nb < L::kNB; ++nb)
+            if ((n_blk * BLOCK_N) / 128 + nb < n_row_tiles) ++sfb_tiles;
+          const uint32_t bytes = L::kABytes + L::kBBytes + uint32_t(atoms) * kAtomBytes * (1 + sfb_tiles);
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          mbar_arrive_expect_tx(bar, bytes);
+          uint8_t* st = smem + s * L::kBytes;
+          tma_load_2d(smem_u32(st), &tmap_a, kb * kBlockKBytes, m_blk * kBlockM, bar);
+          tma_load_2d(smem_u32(st + L::kBOff), &tmap_b, kb * kBlockKBytes, n_blk * BLOCK_N, bar);
+          bulk_load(smem_u32(st + L::kSfaOff),
+                    g.sfa + (int64_t(m_blk) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes, bar);
+#pragma unroll
+          for (int nb = 0; nb < L::kNB; ++nb) {
+            const int rt = (n_blk * BLOCK_N) / 128 + nb;
+            if (rt < n_row_tiles)
+              bulk_load(smem_u32(st + L::kSfbOff + nb * kAtomsPerStage * kAtomBytes),
+                        g.sfb + (int64_t(rt) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes, bar);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mxf4nvf4(kBlockM, BLOCK_N);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tc) {
+        const int acc = tc % ACC;
+        const uint32_t acc_ph = (tc / ACC) & 1;
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          uint8_t* st = smem + s * L::kBytes;
+          const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + L::kBOff);
+          const uint32_t sfa_addr = smem_u32(st + L::kSfaOff), sfb_addr = smem_u32(st + L::kSfbOff);
+          for (int a = 0; a < atoms; ++a) {
+            tcgen05_cp_32x128b_warpx4(tmem_base + L::kSfaCol + a * 4,
+                                      make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
+#pragma unroll
+            for (int nb = 0; nb < L::kNB; ++nb)
+              tcgen05_cp_32x128b_warpx4(
+                  tmem_base + L::kSfbCol + (a * L::kNB + nb) * 4,
+                  make_smem_desc(sfb_addr + (nb * kAtomsPerStage + a) * kAtomBytes, 0, 128, kSwizzleNone));
+          }
+          for (int a = 0; a < atoms; ++a) {
+            // 64 K-elements = 32 bytes further along the 128-byte swizzled row
+            const uint64_t adesc = make_smem_desc(a_addr + a * 32, 16, 1024, kSwizzle128B);
+            const uint64_t bdesc = make_smem_desc(b_addr + a * 32, 16, 1024, kSwizzle128B);
+            mma_mxf4nvf4(tmem_d, adesc, bdesc, idesc, (kb | a) != 0 ? 1u : 0u, tmem_base + L::kSfaCol + a * 4,
+                         tmem_base + L::kSfbCol + a * L::kNB * 4);
+          }
+          tcgen05_commit(smem_u32(&empty_bar[s]));  // stage reusable once these MMAs have read it
+        }
+        if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // the tensor-memory lane quarter this warp may read
+    OutT* out = static_cast<OutT*>(g.out);
+    const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
+    uint32_t tc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tc) {
+      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+      const int acc = tc % ACC;
+      const uint32_t acc_ph = (tc / ACC) & 1;
+      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_ph, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m_blk * kBlockM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BLOCK_N;
+      if constexpr (BLOCK_N >= 32) {
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = n_blk * BLOCK_N + c * 32;
+          if (row < g.m && col < g.n)
+            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r, g.alpha, g.n - col, vec_ok);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 8; ++c) {
+          uint32_t r8[8];
+          tmem_ld_32x32b_x8(taddr + c * 8, r8);
+          tmem_ld_wait();
+          const int col = n_blk * BLOCK_N + c * 8;
+          if (row < g.m) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col + j < g.n) {
+                const float v = __uint_as_float(r8[j]) * g.alpha;
+                if constexpr (sizeof(OutT) == 4) out[int64_t(row) * g.ldc + col + j] = v;
+                else if constexpr (std::is_same<OutT, __half>::value) out[int64_t(row) * g.ldc + col + j] = __float2half_rn(v);
+                else out[int64_t(row) * g.ldc + col + j] = __float2bfloat16_rn(v);
+              }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicMin(&g_device_status, HB200_ERR_DEVICE_TIMEOUT);
+}
+
+// ----------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Packed e2m1 matrix [rows, k/2 bytes] as a byte tensor; box = 128 bytes x box_rows, 128-byte swizzle.
+bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(k_bytes), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(k_bytes)};
+  const cuuint32_t box[2] = {cuuint32_t(kBlockKBytes), cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count_gemm() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n > 0 ? n : 148;
+}
+
+template <int BLOCK_N, int STAGES, typename OutT>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream) {
+  using L = StageLayout<BLOCK_N>;
+  constexpr size_t smem = size_t(STAGES) * L::kBytes + (2 * STAGES + 2 * L::kAccStages) * 8 + 16 + 1024;
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  auto kernel = nvfp4_gemm_kernel<BLOCK_N, STAGES, OutT>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    return HB200_ERR_CUDA;
+  g.m_tiles = (g.m + kBlockM - 1) / kBlockM;
+  g.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
+  const int tiles = g.m_tiles * g.n_tiles;
+  const int grid = tiles < sm_count_gemm() ? tiles : sm_count_gemm();
+  kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, g);
+  return launch_status();
+}
+
+template <typename OutT>
+int dispatch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  const int block_n = g.n > 128 ? 256 : 128;
+  if (!make_operand_map(&ta, a, g.m, g.k / 2, kBlockM)) return HB200_ERR_CUDA;
+  if (!make_operand_map(&tb, b, g.n, g.k / 2, block_n)) return HB200_ERR_CUDA;
+  if (block_n == 256) return launch_gemm<256, 4, OutT>(ta, tb, g, stream);
+  return launch_gemm<128, 6, OutT>(ta, tb, g, stream);
+}
+
+}  // namespace
+}  // namespace hb200
+
+extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_packed, const void* scale_a,
+                                         const void* scale_b, void* out, int64_t m, int64_t n, int64_t k,
+                                         int64_t ldc, float alpha, int out_dtype, void* stream) {
+  using namespace hb200;
+  if (!a_packed || !b_packed || !scale_a || !scale_b || !out) return HB200_ERR_INVALID_ARGUMENT;
+  if (m < 0 || n < 0 || k < 0 || ldc < n || out_dtype < 0 || out_dtype > 2) return HB200_ERR_INVALID_ARGUMENT;
+  if ((k % 16) != 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a_packed) % 16 || reinterpret_cast<uintptr_t>(b_packed) % 16 ||
+      reinterpret_cast<uintptr_t>(scale_a) % 16 || reinterpret_cast<uintptr_t>(scale_b) % 16)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0) return HB200_OK;
+  if ((k % 32) != 0) return HB200_ERR_UNSUPPORTED;  // TMA needs 16-byte row pitch
+  if (m > 0x7fffff00 || n > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t elt = out_dtype == 2 ? 4 : 2;
+  if (k == 0) {
+    return cudaMemset2DAsync(out, size_t(ldc) * elt, 0, size_t(n) * elt, size_t(m), s) == cudaSuccess ? HB200_OK
+                                                                                                      : HB200_ERR_CUDA;
+  }
+  GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
+             int(m), int(n), int(k), alpha, 0, 0};
+  switch (out_dtype) {
+    case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, s);
+    case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, s);
+    default: return dispatch_gemm<float>(a_packed, b_packed, g, s);
+  }
+}
+
+// Reads (and optionally clears) the sticky device status set by kernels whose
+// bounded waits ran out.  Synchronises the device.
+extern "C" int hb200_device_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, hb200::g_device_status, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  if (reset && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(hb200::g_device_status, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  }
+  return v;
+}

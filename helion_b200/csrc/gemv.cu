@@ -237,7 +237,8 @@ int sm_count() {
 template <bool X_FP4, bool VEC16>
 int launch_gemv(const GemvArgs& base, cudaStream_t stream) {
   GemvArgs a = base;
-  const int64_t row_groups = ceil_div64(a.n, kRowsPerCta);
+  // four CTAs cover one 128-row scale tile (rows l + 32q), so tiles are launched whole
+  const int64_t row_groups = ceil_div64(a.n, 128) * 4;
   const int64_t total_iters = ceil_div64(a.k, kIterK);
   // Split K over a cluster until the grid can fill the machine (>= 4 CTAs per
   // SM) while every CTA keeps at least 4 iterations.

@@ -201,6 +201,33 @@ def _(x, global_scale):
     )
 
 
+_OUT_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+@torch.library.custom_op("helion_b200::nvfp4_scaled_matmul", mutates_args=())
+def _scaled_matmul_op(
+    a_bytes: Tensor, b_bytes: Tensor, scale_a: Tensor, scale_b: Tensor, alpha: float, out_dtype: torch.dtype
+) -> Tensor:
+    """``a_bytes [M, K/2]`` and ``b_bytes [N, K/2]`` (both K-major, contiguous) -> ``[M, N]``."""
+    _require_cuda(a_bytes, b_bytes, scale_a, scale_b)
+    m, k_bytes = a_bytes.shape
+    n = b_bytes.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a_bytes.device)
+    if m and n:
+        with torch.cuda.device(a_bytes.device):
+            _lib.call(
+                "hb200_nvfp4_scaled_matmul",
+                a_bytes.data_ptr(), b_bytes.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), out.data_ptr(),
+                m, n, k_bytes * 2, n, float(alpha), _OUT_DTYPES[out_dtype], _stream(),
+            )
+    return out
+
+
+@_scaled_matmul_op.register_fake
+def _(a_bytes, b_bytes, scale_a, scale_b, alpha, out_dtype):
+    return a_bytes.new_empty((a_bytes.shape[0], b_bytes.shape[0]), dtype=out_dtype)
+
+
 # ---------------------------------------------------------------- public entry points
 def nvfp4_gemv_bf16in(
     weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, backend: str | None = None
@@ -263,6 +290,49 @@ def nvfp4_gemv_fp4in(
     return _gemv_fp4in_op(
         weight_bytes, _aligned(x_bytes), weight_scale.reshape(-1).view(torch.uint8),
         x_scale.reshape(-1).view(torch.uint8), alpha,
+    )
+
+
+def nvfp4_scaled_matmul(
+    A_packed: Tensor, B_packed_t: Tensor, scale_a: Tensor, scale_b: Tensor,  # noqa: N803
+    out_dtype: torch.dtype = torch.bfloat16, *, alpha: float = 1.0,
+) -> Tensor:
+    """Block-scaled FP4 x FP4 GEMM on the tensor cores: ``[M, K/2] x [K/2, N] -> [M, N]``.
+
+    Drop-in for ``nvfp4_scaled_matmul`` (examples/nvfp4_gemm.py:331-364): ``B_packed_t`` is the transposed
+    packed right-hand side (storage K-major, stride ``(1, K/2)``; anything else is re-laid out as the
+    reference does), scales are flat SWIZZLE_32_4_4 e4m3 tensors for logical ``[M, K/16]`` / ``[N, K/16]``.
+    ``alpha`` (keyword, default 1) is an extension that applies the operands' global scales in the epilogue.
+    """
+    if out_dtype not in _OUT_DTYPES:
+        raise TypeError(f"unsupported output dtype for nvfp4_scaled_matmul: {out_dtype}")
+    a = fp4_storage(A_packed)
+    b_t = fp4_storage(B_packed_t)
+    if a.dim() != 2 or b_t.dim() != 2:
+        raise ValueError("nvfp4_scaled_matmul expects 2D FP4 matrices")
+    m, k_bytes = a.shape
+    k_bytes_b, n = b_t.shape
+    if k_bytes_b != k_bytes:
+        raise ValueError(
+            f"B_packed_t shape {tuple(b_t.shape)} is incompatible with A_packed shape {tuple(a.shape)}"
+        )
+    if k_bytes % 8 != 0:
+        raise ValueError(f"K must be divisible by 16, got {k_bytes * 2}")
+    if a.stride() != (k_bytes, 1):
+        a = a.contiguous()
+    b = b_t.t()  # [N, K/2]
+    if b.stride() != (k_bytes, 1):
+        b = b.contiguous()
+    k_groups = k_bytes // 8
+    _check_swizzled_scales("scale_a", scale_a, m, k_groups)
+    _check_swizzled_scales("scale_b", scale_b, n, k_groups)
+    if scale_a.dtype is not _FP8:
+        raise TypeError(f"scale_a must be torch.float8_e4m3fn, got {scale_a.dtype}")
+    if scale_b.dtype is not _FP8:
+        raise TypeError(f"scale_b must be torch.float8_e4m3fn, got {scale_b.dtype}")
+    return _scaled_matmul_op(
+        _aligned(a), _aligned(b), _aligned(scale_a.reshape(-1).view(torch.uint8)),
+        _aligned(scale_b.reshape(-1).view(torch.uint8)), alpha, out_dtype,
     )
 
 

@@ -111,6 +111,25 @@ int hb200_per_token_group_fp8_quant(const void* input, void* output_q, void* out
 int hb200_nvfp4_quantize(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
                          int64_t rows, int64_t k, int64_t ldx, int per_token, void* stream);
 
+/* ------------------------------------------------------------ NVFP4 GEMM
+ * D[M, N] = out_dtype(alpha * A[M, K] . B[N, K]^T), both operands packed e2m1
+ * and K-major, e4m3 block scales in SWIZZLE_32_4_4 order for logical [M, K/16]
+ * and [N, K/16], fp32 accumulation on the tensor cores
+ * (tcgen05.mma kind::mxf4nvf4).  Replaces nvfp4_scaled_matmul
+ * (examples/nvfp4_gemm.py:331-364, which defers to torch._scaled_mm); alpha
+ * carries the product of the operands' global scales (1.0 reproduces the
+ * reference call).  out_dtype: 0 bf16, 1 fp16, 2 fp32; ldc in elements.
+ * K % 32 == 0; all pointers 16-byte aligned. */
+int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_packed, const void* scale_a,
+                              const void* scale_b, void* out, int64_t m, int64_t n, int64_t k, int64_t ldc,
+                              float alpha, int out_dtype, void* stream);
+
+/* Sticky device-side status: HB200_OK, or HB200_ERR_DEVICE_TIMEOUT once a
+ * kernel gave up a bounded wait (its outputs are then undefined).  reset != 0
+ * clears it.  Synchronises the device; not for use on the hot path.  (No
+ * counterpart in the reference, whose device waits are unbounded.) */
+int hb200_device_status(int reset);
+
 #ifdef __cplusplus
 }
 #endif
