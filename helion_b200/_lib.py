@@ -37,6 +37,10 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_quantize": [_P, _P, _P, _P, _I64, _I64, _I64, c_int, _P],
     "hb200_nvfp4_scaled_matmul": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, c_float, c_int, _P],
     "hb200_device_status": [c_int],
+    "hb200_nvfp4_grouped_matmul": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, c_int, _P],
+    "hb200_moe_build_schedule": [_P, _I64, _P, _I64, _P, _P, _I64, _P, _P, _P],
+    "hb200_nvfp4_quantize_rows": [_P, _P, _P, _P, _I64, _I64, _I64, _P, c_int, _P, _P, c_int, _P],
+    "hb200_moe_combine": [_P, _I64, _P, _P, _I64, _I64, _I64, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p}
 

@@ -37,13 +37,46 @@ constexpr int kTmemCols = 512;
 
 struct GemmArgs {
   const uint8_t* sfa;  // swizzled scales of A, logical [M, K/16]
-  const uint8_t* sfb;  // swizzled scales of B, logical [N, K/16]
+  const uint8_t* sfb;  // swizzled scales of B, logical [N, K/16] (per group when grouped)
   void* out;           // [M, N] row-major, leading dimension ldc elements
   int64_t ldc;
-  int m, n, k;
+  int m, n, k;         // m counts the (padded) rows of A and of the output
   float alpha;
   int m_tiles, n_tiles;
+  // Grouped mode (tile_info != nullptr): the rows of A are laid out group after
+  // group, every group padded to a multiple of 128 rows; tile_info[t] = (group,
+  // valid rows) of 128-row tile t, group < 0 for tiles past the last group.  B is
+  // [groups * n, K/2] with one scale buffer of sfb_group_stride bytes per group.
+  const int2* tile_info;
+  int64_t sfb_group_stride;
+  const float* row_scale;    // optional fp32 factor per row of A
+  const float* group_alpha;  // optional fp32 factor per group
 };
+
+struct Tile {
+  int m_blk, n_blk, group, rows;
+  bool valid;
+};
+
+__device__ __forceinline__ Tile decode_tile(const GemmArgs& g, int tile) {
+  Tile t;
+  if (g.tile_info != nullptr) {
+    // all column tiles of a 128-row tile run back to back: its group's weights stay in L2
+    t.m_blk = tile / g.n_tiles;
+    t.n_blk = tile - t.m_blk * g.n_tiles;
+    const int2 ti = g.tile_info[t.m_blk];
+    t.group = ti.x;
+    t.rows = ti.y;
+    t.valid = ti.x >= 0 && ti.y > 0;
+  } else {
+    t.m_blk = tile % g.m_tiles;
+    t.n_blk = tile / g.m_tiles;
+    t.group = 0;
+    t.rows = min(kBlockM, g.m - t.m_blk * kBlockM);
+    t.valid = true;
+  }
+  return t;
+}
 
 template <int BLOCK_N>
 struct StageLayout {
@@ -56,11 +89,12 @@ struct StageLayout {
   static constexpr int kSfaOff = kBOff + ((kBBytes + 1023) / 1024) * 1024;
   static constexpr int kSfbOff = kSfaOff + kSfaBytes;
   static constexpr int kBytes = ((kSfbOff + kSfbBytes + 1023) / 1024) * 1024;
-  // tensor memory: accumulator ring, then the scale columns of one stage
+  // tensor memory: accumulator ring, then one set of scale columns per shared-memory stage
   static constexpr int kSfCols = kAtomsPerStage * 4 * (1 + kNB);
-  static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= kTmemCols) ? 2 : 1;
-  static constexpr int kSfaCol = kAccStages * BLOCK_N;
-  static constexpr int kSfbCol = kSfaCol + kAtomsPerStage * 4;
+  static constexpr int kSfaColOff = 0;                       // inside a stage's scale columns
+  static constexpr int kSfbColOff = kAtomsPerStage * 4;
+  template <int STAGES>
+  static constexpr int acc_stages() { return (2 * BLOCK_N + STAGES * kSfCols <= kTmemCols) ? 2 : 1; }
 };
 
 template <typename OutT>
@@ -129,7 +163,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmArgs g) {
   using L = StageLayout<BLOCK_N>;
-  constexpr int ACC = L::kAccStages;
+  constexpr int ACC = L::template acc_stages<STAGES>();
+  constexpr int kSfBase = ACC * BLOCK_N;
+  static_assert(kSfBase + STAGES * L::kSfCols <= kTmemCols, "tensor memory budget exceeded");
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -172,11 +208,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    // the whole warp walks the schedule; one elected lane issues the copies
+    {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+        const Tile t = decode_tile(g, tile);
+        if (!t.valid) continue;
+        const int m_blk = t.m_blk, n_blk = t.n_blk;
+        const int b_row0 = t.group * g.n + n_blk * BLOCK_N;
+        const uint8_t* sfb_base = g.sfb + int64_t(t.group) * g.sfb_group_stride;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -188,62 +229,96 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if ((n_blk * BLOCK_N) / 128 + nb < n_row_tiles) ++sfb_tiles;
           const uint32_t bytes = L::kABytes + L::kBBytes + uint32_t(atoms) * kAtomBytes * (1 + sfb_tiles);
           const uint32_t bar = smem_u32(&full_bar[s]);
-          mbar_arrive_expect_tx(bar, bytes);
           uint8_t* st = smem + s * L::kBytes;
-          tma_load_2d(smem_u32(st), &tmap_a, kb * kBlockKBytes, m_blk * kBlockM, bar);
-          tma_load_2d(smem_u32(st + L::kBOff), &tmap_b, kb * kBlockKBytes, n_blk * BLOCK_N, bar);
-          bulk_load(smem_u32(st + L::kSfaOff),
-                    g.sfa + (int64_t(m_blk) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes, bar);
+          if (elect_one()) {
+            mbar_arrive_expect_tx(bar, bytes);
+            tma_load_2d(smem_u32(st), &tmap_a, kb * kBlockKBytes, m_blk * kBlockM, bar);
+            tma_load_2d(smem_u32(st + L::kBOff), &tmap_b, kb * kBlockKBytes, b_row0, bar);
+            bulk_load(smem_u32(st + L::kSfaOff),
+                      g.sfa + (int64_t(m_blk) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes,
+                      bar);
 #pragma unroll
-          for (int nb = 0; nb < L::kNB; ++nb) {
-            const int rt = (n_blk * BLOCK_N) / 128 + nb;
-            if (rt < n_row_tiles)
-              bulk_load(smem_u32(st + L::kSfbOff + nb * kAtomsPerStage * kAtomBytes),
-                        g.sfb + (int64_t(rt) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes, bar);
+            for (int nb = 0; nb < L::kNB; ++nb) {
+              const int rt = (n_blk * BLOCK_N) / 128 + nb;
+              if (rt < n_row_tiles)
+                bulk_load(smem_u32(st + L::kSfbOff + nb * kAtomsPerStage * kAtomBytes),
+                          sfb_base + (int64_t(rt) * col_tiles + kb * kAtomsPerStage) * kAtomBytes, atoms * kAtomBytes,
+                          bar);
+            }
           }
+          __syncwarp();
         }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The scale atoms of a stage are copied into that stage's own tensor-memory
+    // columns one k-block ahead of the MMAs that use them, so the copies overlap
+    // the previous k-block's MMAs instead of draining the tensor pipe.  The whole
+    // warp walks the schedule and waits; one elected lane issues.
+    {
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(kBlockM, BLOCK_N);
-      uint32_t it = 0, tc = 0;
+      int my_tiles = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) my_tiles += decode_tile(g, tile).valid ? 1 : 0;
+      const uint32_t total = uint32_t(my_tiles) * uint32_t(num_kb);
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tc) {
-        const int acc = tc % ACC;
-        const uint32_t acc_ph = (tc / ACC) & 1;
-        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+
+      auto copy_scales = [&](uint32_t it) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) return false;
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; break; }
-          tcgen05_fence_after();
-          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
-          uint8_t* st = smem + s * L::kBytes;
-          const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + L::kBOff);
-          const uint32_t sfa_addr = smem_u32(st + L::kSfaOff), sfb_addr = smem_u32(st + L::kSfbOff);
-          for (int a = 0; a < atoms; ++a) {
-            tcgen05_cp_32x128b_warpx4(tmem_base + L::kSfaCol + a * 4,
+        const int kb = int(it % uint32_t(num_kb));
+        const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+        uint8_t* st = smem + s * L::kBytes;
+        const uint32_t sfa_addr = smem_u32(st + L::kSfaOff), sfb_addr = smem_u32(st + L::kSfbOff);
+        const uint32_t sf_col = tmem_base + kSfBase + s * L::kSfCols;
+        if (elect_one()) {
+            for (int a = 0; a < atoms; ++a) {
+            tcgen05_cp_32x128b_warpx4(sf_col + L::kSfaColOff + a * 4,
                                       make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
 #pragma unroll
             for (int nb = 0; nb < L::kNB; ++nb)
               tcgen05_cp_32x128b_warpx4(
-                  tmem_base + L::kSfbCol + (a * L::kNB + nb) * 4,
+                  sf_col + L::kSfbColOff + (a * L::kNB + nb) * 4,
                   make_smem_desc(sfb_addr + (nb * kAtomsPerStage + a) * kAtomBytes, 0, 128, kSwizzleNone));
           }
-          for (int a = 0; a < atoms; ++a) {
-            // 64 K-elements = 32 bytes further along the 128-byte swizzled row
-            const uint64_t adesc = make_smem_desc(a_addr + a * 32, 16, 1024, kSwizzle128B);
-            const uint64_t bdesc = make_smem_desc(b_addr + a * 32, 16, 1024, kSwizzle128B);
-            mma_mxf4nvf4(tmem_d, adesc, bdesc, idesc, (kb | a) != 0 ? 1u : 0u, tmem_base + L::kSfaCol + a * 4,
-                         tmem_base + L::kSfbCol + a * L::kNB * 4);
-          }
-          tcgen05_commit(smem_u32(&empty_bar[s]));  // stage reusable once these MMAs have read it
         }
-        if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
+        __syncwarp();
+        return true;
+      };
+
+      if (total > 0) ok = copy_scales(0);
+      uint32_t it = 0, tc = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!decode_tile(g, tile).valid) continue;
+        const int acc = tc % ACC;
+        const uint32_t acc_ph = (tc / ACC) & 1;
+        ++tc;
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          if (it + 1 < total && !copy_scales(it + 1)) { ok = false; break; }
+          const int s = it % STAGES;
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          uint8_t* st = smem + s * L::kBytes;
+          const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + L::kBOff);
+          const uint32_t sf_col = tmem_base + kSfBase + s * L::kSfCols;
+          if (elect_one()) {
+            for (int a = 0; a < atoms; ++a) {
+              // 64 K-elements = 32 bytes further along the 128-byte swizzled row
+              const uint64_t adesc = make_smem_desc(a_addr + a * 32, 16, 1024, kSwizzle128B);
+              const uint64_t bdesc = make_smem_desc(b_addr + a * 32, 16, 1024, kSwizzle128B);
+              mma_mxf4nvf4(tmem_d, adesc, bdesc, idesc, (kb | a) != 0 ? 1u : 0u, sf_col + L::kSfaColOff + a * 4,
+                           sf_col + L::kSfbColOff + a * L::kNB * 4);
+            }
+            tcgen05_commit(smem_u32(&empty_bar[s]));  // stage reusable once these MMAs have read it
+          }
+          __syncwarp();
+        }
+        if (ok && elect_one()) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
+        __syncwarp();
       }
     }
   } else {
@@ -253,13 +328,21 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
     uint32_t tc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tc) {
-      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const Tile t = decode_tile(g, tile);
+      if (!t.valid) continue;
+      const int m_blk = t.m_blk, n_blk = t.n_blk;
       const int acc = tc % ACC;
       const uint32_t acc_ph = (tc / ACC) & 1;
+      ++tc;
       if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_ph, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
-      const int row = m_blk * kBlockM + quarter * 32 + lane;
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = m_blk * kBlockM + row_in_tile;
+      const bool row_ok = row_in_tile < t.rows;
+      float alpha = g.alpha;
+      if (g.group_alpha != nullptr) alpha *= g.group_alpha[t.group];
+      if (g.row_scale != nullptr && row_ok) alpha *= g.row_scale[row];
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BLOCK_N;
       if constexpr (BLOCK_N >= 32) {
 #pragma unroll 1
@@ -268,8 +351,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_ld_32x32b_x32(taddr + c * 32, r);
           tmem_ld_wait();
           const int col = n_blk * BLOCK_N + c * 32;
-          if (row < g.m && col < g.n)
-            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r, g.alpha, g.n - col, vec_ok);
+          if (row_ok && col < g.n)
+            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r, alpha, g.n - col, vec_ok);
         }
       } else {
 #pragma unroll 1
@@ -278,11 +361,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_ld_32x32b_x8(taddr + c * 8, r8);
           tmem_ld_wait();
           const int col = n_blk * BLOCK_N + c * 8;
-          if (row < g.m) {
+          if (row_ok) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (col + j < g.n) {
-                const float v = __uint_as_float(r8[j]) * g.alpha;
+                const float v = __uint_as_float(r8[j]) * alpha;
                 if constexpr (sizeof(OutT) == 4) out[int64_t(row) * g.ldc + col + j] = v;
                 else if constexpr (std::is_same<OutT, __half>::value) out[int64_t(row) * g.ldc + col + j] = __float2half_rn(v);
                 else out[int64_t(row) * g.ldc + col + j] = __float2bfloat16_rn(v);
@@ -344,12 +427,12 @@ int sm_count_gemm() {
 template <int BLOCK_N, int STAGES, typename OutT>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream) {
   using L = StageLayout<BLOCK_N>;
-  constexpr size_t smem = size_t(STAGES) * L::kBytes + (2 * STAGES + 2 * L::kAccStages) * 8 + 16 + 1024;
+  constexpr size_t smem = size_t(STAGES) * L::kBytes + (2 * STAGES + 4) * 8 + 16 + 1024;
   static_assert(smem <= 232448, "shared memory budget exceeded");
   auto kernel = nvfp4_gemm_kernel<BLOCK_N, STAGES, OutT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
     return HB200_ERR_CUDA;
-  g.m_tiles = (g.m + kBlockM - 1) / kBlockM;
+  if (g.tile_info == nullptr) g.m_tiles = (g.m + kBlockM - 1) / kBlockM;  // grouped: set by the caller
   g.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
   const int tiles = g.m_tiles * g.n_tiles;
   const int grid = tiles < sm_count_gemm() ? tiles : sm_count_gemm();
@@ -358,11 +441,11 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaSt
 }
 
 template <typename OutT>
-int dispatch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t stream) {
+int dispatch_gemm(const void* a, const void* b, GemmArgs g, int groups, cudaStream_t stream) {
   CUtensorMap ta, tb;
   const int block_n = g.n > 128 ? 256 : 128;
   if (!make_operand_map(&ta, a, g.m, g.k / 2, kBlockM)) return HB200_ERR_CUDA;
-  if (!make_operand_map(&tb, b, g.n, g.k / 2, block_n)) return HB200_ERR_CUDA;
+  if (!make_operand_map(&tb, b, int64_t(g.n) * groups, g.k / 2, block_n)) return HB200_ERR_CUDA;
   if (block_n == 256) return launch_gemm<256, 4, OutT>(ta, tb, g, stream);
   return launch_gemm<128, 6, OutT>(ta, tb, g, stream);
 }
@@ -390,11 +473,40 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
                                                                                                       : HB200_ERR_CUDA;
   }
   GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
-             int(m), int(n), int(k), alpha, 0, 0};
+             int(m), int(n), int(k), alpha, 0, 0, nullptr, 0, nullptr, nullptr};
   switch (out_dtype) {
-    case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, s);
-    case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, s);
-    default: return dispatch_gemm<float>(a_packed, b_packed, g, s);
+    case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, 1, s);
+    case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, 1, s);
+    default: return dispatch_gemm<float>(a_packed, b_packed, g, 1, s);
+  }
+}
+
+extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_packed, const void* scale_a,
+                                          const void* scale_b, void* out, const int32_t* tile_info,
+                                          int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups, int64_t ldc,
+                                          const float* row_scale, const float* group_alpha, float alpha,
+                                          int out_dtype, void* stream) {
+  using namespace hb200;
+  if (!a_packed || !b_packed || !scale_a || !scale_b || !out || !tile_info) return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles < 0 || n < 0 || k <= 0 || groups <= 0 || ldc < n || out_dtype < 0 || out_dtype > 2)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if ((k % 16) != 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a_packed) % 16 || reinterpret_cast<uintptr_t>(b_packed) % 16 ||
+      reinterpret_cast<uintptr_t>(scale_a) % 16 || reinterpret_cast<uintptr_t>(scale_b) % 16 ||
+      reinterpret_cast<uintptr_t>(tile_info) % 8)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles == 0 || n == 0) return HB200_OK;
+  if ((k % 32) != 0) return HB200_ERR_UNSUPPORTED;
+  if (max_m_tiles * 128 > 0x7fffff00 || n * groups > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  const int64_t sfb_stride = round_up64(n, 128) * round_up64(k / 16, 4);
+  GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
+             int(max_m_tiles * 128), int(n), int(k), alpha, int(max_m_tiles), 0,
+             reinterpret_cast<const int2*>(tile_info), sfb_stride, row_scale, group_alpha};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (out_dtype) {
+    case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, int(groups), s);
+    case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, int(groups), s);
+    default: return dispatch_gemm<float>(a_packed, b_packed, g, int(groups), s);
   }
 }
 

@@ -1,0 +1,134 @@
+// Expert-parallel bookkeeping for the NVFP4 MoE layer: the device-side tile
+// schedule of the grouped GEMM (no host read of the routing result) and the
+// routing-weighted combine.
+#include "common.cuh"
+
+namespace hb200 {
+namespace {
+
+// One CTA.  counts[e] tokens were routed to expert e; sorted_pairs lists the
+// (token, slot) pairs (pair = token * top_k + slot) ordered by expert, stably.
+//   padded_offsets[e] : first row of expert e when every expert is padded to 128 rows
+//   tile_info[t]      : (expert, valid rows) of 128-row tile t, (-1, 0) past the end
+//   row_of_sorted[p]  : padded row of sorted position p
+//   row_of_pair[pair] : padded row of a (token, slot) pair
+__global__ void __launch_bounds__(1024)
+moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, const int32_t* __restrict__ sorted_pairs,
+                    int pairs, int32_t* __restrict__ padded_offsets, int2* __restrict__ tile_info, int max_tiles,
+                    int32_t* __restrict__ row_of_sorted, int32_t* __restrict__ row_of_pair) {
+  extern __shared__ int32_t sh[];  // offsets[experts + 1], padded[experts + 1]
+  int32_t* off = sh;
+  int32_t* pad = sh + experts + 1;
+  if (threadIdx.x == 0) {
+    int32_t o = 0, p = 0;
+    for (int e = 0; e < experts; ++e) {
+      off[e] = o;
+      pad[e] = p;
+      const int32_t c = max(counts[e], 0);
+      o += c;
+      p += (c + 127) / 128 * 128;
+    }
+    off[experts] = o;
+    pad[experts] = p;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) padded_offsets[e] = pad[e];
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    const int32_t row0 = t * 128;
+    int2 info = make_int2(-1, 0);
+    if (row0 < pad[experts]) {
+      int lo = 0, hi = experts;  // last e with pad[e] <= row0
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (pad[mid] <= row0) lo = mid; else hi = mid;
+      }
+      const int32_t cnt = off[lo + 1] - off[lo];
+      info = make_int2(lo, min(128, cnt - (row0 - pad[lo])));
+    }
+    tile_info[t] = info;
+  }
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    int lo = 0, hi = experts;  // last e with off[e] <= p (experts with zero tokens share an offset)
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (off[mid] <= p) lo = mid; else hi = mid;
+    }
+    const int32_t row = pad[lo] + (p - off[lo]);
+    row_of_sorted[p] = row;
+    row_of_pair[sorted_pairs[p]] = row;
+  }
+}
+
+// out[t, :] = bf16(sum over the token's top_k slots, in slot order, of o[row_of_pair[t*top_k + s], :]) in fp32.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32_t* __restrict__ row_of_pair,
+                   __nv_bfloat16* __restrict__ out, int64_t tokens, int top_k, int64_t hidden) {
+  const int64_t chunks = hidden >> 3;
+  const int64_t total = tokens * chunks;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t t = i / chunks, c = i - t * chunks;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < top_k; ++s) {
+      const int64_t row = row_of_pair[t * top_k + s];
+      const uint4 v = ldg_stream_u4(o + row * ldo + c * 8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += __uint_as_float(w[e] << 16);
+        acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      }
+    }
+    uint32_t p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      p[e] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + t * hidden + c * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+  }
+}
+
+}  // namespace
+}  // namespace hb200
+
+// Device-side replacement for the host bookkeeping of
+// moe_matmul_ogs_helion_kernel_args_gen (examples/moe_matmul_ogs.py:89-124), which
+// reads max_T_per_expert back to the host; nothing here synchronises.
+extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs,
+                                        int64_t pairs, int32_t* padded_offsets, int32_t* tile_info,
+                                        int64_t max_tiles, int32_t* row_of_sorted, int32_t* row_of_pair,
+                                        void* stream) {
+  using namespace hb200;
+  if (!counts || !sorted_pairs || !padded_offsets || !tile_info || !row_of_sorted || !row_of_pair)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (experts <= 0 || experts > 4096 || pairs < 0 || max_tiles < 0 || pairs > 0x7fffff00 || max_tiles > 0xffffff)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(tile_info) % 8) return HB200_ERR_INVALID_ARGUMENT;
+  const size_t smem = size_t(2 * (experts + 1)) * sizeof(int32_t);
+  moe_schedule_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
+      counts, int(experts), sorted_pairs, int(pairs), padded_offsets, reinterpret_cast<int2*>(tile_info),
+      int(max_tiles), row_of_sorted, row_of_pair);
+  return launch_status();
+}
+
+// Routing-weighted combine of the expert outputs (the weights were folded into
+// the rows by the down-projection's epilogue).  No reference counterpart.
+extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair, void* out_bf16,
+                                 int64_t tokens, int64_t top_k, int64_t hidden, void* stream) {
+  using namespace hb200;
+  if (!expert_out_bf16 || !row_of_pair || !out_bf16) return HB200_ERR_INVALID_ARGUMENT;
+  if (tokens < 0 || top_k <= 0 || hidden < 0 || (hidden % 8) != 0 || ld < hidden || (ld % 8) != 0)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(expert_out_bf16) % 16 || reinterpret_cast<uintptr_t>(out_bf16) % 16)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (tokens == 0 || hidden == 0) return HB200_OK;
+  const int64_t items = tokens * hidden / 8;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t need = ceil_div64(items, 256);
+  const int grid = int(need < int64_t(sms) * 8 ? need : int64_t(sms) * 8);
+  moe_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(expert_out_bf16), ld, row_of_pair, static_cast<__nv_bfloat16*>(out_bf16),
+      tokens, int(top_k), hidden);
+  return launch_status();
+}

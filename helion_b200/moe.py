@@ -1,0 +1,168 @@
+"""NVFP4 mixture-of-experts layer on the grouped tcgen05 GEMM.
+
+The reference ships a top-1 bf16/fp16 expert GEMM (``moe_matmul_ogs``,
+examples/moe_matmul_ogs.py:31-124) whose argument generator sorts tokens by expert
+on the host side of the stream and reads ``max_T_per_expert`` back.  This module is
+the NVFP4, top-k form of that operator: routing (softmax, top-k, stable sort by
+expert) stays in tensor code on the device, the schedule is built by a kernel, and
+nothing synchronises with the host.
+
+Pipeline for tokens ``x [T, H]``:
+  route -> per-token NVFP4 quantisation of the gathered rows -> grouped GEMM with
+  ``W_gu [E, 2I, H]`` (bf16 out) -> fused SiLU-mul + per-token NVFP4 quantisation ->
+  grouped GEMM with ``W_d [E, H, I]`` (routing weight folded into the row scale) ->
+  combine over the top-k slots.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .layouts import ceil_div
+from .layouts import swizzled_scale_numel
+from .ops import _require_cuda
+from .ops import _stream
+
+
+@dataclass
+class GroupedNvfp4Weight:
+    """Expert weights ``[E, N, K]`` quantised to NVFP4: packed codes ``[E, N, K/2]`` (uint8), one swizzled
+    e4m3 scale buffer per expert back to back (``[E, swizzled_scale_numel(N, K/16)]``) and one fp32 global
+    scale per expert ``[E]``."""
+
+    packed: Tensor
+    scales: Tensor
+    global_scale: Tensor
+
+    @property
+    def experts(self) -> int:
+        return self.packed.shape[0]
+
+    @property
+    def n(self) -> int:
+        return self.packed.shape[1]
+
+    @property
+    def k(self) -> int:
+        return self.packed.shape[2] * 2
+
+
+def quantize_expert_weights(w: Tensor) -> GroupedNvfp4Weight:
+    """``[E, N, K]`` float weights -> :class:`GroupedNvfp4Weight` with a global scale per expert (on ``w``'s device,
+    through the CUDA quantiser)."""
+    from .ops import nvfp4_quantize
+
+    e, n, k = w.shape
+    packed = torch.empty(e, n, k // 2, dtype=torch.uint8, device=w.device)
+    scales = torch.empty(e, swizzled_scale_numel(n, k // 16), dtype=torch.uint8, device=w.device)
+    gs = torch.empty(e, dtype=torch.float32, device=w.device)
+    for i in range(e):
+        wb = w[i].to(torch.bfloat16)  # the quantiser consumes bf16; the global scale must see the same values
+        g = (wb.abs().amax().to(torch.float32) / (6.0 * 448.0)).reshape(1)
+        c, s, _ = nvfp4_quantize(wb, g)
+        packed[i], scales[i], gs[i] = c, s.view(torch.uint8), g[0]
+    return GroupedNvfp4Weight(packed, scales.view(torch.float8_e4m3fn), gs)
+
+
+def route_top_k(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
+    """softmax over experts in fp32, then top-k; weights are used as produced (not renormalised)."""
+    probs = torch.softmax(router_logits.to(torch.float32), dim=-1)
+    return torch.topk(probs, top_k, dim=-1)
+
+
+@dataclass
+class MoeSchedule:
+    max_tiles: int
+    tile_info: Tensor       # int32 [max_tiles, 2]
+    padded_offsets: Tensor  # int32 [E + 1]
+    sorted_pairs: Tensor    # int32 [T * top_k]
+    row_of_sorted: Tensor   # int32 [T * top_k]
+    row_of_pair: Tensor     # int32 [T * top_k]
+
+
+def build_schedule(experts_per_token: Tensor, num_experts: int) -> MoeSchedule:
+    """Sort the (token, slot) pairs by expert (stable, as examples/moe_matmul_ogs.py:107-109 does for
+    top-1) and lay the experts out in 128-row padded groups; all on the device."""
+    _require_cuda(experts_per_token)
+    flat = experts_per_token.reshape(-1)
+    pairs = flat.numel()
+    sorted_pairs = torch.argsort(flat, stable=True).to(torch.int32)
+    counts = torch.bincount(flat, minlength=num_experts).to(torch.int32)
+    max_tiles = ceil_div(pairs, 128) + num_experts  # bound that does not depend on the routing
+    dev = flat.device
+    tile_info = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
+    padded_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    row_of_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)
+    row_of_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call(
+            "hb200_moe_build_schedule", counts.data_ptr(), num_experts, sorted_pairs.data_ptr(), pairs,
+            padded_offsets.data_ptr(), tile_info.data_ptr(), max_tiles, row_of_sorted.data_ptr(),
+            row_of_pair.data_ptr(), _stream(),
+        )
+    return MoeSchedule(max_tiles, tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair)
+
+
+def _quantize_rows(x: Tensor, k: int, sched: MoeSchedule, src_div: int, item_scale: Tensor | None, silu_mul: bool,
+                   gather: bool):
+    rows = sched.max_tiles * 128
+    dev = x.device
+    codes = torch.empty(rows, k // 2, dtype=torch.uint8, device=dev)
+    scales = torch.empty(swizzled_scale_numel(rows, k // 16), dtype=torch.uint8, device=dev)
+    gscale = torch.zeros(rows, dtype=torch.float32, device=dev)
+    items = sched.sorted_pairs.numel()
+    with torch.cuda.device(dev):
+        _lib.call(
+            "hb200_nvfp4_quantize_rows", x.data_ptr(), codes.data_ptr(), scales.data_ptr(), gscale.data_ptr(),
+            items, k, x.stride(0),
+            sched.sorted_pairs.data_ptr() if gather else sched.row_of_sorted.data_ptr(), src_div,
+            sched.row_of_sorted.data_ptr(), None if item_scale is None else item_scale.data_ptr(),
+            int(silu_mul), _stream(),
+        )
+    return codes, scales, gscale
+
+
+def grouped_matmul(a_codes: Tensor, a_scales: Tensor, w: GroupedNvfp4Weight, sched: MoeSchedule,
+                   row_scale: Tensor | None, out_dtype: torch.dtype = torch.bfloat16) -> Tensor:
+    """``out[r] = row_scale[r] * w.global_scale[g(r)] * A[r] @ W[g(r)]^T`` over the padded row layout."""
+    rows = sched.max_tiles * 128
+    out = torch.empty(rows, w.n, dtype=out_dtype, device=a_codes.device)
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]
+    with torch.cuda.device(a_codes.device):
+        _lib.call(
+            "hb200_nvfp4_grouped_matmul", a_codes.data_ptr(), w.packed.data_ptr(), a_scales.data_ptr(),
+            w.scales.data_ptr(), out.data_ptr(), sched.tile_info.data_ptr(), sched.max_tiles, w.n, w.k,
+            w.experts, w.n, None if row_scale is None else row_scale.data_ptr(), w.global_scale.data_ptr(),
+            1.0, code, _stream(),
+        )
+    return out
+
+
+def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNvfp4Weight,
+              w_down: GroupedNvfp4Weight) -> Tensor:
+    """NVFP4 MoE layer: ``x [T, H]`` bf16, ``router_logits [T, E]`` -> bf16 ``[T, H]``."""
+    _require_cuda(x, router_logits)
+    if x.dtype is not torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous 2D bfloat16 tensor")
+    t, h = x.shape
+    e = w_gate_up.experts
+    inter = w_gate_up.n // 2
+    if w_gate_up.k != h or w_down.k != inter or w_down.n != h or w_down.experts != e:
+        raise ValueError("expert weight shapes do not match the activations")
+    weights, experts = route_top_k(router_logits, top_k)
+    sched = build_schedule(experts, e)
+    # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
+    w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()
+    a1, sf1, g1 = _quantize_rows(x, h, sched, top_k, None, False, gather=True)
+    h1 = grouped_matmul(a1, sf1, w_gate_up, sched, g1)
+    a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, w_sorted, True, gather=False)
+    o = grouped_matmul(a2, sf2, w_down, sched, g2)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(), out.data_ptr(),
+                  t, top_k, h, _stream())
+    return out

@@ -124,6 +124,47 @@ int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_packed, const 
                               const void* scale_b, void* out, int64_t m, int64_t n, int64_t k, int64_t ldc,
                               float alpha, int out_dtype, void* stream);
 
+/* ------------------------------------------------------- grouped NVFP4 GEMM
+ * The MoE expert GEMM: out[r, :] = out_dtype(alpha * group_alpha[g] * row_scale[r]
+ * * A[r, :] . B[g]^T) for every row r of group g.  Rows of A (and of out) are laid
+ * out group after group, each group padded to a multiple of 128 rows, as produced
+ * by hb200_moe_build_schedule; tile_info holds (group, valid rows) per 128-row
+ * tile as int32 pairs, group < 0 for unused tiles (read on the device only).
+ * b_packed is [groups, N, K/2]; scale_b holds one swizzled [N, K/16] buffer per
+ * group, back to back; scale_a is the swizzled buffer for logical
+ * [max_m_tiles*128, K/16].  row_scale / group_alpha may be null.
+ * Generalises grouped_gemm_deepgemm's worklist form
+ * (pretuned_kernels/grouped_gemm_deepgemm/grouped_gemm_deepgemm.py:172-224) and
+ * moe_matmul_ogs (examples/moe_matmul_ogs.py:31-85) to NVFP4 operands. */
+int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_packed, const void* scale_a,
+                               const void* scale_b, void* out, const int32_t* tile_info, int64_t max_m_tiles,
+                               int64_t n, int64_t k, int64_t groups, int64_t ldc, const float* row_scale,
+                               const float* group_alpha, float alpha, int out_dtype, void* stream);
+
+/* Device-side schedule of the grouped GEMM from a routing result (no host read):
+ * counts[experts] tokens per expert and sorted_pairs[pairs] = the (token, slot)
+ * pairs (token * top_k + slot) ordered by expert, stably.  Writes
+ * padded_offsets[experts+1], tile_info[max_tiles] (int32 pairs), the padded row of
+ * every sorted position and of every pair.  Replaces the host bookkeeping of
+ * moe_matmul_ogs_helion_kernel_args_gen (examples/moe_matmul_ogs.py:89-124). */
+int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs, int64_t pairs,
+                             int32_t* padded_offsets, int32_t* tile_info, int64_t max_tiles,
+                             int32_t* row_of_sorted, int32_t* row_of_pair, void* stream);
+
+/* Per-token NVFP4 quantisation of gathered rows; with silu_mul != 0 the row is
+ * bf16(silu(x[:, :k]) * x[:, k:2k]) of a [*, 2k] input.  Item i reads source row
+ * src_idx[i] / src_div (i if src_idx is null) and writes at row dst_idx[i] (i if
+ * null); global_scale[row] = row_amax / (6*448) * item_scale[i] (1 if null).
+ * No reference counterpart (see hb200_nvfp4_quantize). */
+int hb200_nvfp4_quantize_rows(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
+                              int64_t items, int64_t k, int64_t ldx, const int32_t* src_idx, int src_div,
+                              const int32_t* dst_idx, const float* item_scale, int silu_mul, void* stream);
+
+/* out[t, :] = bf16(sum_s expert_out[row_of_pair[t * top_k + s], :]) in fp32, slot
+ * order.  No reference counterpart (the reference has no top-k combine). */
+int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair, void* out_bf16,
+                      int64_t tokens, int64_t top_k, int64_t hidden, void* stream);
+
 /* Sticky device-side status: HB200_OK, or HB200_ERR_DEVICE_TIMEOUT once a
  * kernel gave up a bounded wait (its outputs are then undefined).  reset != 0
  * clears it.  Synchronises the device; not for use on the hot path.  (No

@@ -1,0 +1,123 @@
+"""Grouped NVFP4 GEMM and the NVFP4 MoE layer against the CPU oracle."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helion_b200 as hb
+from helion_b200 import _lib
+from helion_b200 import moe as M
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(y, ref):
+    y, ref = y.detach().float().cpu(), ref.detach().float().cpu()
+    assert torch.isfinite(y).all()
+    floor = ref.pow(2).mean().sqrt().clamp(min=1e-30)
+    return float(((y - ref).abs() / torch.maximum(ref.abs(), floor)).max())
+
+
+def oracle_weights(w: torch.Tensor):
+    """Quantise ``[E, N, K]`` with the oracle, one global scale per expert; returns oracle-side lists and the device-side bundle."""
+    packed, scales, gs = [], [], []
+    for e in range(w.shape[0]):
+        p, s, g = O.nvfp4_quantize(w[e])
+        packed.append(p)
+        scales.append(s)
+        gs.append(g)
+    bundle = M.GroupedNvfp4Weight(
+        torch.stack(packed).to(DEV), torch.stack([s.view(torch.uint8) for s in scales]).to(DEV).view(torch.float8_e4m3fn),
+        torch.stack(gs).to(DEV),
+    )
+    return torch.stack(packed), scales, torch.stack(gs), bundle
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 130, 1, 0, 128, 256, 3], [0, 0, 0, 7], [128], [1, 1, 1, 1, 1]])
+def test_schedule_edge_cases(counts):
+    """Ragged groups incl. empty, single-row, exactly-full and multi-tile experts
+    (the cases of test/test_cute_grouped_gemm_split_sizes.py:620-745 that apply to a routing result)."""
+    e = len(counts)
+    experts = torch.cat([torch.full((c,), i, dtype=torch.int64) for i, c in enumerate(counts)])
+    experts = experts[torch.randperm(experts.numel(), generator=torch.Generator().manual_seed(0))]
+    sched = M.build_schedule(experts.to(DEV).reshape(-1, 1), e)
+    torch.cuda.synchronize()
+    pad = [0]
+    for c in counts:
+        pad.append(pad[-1] + (c + 127) // 128 * 128)
+    assert sched.padded_offsets.cpu().tolist() == pad
+    info = sched.tile_info.cpu().tolist()
+    assert len(info) == (sum(counts) + 127) // 128 + e
+    for t, (g, rows) in enumerate(info):
+        row0 = t * 128
+        if row0 >= pad[-1]:
+            assert (g, rows) == (-1, 0)
+        else:
+            exp_g = max(i for i in range(e) if pad[i] <= row0 and counts[i] > 0 and row0 < pad[i + 1])
+            assert g == exp_g and rows == min(128, counts[g] - (row0 - pad[g]))
+    # stable order: inside an expert rows follow the original pair order
+    order, _, offsets = O.moe_sort(experts.reshape(-1, 1), e)
+    assert torch.equal(sched.sorted_pairs.cpu(), order)
+    rows = sched.row_of_sorted.cpu()
+    for i, c in enumerate(counts):
+        assert rows[offsets[i] : offsets[i] + c].tolist() == list(range(pad[i], pad[i] + c))
+    assert torch.equal(sched.row_of_pair.cpu()[order.long()], rows)
+
+
+def test_grouped_matmul_against_oracle():
+    torch.manual_seed(0)
+    e, n, k = 6, 384, 512
+    counts = [70, 0, 200, 1, 128, 33]
+    w = torch.randn(e, n, k) * 0.02
+    wp, ws, wg, bundle = oracle_weights(w)
+    experts = torch.cat([torch.full((c,), i, dtype=torch.int64) for i, c in enumerate(counts)])
+    experts = experts[torch.randperm(experts.numel())]
+    x = torch.randn(experts.numel(), k).to(torch.bfloat16)
+    sched = M.build_schedule(experts.to(DEV).reshape(-1, 1), e)
+    a, sf, g = M._quantize_rows(x.to(DEV), k, sched, 1, None, False, gather=True)
+    out = M.grouped_matmul(a, sf, bundle, sched, g, torch.float32)
+    torch.cuda.synchronize()
+    assert _lib.load().hb200_device_status(1) == 0
+    rows = sched.row_of_pair.cpu().long()
+    ap, asc, ag = O.nvfp4_quantize(x, per_token=True)
+    aq = O.dequant_scaled_k_major(ap, asc) * ag.reshape(-1, 1)
+    ref = torch.empty(x.shape[0], n)
+    for i in range(e):
+        idx = (experts == i).nonzero(as_tuple=True)[0]
+        ref[idx] = aq[idx] @ (O.dequant_scaled_k_major(wp[i], ws[i]) * wg[i]).t()
+    assert rel_err(out.cpu()[rows], ref) <= 1e-4
+
+
+@pytest.mark.parametrize("t,h,inter,e,k", [(64, 256, 128, 8, 2), (300, 512, 384, 16, 4), (128, 256, 256, 4, 1)])
+def test_moe_layer_against_oracle(t, h, inter, e, k):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    logits = torch.randn(t, e, generator=g)
+    w_gu = torch.randn(e, 2 * inter, h, generator=g) * 0.02
+    w_d = torch.randn(e, h, inter, generator=g) * 0.02
+    gp, gsc, gg, gu_bundle = oracle_weights(w_gu)
+    dp, dsc, dg, d_bundle = oracle_weights(w_d)
+    ref = O.nvfp4_moe(x, logits, k, gp, gsc, gg, dp, dsc, dg)
+    y = M.nvfp4_moe(x.to(DEV), logits.to(DEV), k, gu_bundle, d_bundle)
+    torch.cuda.synchronize()
+    assert _lib.load().hb200_device_status(1) == 0
+    assert y.shape == (t, h) and y.dtype is torch.bfloat16
+    # Two quantisation steps sit between input and output: a last-place difference in exp() or in the fp32
+    # summation order can flip one bf16 rounding of the intermediate and with it one 4-bit code, which moves a
+    # single output by about one percent.  Bound the worst element at 2e-2 and the overall error far tighter.
+    assert rel_err(y, ref) <= 2e-2
+    yc, rc = y.float().cpu(), ref.float()
+    assert float((yc - rc).pow(2).mean().sqrt() / rc.pow(2).mean().sqrt()) <= 2e-3
+
+
+def test_device_weight_quantiser_matches_oracle():
+    torch.manual_seed(5)
+    w = torch.randn(3, 128, 256) * 0.02
+    wp, ws, wg, _ = oracle_weights(w.to(torch.bfloat16).float())
+    b = M.quantize_expert_weights(w.to(DEV))
+    assert torch.equal(b.packed.cpu(), wp)
+    assert torch.equal(b.global_scale.cpu(), wg)
+    assert torch.equal(b.scales.cpu().view(torch.uint8), torch.stack([s.view(torch.uint8) for s in ws]))
