@@ -1,16 +1,24 @@
 """Benchmark driver: ``python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]``.
 
-Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of synthetic input:
+Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of synthetic input, with the
+inputs already resident in HBM; ``e2e`` repeats it through the public operator API from pinned host buffers.
 
-* ``gemv_decode_layer`` : the four NVFP4 weight matrices of a 70B-class dense layer (QKV 10240x8192,
-  O 8192x8192, gate|up 57344x8192, down 8192x28672) applied to one bf16 activation row each (M=1);
-  481 MB of weights per step, so every step streams far more than the 126 MB L2 (no flush needed).
-  metric = HBM bytes the step must move / time (TB/s).  With N GPUs the rows of every matrix are split
-  evenly (column tensor parallelism) and the bf16 outputs are all-gathered over NCCL.
+Workloads (``--workload``):
+  gemm   (default) dense NVFP4 GEMM, M=N=K=8192: A ~ N(0,1) bf16 and B ~ N(0,0.02), both quantised to NVFP4
+         (16-wide blocks, e4m3 scales, fp32 global scale); bf16 output; metric TFLOP/s.  With N GPUs the
+         rows of B (output columns) are split evenly and the outputs all-gathered.
+  gemv   the four NVFP4 matrices of a 70B-class dense layer applied to M activation rows (--batch, default 1);
+         metric TB/s of HBM traffic the step must move; column-parallel over N GPUs.
+  moe    NVFP4 MoE layer: 8192 tokens, hidden 4096, 128 experts, top-8, intermediate 1536; metric TFLOP/s;
+         expert-parallel over N GPUs.
+  quant  the fused FP8 quant producers at 16384 tokens (RMSNorm hidden 7168 as the headline; the others in
+         ``ops``); metric TB/s.
 
-Timing: CUDA events on the launching stream, barrier + synchronize on both sides, max over ranks.
-``--impl reference`` times the reference's CPU path (the oracle port of its PyTorch reference functions)
-on the host cores, on a bounded sample of the same workload.
+Timing: every step is bracketed by its own CUDA-event pair on the launching stream and the L2 is flushed
+(a 256 MB write) between steps, outside the pairs; ms_per_step is the mean over K steps and the max over
+ranks.  Steps whose launch sequence is fixed are replayed from a CUDA graph so that the host does not sit
+between kernels.  ``--impl reference`` times the CPU port of the reference's PyTorch reference functions on
+a bounded sample of the same workload.
 """
 
 from __future__ import annotations
@@ -29,6 +37,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 LAYER_70B = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
+MOE_CFG = dict(tokens=8192, hidden=4096, experts=128, top_k=8, inter=1536)
+GEMM_CFG = dict(m=8192, n=8192, k=8192)
 
 
 def gemv_bytes(n: int, k: int, m: int = 1) -> int:
@@ -36,17 +46,17 @@ def gemv_bytes(n: int, k: int, m: int = 1) -> int:
     return n * k // 2 + n * k // 16 + 2 * m * k + 2 * m * n
 
 
+def moe_flops(c=MOE_CFG) -> int:
+    pairs = c["tokens"] * c["top_k"]
+    return 2 * pairs * c["hidden"] * 2 * c["inter"] + 2 * pairs * c["inter"] * c["hidden"]
+
+
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
 
-    REASONS = {
-        0x8: "hw_slowdown",
-        0x40: "hw_thermal_slowdown",
-        0x20: "sw_thermal_slowdown",
-        0x4: "sw_power_cap",
-        0x80: "hw_power_brake_slowdown",
-    }
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, index: int):
         self.samples: list[int] = []
@@ -75,7 +85,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.02)
 
     def __enter__(self):
         if self._nv is not None:
@@ -90,61 +100,100 @@ class ClockSampler:
 
     def summary(self) -> dict:
         s = sorted(self.samples)
-        return {
-            "sm_mhz": s[len(s) // 2] if s else None,
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(s),
-        }
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
 
 
-def measured_peaks() -> tuple[float, float, str]:
-    """(HBM GB/s, dense bf16 TFLOP/s, provenance)."""
+def measured_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
-    return 6650.0, 1590.0, "fallback"
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
 
 
-def ncu_traffic(kernel_key: str):
+def ncu_traffic(key: str):
     """DRAM bytes per launch recorded from an ncu capture (profiles/traffic.json), or None."""
     p = ROOT / "profiles" / "traffic.json"
     if p.exists():
-        return json.loads(p.read_text()).get(kernel_key)
+        return json.loads(p.read_text()).get(key)
     return None
 
 
-# ------------------------------------------------------------- reference arm
-def cpu_sample_gemv(seconds_budget: float = 8.0):
-    """Times the oracle port of reference_nvfp4_gemv_bf16in on a bounded slice of the O-projection
-    (rows x 8192) with all host threads; returns (TB/s, cores, sample description, seconds per call)."""
+# ------------------------------------------------------------------ timing
+class Timer:
+    def __init__(self, dev, world: int):
+        self.dev = dev
+        self.world = world
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def sync(self):
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(self, step, steps: int, warmup: int) -> float:
+        """Mean milliseconds per step (max over ranks): per-step event pairs, L2 flushed between steps."""
+        for _ in range(warmup):
+            step()
+        self.sync()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in pairs:
+            self.flush_buf.zero_()
+            s.record()
+            step()
+            e.record()
+        self.sync()
+        ms = sum(s.elapsed_time(e) for s, e in pairs) / steps
+        if self.world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([ms], device=self.dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        return ms
+
+
+def graphed(fn, warmup: int = 3):
+    """Capture ``fn`` (fixed launch sequence, static buffers) in a CUDA graph; returns (replay, outputs)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = fn()
+    return g.replay, out
+
+
+def rel_err(y, ref) -> float:
+    y, ref = y.detach().float().cpu(), ref.detach().float().cpu()
+    floor = ref.pow(2).mean().sqrt().clamp(min=1e-30)
+    return float(((y - ref).abs() / torch.maximum(ref.abs(), floor)).max())
+
+
+# ------------------------------------------------------------- CPU baselines
+def cpu_gemm(seconds: float = 8.0):
+    """Oracle port of reference_nvfp4_w4a4_matmul semantics (dequantise -> fp32 matmul) on a 1024x1024x8192 slice."""
     from oracle import oracle as O
 
     torch.set_num_threads(os.cpu_count() or 1)
-    k = 8192
-    rows = 1024
-    g = torch.Generator().manual_seed(4)
-    w = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, generator=g)
-    x = torch.randn(k, generator=g).to(torch.bfloat16)
-    s = O.swizzle_scales((torch.rand(rows, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn))
-    O.nvfp4_gemv_bf16in(w, x, s, 1.0)  # warm-up
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        O.nvfp4_gemv_bf16in(w, x, s, 1.0)
-        reps += 1
-        if time.perf_counter() - t0 > seconds_budget or reps >= 50:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    tbs = gemv_bytes(rows, k) / dt / 1e12
-    return tbs, torch.get_num_threads(), f"{rows}x{k} slice of the O projection, {reps} calls", dt
+    m = n = 1024
+    k = GEMM_CFG["k"]
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, generator=g)
+    b = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, generator=g)
+    sa = O.swizzle_scales((torch.rand(m, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn))
+    sb = O.swizzle_scales((torch.rand(n, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn))
+
+    def step():
+        return O.nvfp4_scaled_matmul(a, b, sa, sb)
+
+    return step, 2 * m * n * k, f"{m}x{n}x{k} slice of the 8192^3 GEMM (dequantise -> fp32 matmul -> bf16)"
 
 
-def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def cpu_gemv():
     from oracle import oracle as O
 
     torch.set_num_threads(os.cpu_count() or 1)
@@ -153,63 +202,347 @@ def run_reference(args) -> None:
     w = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, generator=g)
     x = torch.randn(k, generator=g).to(torch.bfloat16)
     s = O.swizzle_scales((torch.rand(rows, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn))
-    for _ in range(args.warmup):
-        O.nvfp4_gemv_bf16in(w, x, s, 1.0)
+    return (lambda: O.nvfp4_gemv_bf16in(w, x, s, 1.0)), gemv_bytes(rows, k), f"{rows}x{k} slice of the O projection"
+
+
+def cpu_quant():
+    from oracle import oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    t, h = 2048, 7168
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    w = (torch.rand(h, generator=g) + 0.5).to(torch.bfloat16)
+    return (lambda: O.rms_norm_dynamic_per_token_quant(x, w, 1e-6)), 2 * t * h + 2 * h + t * h + 4 * t, f"{t} of 16384 tokens"
+
+
+def cpu_moe():
+    from oracle import oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    t, h, inter, e, k = 256, MOE_CFG["hidden"], MOE_CFG["inter"], 8, 2
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    logits = torch.randn(t, e, generator=g)
+    gu = [O.nvfp4_quantize(torch.randn(2 * inter, h, generator=g) * 0.02) for _ in range(e)]
+    dn = [O.nvfp4_quantize(torch.randn(h, inter, generator=g) * 0.02) for _ in range(e)]
+    gp, gs, gg = torch.stack([p for p, _, _ in gu]), [s for _, s, _ in gu], torch.stack([q for _, _, q in gu])
+    dp, ds, dg = torch.stack([p for p, _, _ in dn]), [s for _, s, _ in dn], torch.stack([q for _, _, q in dn])
+    flops = 2 * t * k * h * 2 * inter + 2 * t * k * inter * h
+    return (lambda: O.nvfp4_moe(x, logits, k, gp, gs, gg, dp, ds, dg)), flops, f"{t} tokens, {e} experts, top-{k} (same hidden/intermediate sizes)"
+
+
+CPU_WORKLOADS = {"gemm": (cpu_gemm, 1e12, "TFLOP/s"), "gemv": (cpu_gemv, 1e12, "TB/s"), "quant": (cpu_quant, 1e12, "TB/s"),
+                 "moe": (cpu_moe, 1e12, "TFLOP/s")}
+METRICS = {"gemm": "nvfp4_gemm_tflops", "gemv": "nvfp4_gemv_hbm_throughput", "quant": "fp8_quant_producer_hbm_throughput",
+           "moe": "nvfp4_moe_tflops"}
+
+
+def time_cpu(workload: str, budget_s: float = 10.0, steps: int | None = None, warmup: int = 1):
+    make, scale, unit = CPU_WORKLOADS[workload]
+    step, work, sample = make()
+    for _ in range(max(1, warmup)):
+        step()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.nvfp4_gemv_bf16in(w, x, s, 1.0)
-    dt = (time.perf_counter() - t0) / args.steps
-    value = gemv_bytes(rows, k) / dt / 1e12
-    sample = f"each step = reference_nvfp4_gemv_bf16in semantics on a {rows}x{k} slice of the O projection"
+    reps = 0
+    while True:
+        step()
+        reps += 1
+        if steps is not None:
+            if reps >= steps:
+                break
+        elif time.perf_counter() - t0 > budget_s or reps >= 50:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return work / dt / scale, unit, torch.get_num_threads(), f"{sample}; {reps} calls", dt
+
+
+def run_reference(args) -> None:
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    value, unit, cores, sample, dt = time_cpu(args.workload, steps=args.steps, warmup=args.warmup)
     line = {
-        "impl": "reference",
-        "metric": "nvfp4_gemv_hbm_throughput",
-        "value": value,
-        "unit": "TB/s",
-        "n_gpus": args.gpus,
-        "steps": args.steps,
-        "warmup": args.warmup,
-        "ms_per_step": dt * 1e3,
-        "higher_is_better": True,
-        "scaling": "strong",
-        "vs_baseline": None,
-        "dtype": "fp32",
-        "data": "synthetic",
-        "config": {"workload": "gemv_decode_layer", "batch": 1, "layer": "70B-class dense (cfg 4)", "sampled": True},
-        "cpu_baseline": {"value": value, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRICS[args.workload], "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": args.workload, "sampled": True},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-# ------------------------------------------------------------------ GPU arm
-def build_layer(dev, rank: int, world: int):
-    """Synthetic 70B-class layer: W ~ N(0, 0.02) quantised to NVFP4 by the CUDA quantiser; each rank keeps
-    rows [rank*N/world, (rank+1)*N/world) of every matrix (N/world is a multiple of 128 for world <= 8)."""
+# ------------------------------------------------------------------ workloads
+def random_nvfp4(rows: int, k: int, dev, seed: int, sigma: float):
+    """N(0, sigma) matrix quantised to NVFP4 by the CUDA quantiser in row chunks (keeps device memory small)."""
     import helion_b200 as hb
 
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    codes = torch.empty(rows, k // 2, dtype=torch.uint8, device=dev)
+    chunks = []
+    g = torch.tensor(sigma * 6.0 / (6.0 * 448.0), device=dev, dtype=torch.float32)  # amax taken as 6 sigma
+    for r0 in range(0, rows, 2048):
+        r1 = min(rows, r0 + 2048)
+        w = (torch.randn(r1 - r0, k, generator=gen, device=dev) * sigma).to(torch.bfloat16)
+        c, s, _ = hb.nvfp4_quantize(w, g)
+        codes[r0:r1] = c
+        chunks.append(s.view(torch.uint8))
+    return codes, torch.cat(chunks).view(torch.float8_e4m3fn), float(g)
+
+
+def wl_gemm(args, dev, rank, world, timer):
+    import helion_b200 as hb
+    from helion_b200 import dist as D
+    from oracle import oracle as O
+
+    m, n, k = GEMM_CFG["m"], GEMM_CFG["n"], GEMM_CFG["k"]
+    n_local = n // world
+    host_a = torch.randn(m, k, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+    a_dev = host_a.to(dev)
+    ga = hb.layouts.nvfp4_global_scale(a_dev).reshape(1)
+    a_codes, a_scales, _ = hb.nvfp4_quantize(a_dev, ga)
+    b_codes, b_scales, gb = random_nvfp4(n_local, k, dev, 1000 + rank, 0.02)
+    alpha = float(ga) * gb
+
+    def gemm_only():
+        return hb.nvfp4_scaled_matmul(a_codes, b_codes.t(), a_scales, b_scales, alpha=alpha)
+
+    def step():
+        y = gemm_only()
+        return D.all_gather_columns(y) if world > 1 else y
+
+    # parity on a slice, against the oracle
+    y = gemm_only()
+    ref = O.nvfp4_scaled_matmul(a_codes[:256].cpu(), b_codes[:256].cpu(), a_scales[: 256 * (k // 16)].cpu(),
+                                b_scales[: 256 * (k // 16)].cpu(), torch.float32, alpha=alpha)
+    parity = rel_err(y[:256, :256], ref)
+
+    replay = step if world > 1 else graphed(step)[0]
+    ms = timer.run(replay, args.steps, args.warmup)
+    flops = 2 * m * n * k
+    extra = {}
+    if world > 1:
+        ms_gemm = timer.run(graphed(gemm_only)[0], args.steps, args.warmup)
+        extra["gemm_only_ms"] = ms_gemm
+
+    host_out = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        a = host_a.to(dev, non_blocking=True)
+        c, s, _ = hb.nvfp4_quantize(a, ga)
+        y = hb.nvfp4_scaled_matmul(c, b_codes.t(), s, b_scales, alpha=alpha)
+        if world > 1:
+            y = D.all_gather_columns(y)
+        host_out.copy_(y, non_blocking=True)
+
+    e2e_ms = timer.run(e2e_step, max(3, args.steps // 10), 3)
+    peaks = measured_peaks()
+    ach = 2 * m * n_local * k / (extra.get("gemm_only_ms", ms) * 1e-3) / 1e12
+    roof = {
+        "bound": "tensor", "kernel": "nvfp4_gemm_kernel", "launch": f"{m}x{n_local}x{k}",
+        "achieved": ach, "peak": 4 * peaks["bf16_tflops"],
+        "peak_kind": f"4 x {peaks['kind']} dense bf16 burst (e2m1 runs at four times the bf16 rate of the same pipe); nominal dense FP4 is 9000",
+        "unit": "TFLOP/s", "frac": ach / (4 * peaks["bf16_tflops"]), "frac_of_nominal": ach / 9000.0,
+        "traffic": ncu_traffic("gemm_8192"),
+    }
+    return dict(value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s", ms=ms, e2e_value=flops / (e2e_ms * 1e-3) / 1e12,
+                e2e_ms=e2e_ms, h2d=host_a.numel() * 2, d2h=host_out.numel() * 2, launches=1 + (1 if world > 1 else 0),
+                roofline=roof, parity=parity, extra=extra,
+                dtype="e2m1 x e2m1 with e4m3 block scales, fp32 accumulate, bf16 out",
+                config={"workload": "gemm", "m": m, "n": n, "k": k, "parallelism": f"column-tp{world}" if world > 1 else "single",
+                        "l2": "flushed between steps"})
+
+
+def wl_gemv(args, dev, rank, world, timer):
+    import helion_b200 as hb
+    from helion_b200 import dist as D
+    from oracle import oracle as O
+
+    batch = args.batch
     mats = {}
     for i, (name, (n, k)) in enumerate(LAYER_70B.items()):
-        n_local = n // world
-        gen = torch.Generator(device=dev).manual_seed(4 * 1000 + i * 16 + rank)
-        codes = torch.empty(n_local, k // 2, dtype=torch.uint8, device=dev)
-        scale_chunks = []
-        # global scale from the distribution's expected amax keeps ranks consistent: ~4.9 sigma over 5e8 draws
-        g = torch.tensor(0.02 * 6.0 / (6.0 * 448.0), device=dev, dtype=torch.float32)
-        chunk = 2048
-        for r0 in range(0, n_local, chunk):
-            w = (torch.randn(min(chunk, n_local - r0), k, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
-            c, s, _ = hb.nvfp4_quantize(w, g)
-            codes[r0 : r0 + w.shape[0]] = c
-            scale_chunks.append(s.view(torch.uint8))
-        scales = torch.cat(scale_chunks).view(torch.float8_e4m3fn)  # chunks are multiples of 128 rows
-        mats[name] = (codes, scales, float(g), n, k)
-    return mats
+        c, s, g = random_nvfp4(n // world, k, dev, 4000 + 16 * i + rank, 0.02)
+        mats[name] = (c, s, g, n, k)
+    gen = torch.Generator().manual_seed(4)
+    host_x = {nm: torch.randn(batch, k, generator=gen).to(torch.bfloat16).pin_memory() for nm, (_, k) in LAYER_70B.items()}
+    dev_x = {nm: t.to(dev) for nm, t in host_x.items()}
+
+    def one(name, x):
+        c, s, g, n, k = mats[name]
+        if batch == 1:
+            return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g).reshape(1, -1)
+        return hb.nvfp4_gemv_bf16in_batched(c, x, s, g)
+
+    def layer(xs):
+        outs = {}
+        for name in mats:
+            y = one(name, xs[name])
+            outs[name] = D.all_gather_columns(y) if world > 1 else y
+        return outs
+
+    c, s, g, n, k = mats["o"]
+    y = one("o", dev_x["o"])[0, :256]
+    ref = O.nvfp4_gemv_bf16in(c[:256].cpu(), host_x["o"][0], s[: 256 * (k // 16)].cpu(), g) if batch == 1 else \
+        O.nvfp4_gemm_bf16in(c[:256].cpu(), host_x["o"], s[: 256 * (k // 16)].cpu(), g)[0]
+    parity = rel_err(y, ref)
+
+    step = (lambda: layer(dev_x)) if world > 1 else graphed(lambda: layer(dev_x))[0]
+    ms = timer.run(step, args.steps, args.warmup)
+    layer_bytes = sum(gemv_bytes(n, k, batch) for n, k in LAYER_70B.values())
+
+    per_matrix = {}
+    if world == 1:
+        for name, (n, k) in LAYER_70B.items():
+            r = graphed(lambda name=name: one(name, dev_x[name]))[0]
+            t = timer.run(r, max(10, args.steps // 4), 3)
+            per_matrix[name] = {"us": t * 1e3, "GBps": gemv_bytes(n, k, batch) / (t * 1e-3) / 1e9}
+
+    host_out = {nm: torch.empty(batch, n, dtype=torch.bfloat16).pin_memory() for nm, (n, _) in LAYER_70B.items()}
+
+    def e2e_step():
+        outs = layer({nm: t.to(dev, non_blocking=True) for nm, t in host_x.items()})
+        for nm, y in outs.items():
+            host_out[nm].copy_(y, non_blocking=True)
+
+    e2e_ms = timer.run(e2e_step, args.steps, 3)
+    peaks = measured_peaks()
+    roof = None
+    if per_matrix:
+        ach = per_matrix["gate_up"]["GBps"]
+        roof = {"bound": "hbm", "kernel": "nvfp4_gemv_kernel" if batch == 1 else "nvfp4_gemv_batched_kernel",
+                "launch": f"gate_up 57344x8192 M={batch}", "achieved": ach, "peak": peaks["hbm_gbs"],
+                "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                "traffic": ncu_traffic(f"gemv_gate_up_m{batch}")}
+    return dict(value=layer_bytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=layer_bytes / (e2e_ms * 1e-3) / 1e12,
+                e2e_ms=e2e_ms, h2d=sum(2 * batch * k for _, k in LAYER_70B.values()),
+                d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * (2 if world > 1 else 1),
+                roofline=roof, parity=parity, extra={"per_matrix": per_matrix},
+                dtype="fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
+                config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
+                        "batch": batch, "parallelism": f"column-tp{world}" if world > 1 else "single",
+                        "l2": "flushed between steps; 481 MB of weights per step", "bytes_per_step": layer_bytes})
+
+
+def wl_quant(args, dev, rank, world, timer):
+    import helion_b200 as hb
+    from oracle import oracle as O
+
+    t, h = 16384, 7168
+    g = torch.Generator().manual_seed(2)
+    host_x = torch.randn(t, h, generator=g).to(torch.bfloat16).pin_memory()
+    w = (torch.rand(h, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+    x = host_x.to(dev)
+    q = torch.empty(t, h, dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.empty(t, 1, dtype=torch.float32, device=dev)
+
+    def step():
+        hb.rms_norm_dynamic_per_token_quant(q, x, w, s, 1e-6)
+
+    step()
+    qo, so, _ = O.rms_norm_dynamic_per_token_quant(host_x[:64], w.cpu(), 1e-6)
+    parity = float((q[:64].cpu().view(torch.uint8) != qo.view(torch.uint8)).float().mean())
+    ms = timer.run(graphed(step)[0], args.steps, args.warmup)
+    nbytes = 2 * t * h + 2 * h + t * h + 4 * t
+
+    ops = {}
+    i = 18432
+    xs = torch.randn(t, 2 * i, device=dev, dtype=torch.bfloat16)
+    qs = torch.empty(t, i, dtype=torch.float8_e4m3fn, device=dev)
+    ss = torch.empty(t, i // 128, dtype=torch.float32, device=dev)
+    r = graphed(lambda: hb.silu_and_mul_per_block_quant(qs, xs, ss, 128))[0]
+    tm = timer.run(r, max(10, args.steps // 4), 3)
+    b = 2 * t * 2 * i + t * i + 4 * t * (i // 128)
+    ops["silu_and_mul_per_block_quant_16384x18432"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
+    del xs, qs, ss
+    sg = torch.empty(t, h // 128, dtype=torch.float32, device=dev)
+    r = graphed(lambda: hb.per_token_group_fp8_quant(x, q, sg, 128, 1e-10, -448.0, 448.0, False))[0]
+    tm = timer.run(r, max(10, args.steps // 4), 3)
+    b = 2 * t * h + t * h + 4 * t * (h // 128)
+    ops["per_token_group_fp8_quant_16384x7168"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
+
+    host_q = torch.empty(t, h, dtype=torch.uint8).pin_memory()
+
+    def e2e_step():
+        xd = host_x.to(dev, non_blocking=True)
+        hb.rms_norm_dynamic_per_token_quant(q, xd, w, s, 1e-6)
+        host_q.copy_(q.view(torch.uint8), non_blocking=True)
+
+    e2e_ms = timer.run(e2e_step, max(3, args.steps // 10), 3)
+    peaks = measured_peaks()
+    ach = nbytes / (ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": "rms_norm_token_quant_kernel", "launch": f"{t}x{h}", "achieved": ach,
+            "peak": peaks["hbm_gbs"], "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s",
+            "frac": ach / peaks["hbm_gbs"], "traffic": ncu_traffic("rms_norm_16384x7168")}
+    return dict(value=world * nbytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=world * nbytes / (e2e_ms * 1e-3) / 1e12,
+                e2e_ms=e2e_ms, h2d=host_x.numel() * 2, d2h=host_q.numel(), launches=1, roofline=roof,
+                parity=parity, extra={"ops": ops}, dtype="fp32 arithmetic, bf16 in, e4m3 out",
+                config={"workload": "quant", "op": "rms_norm_dynamic_per_token_quant", "tokens": t, "hidden": h,
+                        "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
+
+
+def wl_moe(args, dev, rank, world, timer):
+    import helion_b200 as hb  # noqa: F401
+    from helion_b200 import dist as D
+    from helion_b200 import moe as M
+
+    c = MOE_CFG
+    e_local = c["experts"] // world
+    t_local = c["tokens"] // world
+
+    def bundle(n, k, seed):
+        codes, scales, g = random_nvfp4(e_local * n, k, dev, seed, 0.02)
+        per = hb.swizzled_scale_numel(n, k // 16)
+        assert scales.numel() == e_local * per
+        return M.GroupedNvfp4Weight(codes.reshape(e_local, n, k // 2), scales.reshape(e_local, per),
+                                    torch.full((e_local,), g, dtype=torch.float32, device=dev))
+
+    w_gu = bundle(2 * c["inter"], c["hidden"], 3000 + rank)
+    w_d = bundle(c["hidden"], c["inter"], 3500 + rank)
+    g = torch.Generator().manual_seed(3 + 97 * rank)
+    host_x = torch.randn(t_local, c["hidden"], generator=g).to(torch.bfloat16).pin_memory()
+    host_l = torch.randn(t_local, c["experts"], generator=g).pin_memory()
+    x, logits = host_x.to(dev), host_l.to(dev)
+
+    if world == 1:
+        def step():
+            return M.nvfp4_moe(x, logits, c["top_k"], w_gu, w_d)
+    else:
+        fn = D.make_nvfp4_expert_fn(w_gu, w_d)
+
+        def step():
+            return D.expert_parallel_moe(x, logits, c["top_k"], c["experts"], fn)
+
+    y = step()
+    parity = float(torch.isfinite(y.float()).all())
+    ms = timer.run(step, args.steps, args.warmup)
+    host_out = torch.empty(t_local, c["hidden"], dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        xd, ld = host_x.to(dev, non_blocking=True), host_l.to(dev, non_blocking=True)
+        if world == 1:
+            out = M.nvfp4_moe(xd, ld, c["top_k"], w_gu, w_d)
+        else:
+            out = D.expert_parallel_moe(xd, ld, c["top_k"], c["experts"], fn)
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_ms = timer.run(e2e_step, max(3, args.steps // 4), 3)
+    flops = moe_flops()
+    peaks = measured_peaks()
+    ach = flops / world / (ms * 1e-3) / 1e12
+    roof = {"bound": "tensor", "kernel": "nvfp4_gemm_kernel (grouped)", "launch": "whole MoE step (2 grouped GEMMs + quantisers + combine)",
+            "achieved": ach, "peak": 4 * peaks["bf16_tflops"], "peak_kind": f"4 x {peaks['kind']} dense bf16 burst",
+            "unit": "TFLOP/s", "frac": ach / (4 * peaks["bf16_tflops"]), "traffic": None}
+    return dict(value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s", ms=ms, e2e_value=flops / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
+                h2d=host_x.numel() * 2 + host_l.numel() * 4, d2h=host_out.numel() * 2, launches=7, roofline=roof,
+                parity=parity, extra={}, dtype="e2m1 x e2m1 with e4m3 block scales, fp32 accumulate, bf16 activations",
+                config={"workload": "moe", **c, "parallelism": f"ep{world}" if world > 1 else "single", "l2": "flushed between steps"})
+
+
+WORKLOADS = {"gemm": wl_gemm, "gemv": wl_gemv, "quant": wl_quant, "moe": wl_moe}
 
 
 def run_gpu(args) -> None:
-    import helion_b200 as hb
     from helion_b200 import _lib
 
     rank = int(os.environ.get("RANK", "0"))
@@ -219,179 +552,52 @@ def run_gpu(args) -> None:
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist = None
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-    _lib.load()
-
-    batch = args.batch
-    mats = build_layer(dev, rank, world)
-    gen = torch.Generator().manual_seed(4)
-    host_x = {name: torch.randn(batch, k, generator=gen).to(torch.bfloat16).pin_memory() for name, (_, k) in LAYER_70B.items()}
-    dev_x = {name: t.to(dev) for name, t in host_x.items()}
-    stream = torch.cuda.current_stream()
-
-    def layer_step(xs):
-        outs = {}
-        for name, (codes, scales, g, n, k) in mats.items():
-            if batch == 1:
-                y = hb.nvfp4_gemv_bf16in(codes, xs[name].reshape(-1), scales, g).reshape(1, -1)
-            else:
-                y = hb.nvfp4_gemv_bf16in_batched(codes, xs[name], scales, g)
-            if world > 1:
-                full = torch.empty(world, batch, n // world, dtype=torch.bfloat16, device=dev)
-                dist.all_gather_into_tensor(full, y)
-                y = full
-            outs[name] = y
-        return outs
-
-    # parity spot check against the oracle on a slice of the O projection (outside the timed region)
-    from oracle import oracle as O
-
-    codes, scales, g, n, k = mats["o"]
-    y = hb.nvfp4_gemv_bf16in(codes[:256], dev_x["o"][0].contiguous(), scales[: 256 * (k // 16)], g)
-    ref = O.nvfp4_gemv_bf16in(codes[:256].cpu(), host_x["o"][0], scales[: 256 * (k // 16)].cpu(), g)
-    err = ((y.float().cpu() - ref.float()).abs() / torch.maximum(ref.float().abs(), ref.float().pow(2).mean().sqrt())).max()
-    parity = {"max_rel_err": float(err), "ok": bool(err <= 1e-2)}
-
-    def sync():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        layer_step(dev_x)
-    sync()
-
-    # ---- device-resident timing (value) + per-matrix launch timing (roofline) ----
-    names = list(LAYER_70B)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
+    lib = _lib.load()
+    timer = Timer(dev, world)
     with ClockSampler(local) as clocks:
-        sync()
-        t_start = torch.cuda.Event(enable_timing=True)
-        t_end = torch.cuda.Event(enable_timing=True)
-        t_start.record(stream)
-        for s in range(args.steps):
-            if world == 1:
-                for i, name in enumerate(names):
-                    codes, scales, g, n, k = mats[name]
-                    ev[s][i].record(stream)
-                    if batch == 1:
-                        hb.nvfp4_gemv_bf16in(codes, dev_x[name].reshape(-1), scales, g)
-                    else:
-                        hb.nvfp4_gemv_bf16in_batched(codes, dev_x[name], scales, g)
-                ev[s][len(names)].record(stream)
-            else:
-                layer_step(dev_x)
-        t_end.record(stream)
-        sync()
-        dev_ms = t_start.elapsed_time(t_end)
-
-        # ---- end to end: pinned host activations in, outputs back to the host, every step ----
-        host_out = {name: torch.empty(world, batch, n // world, dtype=torch.bfloat16).pin_memory() for name, (n, _) in LAYER_70B.items()}
-        for _ in range(min(3, args.warmup)):
-            outs = layer_step({name: t.to(dev, non_blocking=True) for name, t in host_x.items()})
-        sync()
-        e_start = torch.cuda.Event(enable_timing=True)
-        e_end = torch.cuda.Event(enable_timing=True)
-        e_start.record(stream)
-        for _ in range(args.steps):
-            xs = {name: t.to(dev, non_blocking=True) for name, t in host_x.items()}
-            outs = layer_step(xs)
-            for name, y in outs.items():
-                host_out[name].view(-1)[: y.numel()].copy_(y.reshape(-1), non_blocking=True)
-        e_end.record(stream)
-        sync()
-        e2e_ms = e_start.elapsed_time(e_end)
-
-    if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
-
-    layer_bytes = sum(gemv_bytes(n, k, batch) for n, k in LAYER_70B.values())
-    ms_per_step = dev_ms / args.steps
-    value = layer_bytes / (ms_per_step * 1e-3) / 1e12
-    e2e_value = layer_bytes / (e2e_ms / args.steps * 1e-3) / 1e12
-    h2d = sum(2 * batch * k for _, k in LAYER_70B.values())
-    d2h = sum(2 * batch * n for n, _ in LAYER_70B.values())
-
-    hbm_peak, _, peak_kind = measured_peaks()
-    roofline = None
-    per_matrix = {}
-    if world == 1:
-        for i, name in enumerate(names):
-            ms = sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps
-            n, k = LAYER_70B[name]
-            per_matrix[name] = {"us": ms * 1e3, "GBps": gemv_bytes(n, k, batch) / (ms * 1e-3) / 1e9}
-        dom = "gate_up"
-        achieved = per_matrix[dom]["GBps"]
-        roofline = {
-            "bound": "hbm",
-            "kernel": "nvfp4_gemv_kernel" if batch == 1 else "nvfp4_gemv_batched_kernel",
-            "launch": f"{dom} {LAYER_70B[dom][0]}x{LAYER_70B[dom][1]} M={batch}",
-            "achieved": achieved,
-            "peak": hbm_peak,
-            "peak_kind": f"{peak_kind} copy bandwidth",
-            "unit": "GB/s",
-            "frac": achieved / hbm_peak,
-            "traffic": ncu_traffic(f"gemv_{dom}_m{batch}"),
-        }
+        r = WORKLOADS[args.workload](args, dev, rank, world, timer)
+    torch.cuda.synchronize()
+    status = lib.hb200_device_status(0)
 
     if rank == 0:
-        cpu_tbs, cores, sample, _ = cpu_sample_gemv()
+        cpu_v, cpu_unit, cores, sample, _ = time_cpu(args.workload)
         line = {
-            "metric": "nvfp4_gemv_hbm_throughput",
-            "value": value,
-            "unit": "TB/s",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": args.warmup,
-            "ms_per_step": ms_per_step,
-            "higher_is_better": True,
-            "scaling": "strong",
-            "vs_baseline": None,
-            "dtype": "fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
-            "data": "synthetic",
-            "config": {
-                "workload": "gemv_decode_layer",
-                "layer": "70B-class dense: qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672 (cfg 4)",
-                "batch": batch,
-                "parallelism": f"column-tp{world}" if world > 1 else "single",
-                "l2": "inputs larger than L2 (481 MB of weights per step)",
-                "bytes_per_step": layer_bytes,
-            },
-            "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": args.steps * len(names),
-            "roofline": roofline,
-            "per_matrix": per_matrix,
-            "cpu_baseline": {"value": cpu_tbs, "unit": "TB/s", "cores": cores, "kind": "port", "sample": sample},
-            "clocks": clocks.summary(),
-            "parity": parity,
+            "metric": METRICS[args.workload], "value": r["value"], "unit": r["unit"], "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"], "higher_is_better": True,
+            "scaling": "strong" if args.workload != "quant" else "weak", "vs_baseline": None, "dtype": r["dtype"],
+            "data": "synthetic", "config": r["config"],
+            "e2e": {"value": r["e2e_value"], "unit": r["unit"], "h2d_bytes_per_step": r["h2d"],
+                    "d2h_bytes_per_step": r["d2h"], "ms_per_step": r["e2e_ms"]},
+            "gpu_launches": args.steps * r["launches"], "roofline": r["roofline"],
+            "cpu_baseline": {"value": cpu_v, "unit": cpu_unit, "cores": cores, "kind": "port", "sample": sample},
+            "clocks": clocks.summary(), "parity": {"max_rel_err_or_mismatch": r["parity"]}, "device_status": status,
         }
+        line.update(r["extra"])
         print(json.dumps(line))
     if world > 1:
+        import torch.distributed as dist
+
         dist.destroy_process_group()
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemv_decode_layer", choices=["gemv_decode_layer"])
+    ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "ours":
-        args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
-    else:
-        run_gpu(args)
+        return
+    args.warmup = max(3, args.warmup)
+    run_gpu(args)
 
 
 if __name__ == "__main__":

@@ -40,7 +40,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_grouped_matmul": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, c_int, _P],
     "hb200_moe_build_schedule": [_P, _I64, _P, _I64, _P, _P, _I64, _P, _P, _P],
     "hb200_nvfp4_quantize_rows": [_P, _P, _P, _P, _I64, _I64, _I64, _P, c_int, _P, _P, c_int, _P],
-    "hb200_moe_combine": [_P, _I64, _P, _P, _I64, _I64, _I64, _P],
+    "hb200_moe_combine": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p}
 

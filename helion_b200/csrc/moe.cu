@@ -59,10 +59,12 @@ moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, const int32
   }
 }
 
-// out[t, :] = bf16(sum over the token's top_k slots, in slot order, of o[row_of_pair[t*top_k + s], :]) in fp32.
+// out[t, :] = bf16(sum over the token's top_k slots, in slot order, of w * o[row_of_pair[t*top_k + s], :]) in fp32,
+// w = pair_weight[t*top_k + s] or 1.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32_t* __restrict__ row_of_pair,
-                   __nv_bfloat16* __restrict__ out, int64_t tokens, int top_k, int64_t hidden) {
+                   const float* __restrict__ pair_weight, __nv_bfloat16* __restrict__ out, int64_t tokens, int top_k,
+                   int64_t hidden) {
   const int64_t chunks = hidden >> 3;
   const int64_t total = tokens * chunks;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
@@ -70,12 +72,13 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < top_k; ++s) {
       const int64_t row = row_of_pair[t * top_k + s];
+      const float pw = pair_weight ? pair_weight[t * top_k + s] : 1.0f;
       const uint4 v = ldg_stream_u4(o + row * ldo + c * 8);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        acc[2 * e] += __uint_as_float(w[e] << 16);
-        acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        acc[2 * e] = fmaf(pw, __uint_as_float(w[e] << 16), acc[2 * e]);
+        acc[2 * e + 1] = fmaf(pw, __uint_as_float(w[e] & 0xffff0000u), acc[2 * e + 1]);
       }
     }
     uint32_t p[4];
@@ -113,8 +116,9 @@ extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, 
 
 // Routing-weighted combine of the expert outputs (the weights were folded into
 // the rows by the down-projection's epilogue).  No reference counterpart.
-extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair, void* out_bf16,
-                                 int64_t tokens, int64_t top_k, int64_t hidden, void* stream) {
+extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair,
+                                 const float* pair_weight, void* out_bf16, int64_t tokens, int64_t top_k,
+                                 int64_t hidden, void* stream) {
   using namespace hb200;
   if (!expert_out_bf16 || !row_of_pair || !out_bf16) return HB200_ERR_INVALID_ARGUMENT;
   if (tokens < 0 || top_k <= 0 || hidden < 0 || (hidden % 8) != 0 || ld < hidden || (ld % 8) != 0)
@@ -128,7 +132,7 @@ extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const 
   const int64_t need = ceil_div64(items, 256);
   const int grid = int(need < int64_t(sms) * 8 ? need : int64_t(sms) * 8);
   moe_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(expert_out_bf16), ld, row_of_pair, static_cast<__nv_bfloat16*>(out_bf16),
-      tokens, int(top_k), hidden);
+      static_cast<const __nv_bfloat16*>(expert_out_bf16), ld, row_of_pair, pair_weight,
+      static_cast<__nv_bfloat16*>(out_bf16), tokens, int(top_k), hidden);
   return launch_status();
 }

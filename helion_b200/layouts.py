@@ -142,8 +142,12 @@ def unpack_fp4(packed: Tensor) -> Tensor:
 
 # ------------------------------------------------------------ NVFP4 quantiser
 def nvfp4_global_scale(x: Tensor) -> Tensor:
-    """Per-tensor fp32 global scale ``amax / (6 * 448)`` (0-dim tensor)."""
-    return x.abs().amax().to(torch.float32) / (FP4_MAX * E4M3_MAX)
+    """Per-tensor fp32 global scale ``amax / (6 * 448)`` (0-dim tensor).
+
+    The divisor is a tensor on purpose: dividing a CUDA tensor by a Python scalar multiplies by the
+    rounded reciprocal, which can differ from the true quotient in the last place."""
+    amax = x.abs().amax().to(torch.float32)
+    return amax / torch.tensor(FP4_MAX * E4M3_MAX, dtype=torch.float32, device=amax.device)
 
 
 def nvfp4_quantize_host(x: Tensor, global_scale: Tensor | None = None, per_token: bool = False):
@@ -160,7 +164,7 @@ def nvfp4_quantize_host(x: Tensor, global_scale: Tensor | None = None, per_token
     xf = x.to(torch.float32)
     if global_scale is None:
         if per_token:
-            global_scale = xf.abs().amax(dim=-1) / (FP4_MAX * E4M3_MAX)
+            global_scale = xf.abs().amax(dim=-1) / torch.tensor(FP4_MAX * E4M3_MAX, dtype=torch.float32, device=xf.device)
         else:
             global_scale = nvfp4_global_scale(xf)
     g = global_scale.to(torch.float32).reshape(-1, 1, 1) if per_token else global_scale.to(torch.float32)

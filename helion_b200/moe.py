@@ -23,6 +23,7 @@ from torch import Tensor
 
 from . import _lib
 from .layouts import ceil_div
+from .layouts import nvfp4_global_scale
 from .layouts import swizzled_scale_numel
 from .ops import _require_cuda
 from .ops import _stream
@@ -62,7 +63,7 @@ def quantize_expert_weights(w: Tensor) -> GroupedNvfp4Weight:
     gs = torch.empty(e, dtype=torch.float32, device=w.device)
     for i in range(e):
         wb = w[i].to(torch.bfloat16)  # the quantiser consumes bf16; the global scale must see the same values
-        g = (wb.abs().amax().to(torch.float32) / (6.0 * 448.0)).reshape(1)
+        g = nvfp4_global_scale(wb).reshape(1)
         c, s, _ = nvfp4_quantize(wb, g)
         packed[i], scales[i], gs[i] = c, s.view(torch.uint8), g[0]
     return GroupedNvfp4Weight(packed, scales.view(torch.float8_e4m3fn), gs)
@@ -91,7 +92,9 @@ def build_schedule(experts_per_token: Tensor, num_experts: int) -> MoeSchedule:
     flat = experts_per_token.reshape(-1)
     pairs = flat.numel()
     sorted_pairs = torch.argsort(flat, stable=True).to(torch.int32)
-    counts = torch.bincount(flat, minlength=num_experts).to(torch.int32)
+    # (torch.bincount would read the maximum back to the host)
+    counts = torch.zeros(num_experts, dtype=torch.int32, device=flat.device)
+    counts.index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
     max_tiles = ceil_div(pairs, 128) + num_experts  # bound that does not depend on the routing
     dev = flat.device
     tile_info = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
@@ -163,6 +166,6 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
     o = grouped_matmul(a2, sf2, w_down, sched, g2)
     out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(), out.data_ptr(),
-                  t, top_k, h, _stream())
+        _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(), None,
+                  out.data_ptr(), t, top_k, h, _stream())
     return out

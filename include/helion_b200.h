@@ -160,10 +160,12 @@ int hb200_nvfp4_quantize_rows(const void* x_bf16, void* codes, void* scales_swiz
                               int64_t items, int64_t k, int64_t ldx, const int32_t* src_idx, int src_div,
                               const int32_t* dst_idx, const float* item_scale, int silu_mul, void* stream);
 
-/* out[t, :] = bf16(sum_s expert_out[row_of_pair[t * top_k + s], :]) in fp32, slot
- * order.  No reference counterpart (the reference has no top-k combine). */
-int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair, void* out_bf16,
-                      int64_t tokens, int64_t top_k, int64_t hidden, void* stream);
+/* out[t, :] = bf16(sum_s w[t, s] * expert_out[row_of_pair[t * top_k + s], :]) in
+ * fp32, slot order; w = pair_weight (fp32 [tokens * top_k]) or 1 when null.  No
+ * reference counterpart (the reference has no top-k combine). */
+int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* row_of_pair,
+                      const float* pair_weight, void* out_bf16, int64_t tokens, int64_t top_k, int64_t hidden,
+                      void* stream);
 
 /* Sticky device-side status: HB200_OK, or HB200_ERR_DEVICE_TIMEOUT once a
  * kernel gave up a bounded wait (its outputs are then undefined).  reset != 0
