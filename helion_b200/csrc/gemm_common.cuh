@@ -1,0 +1,139 @@
+// Pieces shared by the block-scaled GEMM kernels: tile constants, the epilogue's
+// row-chunk stores and the host-side TMA descriptor construction.
+#pragma once
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#include <mutex>
+
+namespace hb200 {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;   // one swizzle row: 256 e2m1 values
+constexpr int kAtomBytes = 512;     // one 128-row x 4-scale atom (64 K-elements)
+constexpr int kAtomsPerStage = 4;
+
+// 32 consecutive fp32 accumulator columns of one row -> scaled, converted, stored (vectorised when whole and aligned).
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const uint32_t (&r)[32], float alpha, int valid, bool vec_ok);
+
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], float alpha,
+                                                               int valid, bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
+                                                       __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha);
+        p[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const uint32_t (&r)[32], float alpha, int valid,
+                                                        bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        p[j] = h2_as_u32(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
+                                           __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha));
+      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __float2half_rn(__uint_as_float(r[j]) * alpha);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* dst, const uint32_t (&r)[32], float alpha, int valid,
+                                                       bool vec_ok) {
+  if (valid >= 32 && vec_ok) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      *reinterpret_cast<float4*>(dst + v * 4) =
+          make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha,
+                      __uint_as_float(r[v * 4 + 2]) * alpha, __uint_as_float(r[v * 4 + 3]) * alpha);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = __uint_as_float(r[j]) * alpha;
+  }
+}
+
+
+// ----------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Packed e2m1 matrix [rows, k/2 bytes] as a byte tensor; box = 128 bytes x box_rows, 128-byte swizzle.
+inline bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(k_bytes), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(k_bytes)};
+  const cuuint32_t box[2] = {cuuint32_t(kBlockKBytes), cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+
+// Swizzled scale buffer as a [atoms, 128 x u32] tensor: one row per 512-byte atom; box = 4 atoms.
+inline bool make_scale_map(CUtensorMap* map, const void* base, int64_t atoms) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {128, cuuint64_t(atoms)};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, cuuint32_t(kAtomsPerStage)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Row-major 2-byte output [rows, cols] (leading dimension ldc elements) for the epilogue's TMA stores:
+// box = 64 columns (128 bytes) x 32 rows, 128-byte swizzle.
+inline bool make_output_map16(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldc, bool is_bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(ldc) * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
+            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace hb200

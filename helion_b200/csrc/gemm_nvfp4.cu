@@ -16,7 +16,9 @@
 // error status instead of hanging.  No cluster multicast is used anywhere.
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "gemm_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -24,14 +26,16 @@ namespace hb200 {
 
 __device__ int g_device_status = 0;
 
+}  // namespace hb200
+
+#include "gemm_nvfp4_2cta.cuh"
+
+namespace hb200 {
+
 namespace {
 
 using namespace sm100;
 
-constexpr int kBlockM = 128;
-constexpr int kBlockKBytes = 128;   // one swizzle row: 256 e2m1 values
-constexpr int kAtomBytes = 512;     // one 128-row x 4-scale atom (64 K-elements)
-constexpr int kAtomsPerStage = 4;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 
@@ -96,67 +100,6 @@ struct StageLayout {
   template <int STAGES>
   static constexpr int acc_stages() { return (2 * BLOCK_N + STAGES * kSfCols <= kTmemCols) ? 2 : 1; }
 };
-
-template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst, const uint32_t (&r)[32], float alpha, int valid, bool vec_ok);
-
-template <>
-__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], float alpha,
-                                                               int valid, bool vec_ok) {
-  if (valid >= 32 && vec_ok) {
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      uint32_t p[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
-                                                       __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha);
-        p[j] = *reinterpret_cast<const uint32_t*>(&h);
-      }
-      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < valid) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
-  }
-}
-
-template <>
-__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const uint32_t (&r)[32], float alpha, int valid,
-                                                        bool vec_ok) {
-  if (valid >= 32 && vec_ok) {
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      uint32_t p[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        p[j] = h2_as_u32(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]) * alpha,
-                                           __uint_as_float(r[v * 8 + 2 * j + 1]) * alpha));
-      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(p[0], p[1], p[2], p[3]);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < valid) dst[j] = __float2half_rn(__uint_as_float(r[j]) * alpha);
-  }
-}
-
-template <>
-__device__ __forceinline__ void store_row_chunk<float>(float* dst, const uint32_t (&r)[32], float alpha, int valid,
-                                                       bool vec_ok) {
-  if (valid >= 32 && vec_ok) {
-#pragma unroll
-    for (int v = 0; v < 8; ++v)
-      *reinterpret_cast<float4*>(dst + v * 4) =
-          make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha,
-                      __uint_as_float(r[v * 4 + 2]) * alpha, __uint_as_float(r[v * 4 + 3]) * alpha);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < valid) dst[j] = __uint_as_float(r[j]) * alpha;
-  }
-}
 
 template <int BLOCK_N, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -388,36 +331,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 }
 
 // ----------------------------------------------------------------- host side
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// Packed e2m1 matrix [rows, k/2 bytes] as a byte tensor; box = 128 bytes x box_rows, 128-byte swizzle.
-bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k_bytes, int box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {cuuint64_t(k_bytes), cuuint64_t(rows)};
-  const cuuint64_t strides[1] = {cuuint64_t(k_bytes)};
-  const cuuint32_t box[2] = {cuuint32_t(kBlockKBytes), cuuint32_t(box_rows)};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 int sm_count_gemm() {
   int dev = 0, n = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -471,6 +384,11 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
   if (k == 0) {
     return cudaMemset2DAsync(out, size_t(ldc) * elt, 0, size_t(n) * elt, size_t(m), s) == cudaSuccess ? HB200_OK
                                                                                                       : HB200_ERR_CUDA;
+  }
+  static const bool no_pair = getenv("HB200_GEMM_NO_PAIR") != nullptr;
+  if (!no_pair) {
+    const int rc = pair::launch_gemm_pair(a_packed, b_packed, scale_a, scale_b, out, m, n, k, ldc, alpha, out_dtype, s);
+    if (rc != HB200_ERR_UNSUPPORTED) return rc;
   }
   GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
              int(m), int(n), int(k), alpha, 0, 0, nullptr, 0, nullptr, nullptr};

@@ -1,0 +1,317 @@
+// Dense block-scaled NVFP4 GEMM on CTA pairs (tcgen05 cta_group::2).  Included by gemm_nvfp4.cu
+// (one translation unit, so both kernels share the sticky device status word).
+//
+// Two CTAs on neighbouring SMs own one 256 x 256 output tile: CTA r of the pair
+// holds rows [128r, 128r+128) of the A tile and rows [128r, 128r+128) of the B
+// tile (its half of the output columns' operand) in its own shared memory, and
+// the leader (r = 0) issues 256 x 256 x 64 MMAs that read both halves.  Per
+// k-block each SM then pulls 16 KB of A, 16 KB of B and 6 KB of scales from L2
+// instead of 16 + 32 + 6, which is what bounds the single-CTA kernel.  No load
+// is multicast: each CTA loads what it holds.
+//
+// Hand-over: both CTAs' TMA loads credit the leader's "full" barrier (the leader
+// arms it for the bytes of both); the leader's tcgen05.commit releases the stage
+// in both CTAs and publishes the accumulator to both epilogues; epilogue warps of
+// both CTAs arrive on the leader's "accumulator free" barrier.  Every wait is
+// bounded; the kernel ends with a hardware cluster barrier so neither CTA exits
+// while its peer may still touch its shared memory or barriers.
+#pragma once
+
+#include "gemm_common.cuh"
+
+#include <cstdlib>
+#include <type_traits>
+
+namespace hb200 {
+namespace pair {
+
+using namespace sm100;
+
+constexpr int kThreads2 = 384;  // producer, MMA issuer, scale copier, one idle warp, eight epilogue warps
+constexpr int kTileN = 256;
+constexpr int kStages2 = 5;
+constexpr int kABytes2 = kBlockM * kBlockKBytes;          // 16 KB: this CTA's 128 rows of A
+constexpr int kBBytes2 = 128 * kBlockKBytes;              // 16 KB: this CTA's half of B
+constexpr int kSfaBytes2 = kAtomsPerStage * kAtomBytes;   // 2 KB
+constexpr int kSfbBytes2 = 2 * kAtomsPerStage * kAtomBytes;  // 4 KB: scales of all 256 B rows
+constexpr int kBOff2 = kABytes2;
+constexpr int kSfaOff2 = kBOff2 + kBBytes2;
+constexpr int kSfbOff2 = kSfaOff2 + kSfaBytes2;
+constexpr int kStageBytes2 = kSfbOff2 + kSfbBytes2;       // 38912, a multiple of 1024
+constexpr int kOutStageBytes = 8 * 4096;                  // one 32-row x 128-byte box per epilogue warp
+constexpr int kSfCols2 = kAtomsPerStage * 4 * 3;          // 48 scale columns per stage
+constexpr int kSfBase2 = kTileN;                          // after the 256 accumulator columns
+static_assert(kStageBytes2 % 1024 == 0, "stage must keep 1024-byte alignment");
+static_assert(kSfBase2 + kStages2 * kSfCols2 <= 512, "tensor memory budget exceeded");
+
+struct PairArgs {
+  void* out;
+  int64_t ldc;
+  int m, n, k;
+  float alpha;
+  int m_tiles, n_tiles;  // 256 x 256 tiles
+  int debug;
+};
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                       const __grid_constant__ CUtensorMap tmap_out, const PairArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_out = smem + kStages2 * kStageBytes2;  // 8 warps x 4 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + kOutStageBytes);
+  uint64_t* full_bar = bars;                 // used in the leader only
+  uint64_t* empty_bar = bars + kStages2;     // one set per CTA
+  uint64_t* sf_full_bar = bars + 2 * kStages2;   // scales of a stage are in tensor memory (leader only)
+  uint64_t* tmem_full_bar = bars + 3 * kStages2;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 1;  // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int col_tiles = (g.k / 16 + 3) / 4;
+  const int num_kb = (col_tiles + kAtomsPerStage - 1) / kAtomsPerStage;
+  const int num_tiles = g.m_tiles * g.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);   // the leader's producer arms it; bytes come from both CTAs
+      mbar_init(smem_u32(&empty_bar[s]), 1);  // the leader's commit, multicast to both CTAs
+      mbar_init(smem_u32(&sf_full_bar[s]), 1);
+    }
+    mbar_init(smem_u32(tmem_full_bar), 1);
+    mbar_init(smem_u32(tmem_empty_bar), 16);  // eight epilogue warps in each CTA
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anything remote happens
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    uint32_t it = 0;
+    bool ok = true;
+    const uint32_t stage_bytes = kABytes2 + kBBytes2 + kSfaBytes2 + kSfbBytes2;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+      const int a_row = m_blk * 256 + int(rank) * 128;
+      const int b_row = n_blk * kTileN + int(rank) * 128;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kStages2;
+        const uint32_t ph = (it / kStages2) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag)) { ok = false; break; }
+        uint8_t* st = smem + s * kStageBytes2;
+        const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);  // always the leader's barrier
+        if (elect_one()) {
+          if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * stage_bytes);
+          tma_load_2d_pair(smem_u32(st), &tmap_a, kb * kBlockKBytes, a_row, bar);
+          tma_load_2d_pair(smem_u32(st + kBOff2), &tmap_b, kb * kBlockKBytes, b_row, bar);
+          // scale atoms: row = atom index = row_tile * col_tiles + column tile
+          tma_load_2d_pair(smem_u32(st + kSfaOff2), &tmap_sfa, 0, (a_row / 128) * col_tiles + kb * kAtomsPerStage, bar);
+          tma_load_2d_pair(smem_u32(st + kSfbOff2), &tmap_sfb, 0, (n_blk * 2) * col_tiles + kb * kAtomsPerStage, bar);
+          tma_load_2d_pair(smem_u32(st + kSfbOff2 + kSfaBytes2), &tmap_sfb, 0,
+                           (n_blk * 2 + 1) * col_tiles + kb * kAtomsPerStage, bar);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader only)
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_mxf4nvf4(256, kTileN);
+      bool ok = true;
+      uint32_t it = 0, tc = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
+        if (!mbar_wait(smem_u32(tmem_empty_bar), (tc & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(smem_u32(&sf_full_bar[s]), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          uint8_t* st = smem + s * kStageBytes2;
+          const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + kBOff2);
+          const uint32_t sf_col = tmem_base + kSfBase2 + s * kSfCols2;
+          if (elect_one()) {
+            if (!(g.debug & 4))
+            for (int a = 0; a < atoms; ++a) {
+              const uint64_t adesc = make_smem_desc(a_addr + a * 32, 16, 1024, kSwizzle128B);
+              const uint64_t bdesc = make_smem_desc(b_addr + a * 32, 16, 1024, kSwizzle128B);
+              mma_mxf4nvf4_pair(tmem_base, adesc, bdesc, idesc, (kb | a) != 0 ? 1u : 0u, sf_col + a * 4,
+                                sf_col + 16 + a * 8);
+            }
+            tcgen05_commit_pair(smem_u32(&empty_bar[s]), 3);  // stage free in both CTAs
+          }
+          __syncwarp();
+        }
+        if (ok && elect_one()) tcgen05_commit_pair(smem_u32(tmem_full_bar), 3);
+        __syncwarp();
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------------------------------------------------- scale copier (leader only)
+    // A separate issue stream: the copies of stage s+1 run beside the MMAs of stage s instead of
+    // queueing in front of them.  Every stage has its own scale columns in tensor memory.
+    if (leader) {
+      bool ok = true;
+      uint32_t it = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages2;
+          const uint32_t ph = (it / kStages2) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          uint8_t* st = smem + s * kStageBytes2;
+          const uint32_t sfa_addr = smem_u32(st + kSfaOff2), sfb_addr = smem_u32(st + kSfbOff2);
+          const uint32_t sf_col = tmem_base + kSfBase2 + s * kSfCols2;
+          if (elect_one()) {
+            if (!(g.debug & 2) || kb == 0)
+            for (int a = 0; a < atoms; ++a) {
+              tcgen05_cp_32x128b_warpx4_pair(sf_col + a * 4, make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
+              tcgen05_cp_32x128b_warpx4_pair(sf_col + 16 + a * 8,
+                                             make_smem_desc(sfb_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
+              tcgen05_cp_32x128b_warpx4_pair(sf_col + 16 + a * 8 + 4,
+                                             make_smem_desc(sfb_addr + kSfaBytes2 + a * kAtomBytes, 0, 128, kSwizzleNone));
+            }
+            tcgen05_commit_pair_local(smem_u32(&sf_full_bar[s]));
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // idle: keeps the epilogue warps' lane-quarter mapping (warp % 4) aligned
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    // Eight warps: warp w reads lane quarter w % 4 (the only one it may) and column half (w - 2) / 4.
+    // Two 32-column loads are in flight per wait, so a thread stores one full 128-byte line per pass.
+    const int quarter = warp & 3, half = (warp - 4) >> 2;
+    OutT* out = static_cast<OutT*>(g.out);
+    const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
+    const uint32_t free_bar = map_to_cta(smem_u32(tmem_empty_bar), 0);
+    uint32_t tc = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
+      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+      if (!mbar_wait(smem_u32(tmem_full_bar), tc & 1, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m_blk * 256 + int(rank) * 128 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + half * 128;
+      uint8_t* my_out = stage_out + (warp - 4) * 4096;
+#pragma unroll 1
+      for (int c = 0; c < ((g.debug & 1) ? 0 : 2); ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(taddr + c * 64, r0);
+        tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+        tmem_ld_wait();
+        const int col = n_blk * kTileN + half * 128 + c * 64;
+        if constexpr (sizeof(OutT) == 2) {
+          // 64 columns -> 128 bytes per row, staged in this warp's swizzled box and stored by TMA
+          if (lane == 0) bulk_wait_group_read0();  // the previous box has left shared memory
+          __syncwarp();
+          uint8_t* rowp = my_out + lane * 128;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint32_t* src = v < 4 ? &r0[v * 8] : &r1[(v - 4) * 8];
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lo = __uint_as_float(src[2 * j]) * g.alpha, hi = __uint_as_float(src[2 * j + 1]) * g.alpha;
+              if constexpr (std::is_same<OutT, __half>::value) {
+                p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
+              } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                p[j] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+            }
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, col, m_blk * 256 + int(rank) * 128 + quarter * 32, smem_u32(my_out));
+            bulk_commit_group();
+          }
+        } else {
+          if (row < g.m && col < g.n)
+            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r0, g.alpha, g.n - col, vec_ok);
+          if (row < g.m && col + 32 < g.n)
+            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r1, g.alpha, g.n - col - 32, vec_ok);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(free_bar);
+    }
+    if (lane == 0) bulk_wait_group_read0();
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer is done with this CTA's shared memory, barriers and tensor memory
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicMin(&g_device_status, HB200_ERR_DEVICE_TIMEOUT);
+}
+
+// Dense GEMM on CTA pairs; returns HB200_ERR_UNSUPPORTED for shapes it does not take
+// (the caller then uses the single-CTA kernel).
+inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const void* sfb, void* out, int64_t m, int64_t n,
+                     int64_t k, int64_t ldc, float alpha, int out_dtype, cudaStream_t stream) {
+  if (m < 256 || n < 256 || (k % 32) != 0) return HB200_ERR_UNSUPPORTED;
+  CUtensorMap ta, tb, tsa, tsb;
+  const int64_t col_tiles = (k / 16 + 3) / 4;
+  if (!make_operand_map(&ta, a, m, k / 2, 128) || !make_operand_map(&tb, b, n, k / 2, 128)) return HB200_ERR_CUDA;
+  if (!make_scale_map(&tsa, sfa, ceil_div64(m, 128) * col_tiles) ||
+      !make_scale_map(&tsb, sfb, ceil_div64(n, 128) * col_tiles))
+    return HB200_ERR_CUDA;
+  CUtensorMap tout;
+  if (out_dtype != 2) {
+    if ((ldc % 8) != 0 || reinterpret_cast<uintptr_t>(out) % 16) return HB200_ERR_UNSUPPORTED;
+    if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
+  } else {
+    tout = ta;  // unused by the fp32 epilogue
+  }
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), getenv("HB200_GEMM_DEBUG") ? atoi(getenv("HB200_GEMM_DEBUG")) : 0};
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = g.m_tiles * g.n_tiles;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  constexpr size_t smem = size_t(kStages2) * kStageBytes2 + kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+#define HB200_PAIR(T)                                                                                         \
+  do {                                                                                                        \
+    auto kernel = nvfp4_gemm_pair_kernel<T>;                                                                  \
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)  \
+      return HB200_ERR_CUDA;                                                                                  \
+    kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);                                      \
+  } while (0)
+  if (out_dtype == 0) HB200_PAIR(__nv_bfloat16);
+  else if (out_dtype == 1) HB200_PAIR(__half);
+  else HB200_PAIR(float);
+#undef HB200_PAIR
+  return launch_status();
+}
+
+}  // namespace pair
+}  // namespace hb200
