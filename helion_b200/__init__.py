@@ -8,6 +8,11 @@ library ``libhelion_b200.so`` declared in ``include/helion_b200.h``.
 """
 
 from . import layouts
+from .grouped import grouped_gemm_deepgemm
+from .grouped import grouped_gemm_jagged
+from .grouped import grouped_gemm_jagged_persistent
+from .grouped import moe_matmul_ogs
+from .grouped import moe_matmul_ogs_helion_kernel_args_gen
 from .layouts import swizzle_fp8_scales
 from .layouts import swizzled_scale_numel
 from .layouts import swizzled_scale_offsets
@@ -17,17 +22,26 @@ from .ops import nvfp4_gemv_bf16in_batched
 from .ops import nvfp4_gemv_fp4in
 from .ops import nvfp4_quantize
 from .ops import nvfp4_scaled_matmul
+from .ops import nvfp4_w4a4_matmul
+from .ops import nvfp4_w4a16_matmul
 from .ops import per_token_group_fp8_quant
 from .ops import rms_norm_dynamic_per_token_quant
 from .ops import silu_and_mul_per_block_quant
 
 __all__ = [
+    "grouped_gemm_deepgemm",
+    "grouped_gemm_jagged",
+    "grouped_gemm_jagged_persistent",
+    "moe_matmul_ogs",
+    "moe_matmul_ogs_helion_kernel_args_gen",
     "layouts",
     "nvfp4_gemv_bf16in",
     "nvfp4_gemv_bf16in_batched",
     "nvfp4_gemv_fp4in",
     "nvfp4_quantize",
     "nvfp4_scaled_matmul",
+    "nvfp4_w4a4_matmul",
+    "nvfp4_w4a16_matmul",
     "per_token_group_fp8_quant",
     "rms_norm_dynamic_per_token_quant",
     "silu_and_mul_per_block_quant",

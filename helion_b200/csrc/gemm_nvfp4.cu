@@ -2,15 +2,17 @@
 // with both operands packed e2m1 (K-major) and one e4m3 scale per 16 K-elements
 // in the SWIZZLE_32_4_4 layout.
 //
-// One persistent CTA per SM, six warps with fixed roles:
+// One persistent CTA per SM, warps with fixed roles:
 //   warp 0   producer : TMA loads of the A and B tiles (128-byte swizzled rows of
 //                       256 K-elements) and plain bulk copies of the scale tiles
 //                       (the swizzled global layout is already the 128x4 atom the
 //                       tensor core wants, 512 contiguous bytes per 64 K-elements)
-//   warp 1   MMA      : tcgen05.cp moves the scale atoms to tensor memory, then
-//                       tcgen05.mma.kind::mxf4nvf4.block_scale accumulates
+//   warp 1   MMA      : tcgen05.mma.kind::mxf4nvf4.block_scale accumulates
 //                       128 x BLOCK_N x 64 per instruction into tensor memory
-//   warps 2-5 epilogue: tcgen05.ld of the fp32 accumulator, * alpha, convert, store
+//   warp 2   copier   : tcgen05.cp moves the scale atoms of a stage to that stage's own
+//                       tensor-memory columns, as a separate issue stream so the copies
+//                       run beside the MMAs of earlier stages
+//   warps 4-7 epilogue: tcgen05.ld of the fp32 accumulator, * alpha, convert, store
 // Stages of the shared-memory ring and of the accumulator ring are handed over
 // with mbarriers; every wait is bounded and a timeout ends the kernel with an
 // error status instead of hanging.  No cluster multicast is used anywhere.
@@ -36,7 +38,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 256;  // producer, MMA issuer, scale copier, idle, four epilogue warps
 constexpr int kTmemCols = 512;
 
 struct GemmArgs {
@@ -115,7 +117,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::kBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
-  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* sf_full_bar = bars + 2 * STAGES;  // a stage's scales have reached tensor memory
+  uint64_t* tmem_full_bar = bars + 3 * STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -130,6 +133,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&sf_full_bar[s]), 1);
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
@@ -195,44 +199,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    // The scale atoms of a stage are copied into that stage's own tensor-memory
-    // columns one k-block ahead of the MMAs that use them, so the copies overlap
-    // the previous k-block's MMAs instead of draining the tensor pipe.  The whole
-    // warp walks the schedule and waits; one elected lane issues.
+    // The whole warp walks the schedule and waits; one elected lane issues.
     {
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(kBlockM, BLOCK_N);
-      int my_tiles = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) my_tiles += decode_tile(g, tile).valid ? 1 : 0;
-      const uint32_t total = uint32_t(my_tiles) * uint32_t(num_kb);
-      bool ok = true;
-
-      auto copy_scales = [&](uint32_t it) -> bool {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) return false;
-        tcgen05_fence_after();
-        const int kb = int(it % uint32_t(num_kb));
-        const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
-        uint8_t* st = smem + s * L::kBytes;
-        const uint32_t sfa_addr = smem_u32(st + L::kSfaOff), sfb_addr = smem_u32(st + L::kSfbOff);
-        const uint32_t sf_col = tmem_base + kSfBase + s * L::kSfCols;
-        if (elect_one()) {
-            for (int a = 0; a < atoms; ++a) {
-            tcgen05_cp_32x128b_warpx4(sf_col + L::kSfaColOff + a * 4,
-                                      make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
-#pragma unroll
-            for (int nb = 0; nb < L::kNB; ++nb)
-              tcgen05_cp_32x128b_warpx4(
-                  sf_col + L::kSfbColOff + (a * L::kNB + nb) * 4,
-                  make_smem_desc(sfb_addr + (nb * kAtomsPerStage + a) * kAtomBytes, 0, 128, kSwizzleNone));
-          }
-        }
-        __syncwarp();
-        return true;
-      };
-
-      if (total > 0) ok = copy_scales(0);
       uint32_t it = 0, tc = 0;
+      bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!decode_tile(g, tile).valid) continue;
         const int acc = tc % ACC;
@@ -242,8 +213,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          if (it + 1 < total && !copy_scales(it + 1)) { ok = false; break; }
           const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&sf_full_bar[s]), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
           const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
           uint8_t* st = smem + s * L::kBytes;
           const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + L::kBOff);
@@ -264,6 +237,42 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         __syncwarp();
       }
     }
+  } else if (warp == 2) {
+    // -------------------------------------------------------- scale copier
+    // Its own issue stream: the scale atoms of a stage go to that stage's tensor-memory columns while
+    // the MMAs of earlier stages run, instead of queueing in front of them.
+    {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!decode_tile(g, tile).valid) continue;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
+          uint8_t* st = smem + s * L::kBytes;
+          const uint32_t sfa_addr = smem_u32(st + L::kSfaOff), sfb_addr = smem_u32(st + L::kSfbOff);
+          const uint32_t sf_col = tmem_base + kSfBase + s * L::kSfCols;
+          if (elect_one()) {
+            for (int a = 0; a < atoms; ++a) {
+              tcgen05_cp_32x128b_warpx4(sf_col + L::kSfaColOff + a * 4,
+                                        make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
+#pragma unroll
+              for (int nb = 0; nb < L::kNB; ++nb)
+                tcgen05_cp_32x128b_warpx4(
+                    sf_col + L::kSfbColOff + (a * L::kNB + nb) * 4,
+                    make_smem_desc(sfb_addr + (nb * kAtomsPerStage + a) * kAtomBytes, 0, 128, kSwizzleNone));
+            }
+            tcgen05_commit(smem_u32(&sf_full_bar[s]));
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // idle: keeps the epilogue warps' lane-quarter mapping (warp % 4) aligned with warps 4..7
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // the tensor-memory lane quarter this warp may read
@@ -340,7 +349,7 @@ int sm_count_gemm() {
 template <int BLOCK_N, int STAGES, typename OutT>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream) {
   using L = StageLayout<BLOCK_N>;
-  constexpr size_t smem = size_t(STAGES) * L::kBytes + (2 * STAGES + 4) * 8 + 16 + 1024;
+  constexpr size_t smem = size_t(STAGES) * L::kBytes + (3 * STAGES + 4) * 8 + 16 + 1024;
   static_assert(smem <= 232448, "shared memory budget exceeded");
   auto kernel = nvfp4_gemm_kernel<BLOCK_N, STAGES, OutT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
@@ -430,6 +439,10 @@ extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_pa
 
 // Reads (and optionally clears) the sticky device status set by kernels whose
 // bounded waits ran out.  Synchronises the device.
+namespace hb200 {
+int f16_device_status(int reset);
+}
+
 extern "C" int hb200_device_status(int reset) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, hb200::g_device_status, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
@@ -437,5 +450,6 @@ extern "C" int hb200_device_status(int reset) {
     const int zero = 0;
     if (cudaMemcpyToSymbol(hb200::g_device_status, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
   }
-  return v;
+  const int w = hb200::f16_device_status(reset);
+  return v != 0 ? v : w;
 }

@@ -27,7 +27,7 @@ namespace pair {
 
 using namespace sm100;
 
-constexpr int kThreads2 = 384;  // producer, MMA issuer, scale copier, one idle warp, eight epilogue warps
+constexpr int kThreads2 = 640;  // producer, MMA issuer, scale copier, one idle warp, sixteen epilogue warps
 constexpr int kTileN = 256;
 constexpr int kStages2 = 5;
 constexpr int kABytes2 = kBlockM * kBlockKBytes;          // 16 KB: this CTA's 128 rows of A
@@ -38,7 +38,7 @@ constexpr int kBOff2 = kABytes2;
 constexpr int kSfaOff2 = kBOff2 + kBBytes2;
 constexpr int kSfbOff2 = kSfaOff2 + kSfaBytes2;
 constexpr int kStageBytes2 = kSfbOff2 + kSfbBytes2;       // 38912, a multiple of 1024
-constexpr int kOutStageBytes = 8 * 4096;                  // one 32-row x 128-byte box per epilogue warp
+constexpr int kOutStageBytes = 16 * 2048;                 // one 32-row x 64-byte box per epilogue warp
 constexpr int kSfCols2 = kAtomsPerStage * 4 * 3;          // 48 scale columns per stage
 constexpr int kSfBase2 = kTileN;                          // after the 256 accumulator columns
 static_assert(kStageBytes2 % 1024 == 0, "stage must keep 1024-byte alignment");
@@ -85,7 +85,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       mbar_init(smem_u32(&sf_full_bar[s]), 1);
     }
     mbar_init(smem_u32(tmem_full_bar), 1);
-    mbar_init(smem_u32(tmem_empty_bar), 16);  // eight epilogue warps in each CTA
+    mbar_init(smem_u32(tmem_empty_bar), 32);  // sixteen epilogue warps in each CTA
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -201,65 +201,71 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     // idle: keeps the epilogue warps' lane-quarter mapping (warp % 4) aligned
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
-    // Eight warps: warp w reads lane quarter w % 4 (the only one it may) and column half (w - 2) / 4.
-    // Two 32-column loads are in flight per wait, so a thread stores one full 128-byte line per pass.
-    const int quarter = warp & 3, half = (warp - 4) >> 2;
+    // Sixteen warps: warp w reads lane quarter w % 4 (the only one it may) and the 64 columns
+    // [(w - 4) / 4 * 64, +64).  Each warp pulls its whole share into registers with two loads and hands the
+    // accumulator back at once; conversion and the TMA stores happen off the MMA's critical path.
+    const int quarter = warp & 3, cgroup = (warp - 4) >> 2;
     OutT* out = static_cast<OutT*>(g.out);
     const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
     const uint32_t free_bar = map_to_cta(smem_u32(tmem_empty_bar), 0);
+    uint8_t* box = stage_out + (warp - 4) * 2048;
     uint32_t tc = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
       const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
       if (!mbar_wait(smem_u32(tmem_full_bar), tc & 1, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
-      const int row = m_blk * 256 + int(rank) * 128 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + half * 128;
-      uint8_t* my_out = stage_out + (warp - 4) * 4096;
-#pragma unroll 1
-      for (int c = 0; c < ((g.debug & 1) ? 0 : 2); ++c) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(taddr + c * 64, r0);
-        tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+      const int row0 = m_blk * 256 + int(rank) * 128 + quarter * 32;
+      const int row = row0 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + cgroup * 64;
+      uint32_t r[2][32];
+      if (!(g.debug & 1)) {
+        tmem_ld_32x32b_x32(taddr, r[0]);
+        tmem_ld_32x32b_x32(taddr + 32, r[1]);
         tmem_ld_wait();
-        const int col = n_blk * kTileN + half * 128 + c * 64;
-        if constexpr (sizeof(OutT) == 2) {
-          // 64 columns -> 128 bytes per row, staged in this warp's swizzled box and stored by TMA
-          if (lane == 0) bulk_wait_group_read0();  // the previous box has left shared memory
-          __syncwarp();
-          uint8_t* rowp = my_out + lane * 128;
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const uint32_t* src = v < 4 ? &r0[v * 8] : &r1[(v - 4) * 8];
-            uint32_t p[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float lo = __uint_as_float(src[2 * j]) * g.alpha, hi = __uint_as_float(src[2 * j + 1]) * g.alpha;
-              if constexpr (std::is_same<OutT, __half>::value) {
-                p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
-              } else {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                p[j] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-            }
-            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmap_out, col, m_blk * 256 + int(rank) * 128 + quarter * 32, smem_u32(my_out));
-            bulk_commit_group();
-          }
-        } else {
-          if (row < g.m && col < g.n)
-            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r0, g.alpha, g.n - col, vec_ok);
-          if (row < g.m && col + 32 < g.n)
-            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r1, g.alpha, g.n - col - 32, vec_ok);
-        }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(free_bar);
+      if (g.debug & 1) continue;
+      const int col = n_blk * kTileN + cgroup * 64;
+      if constexpr (sizeof(OutT) == 2) {
+        // two boxes of 32 columns (64 bytes per row, 64-byte swizzle) through this warp's staging buffer
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (lane == 0) bulk_wait_group_read0();
+          __syncwarp();
+          uint8_t* rowp = box + lane * 64;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * g.alpha;
+              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * g.alpha;
+              if constexpr (std::is_same<OutT, __half>::value) {
+                p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
+              } else {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
+                p[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+            }
+            // 64-byte swizzle: 16-byte chunk index xor bits 1..2 of the row
+            *reinterpret_cast<uint4*>(rowp + ((v ^ ((lane >> 1) & 3)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, col + h * 32, row0, smem_u32(box));
+            bulk_commit_group();
+          }
+        }
+      } else {
+        if (row < g.m && col < g.n)
+          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r[0], g.alpha, g.n - col, vec_ok);
+        if (row < g.m && col + 32 < g.n)
+          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r[1], g.alpha, g.n - col - 32, vec_ok);
+      }
     }
     if (lane == 0) bulk_wait_group_read0();
   }

@@ -336,6 +336,62 @@ def nvfp4_scaled_matmul(
     )
 
 
+def nvfp4_w4a4_matmul(
+    A_packed: Tensor, B_packed: Tensor, act_scale: Tensor, weight_scale: Tensor, alpha: float = 1.0  # noqa: N803
+) -> Tensor:
+    """``A_packed @ B_packed`` for NVFP4 activations ``[M, K/2]`` and NVFP4 weights stored N-major ``[K/2, N]``
+    (row ``k`` in the low nibble, row ``k+1`` in the high nibble); bf16 ``[M, N]``.
+
+    Drop-in for ``nvfp4_w4a4_matmul`` (examples/nvfp4_gemm.py:259-304).  A byte of the N-major weight holds the
+    same two codes as the byte at the transposed position of the K-major weight, so the weight is transposed
+    byte-wise on the device and fed to the tensor-core GEMM.
+    """
+    a = fp4_storage(A_packed)
+    b = fp4_storage(B_packed)
+    m, k_bytes_a = a.shape
+    k_bytes_b, n = b.shape
+    if k_bytes_a != k_bytes_b:
+        raise ValueError(
+            f"A_packed shape {tuple(a.shape)} is incompatible with B_packed shape {tuple(b.shape)}"
+        )
+    k = k_bytes_a * 2
+    if k % 16 != 0:
+        raise ValueError(f"K must be divisible by 16, got {k}")
+    _check_swizzled_scales("act_scale", act_scale, m, k // 16)
+    _check_swizzled_scales("weight_scale", weight_scale, n, k // 16)
+    return _scaled_matmul_op(
+        _aligned(a.contiguous()), _aligned(b.t().contiguous()), _aligned(act_scale.reshape(-1).view(torch.uint8)),
+        _aligned(weight_scale.reshape(-1).view(torch.uint8)), alpha, torch.bfloat16,
+    )
+
+
+def nvfp4_w4a16_matmul(A: Tensor, B_packed: Tensor, weight_scale: Tensor, alpha: float = 1.0) -> Tensor:  # noqa: N803
+    """``A @ B_packed`` for bf16 activations ``[M, K]`` and NVFP4 weights stored N-major ``[K/2, N]``; bf16 ``[M, N]``.
+
+    Drop-in for ``nvfp4_w4a16_matmul`` (examples/nvfp4_gemm.py:171-210).  The weight is transposed byte-wise to
+    K-major and the activations go through the decode-batch kernel 32 rows at a time (the weights are streamed
+    once per 32 rows; like the reference's kernel this entry point is not the performance path for large M).
+    """
+    m, k = A.shape
+    b = fp4_storage(B_packed)
+    k_bytes, n = b.shape
+    if k % 16 != 0:
+        raise ValueError(f"K must be divisible by 16, got {k}")
+    if k_bytes * 2 != k:
+        raise ValueError(f"B_packed shape {tuple(b.shape)} is incompatible with A shape {tuple(A.shape)}")
+    _check_swizzled_scales("weight_scale", weight_scale, n, k // 16)
+    if A.dtype is not torch.bfloat16:
+        raise TypeError(f"A must be torch.bfloat16, got {A.dtype}")
+    w = b.t().contiguous()
+    sc = weight_scale.reshape(-1).view(torch.uint8)
+    a = A.contiguous()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=A.device)
+    for r0 in range(0, m, 32):
+        r1 = min(m, r0 + 32)
+        out[r0:r1] = _gemv_bf16in_op(w, _aligned(a[r0:r1]), sc, alpha, r1 - r0 == 1 and False)
+    return out
+
+
 def _aligned(t: Tensor) -> Tensor:
     """The kernels read activations with 16-byte loads; re-materialise odd views."""
     return t if t.data_ptr() % 16 == 0 else t.clone()

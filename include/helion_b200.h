@@ -167,6 +167,27 @@ int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* ro
                       const float* pair_weight, void* out_bf16, int64_t tokens, int64_t top_k, int64_t hidden,
                       void* stream);
 
+/* ------------------------------------------------ bf16 / fp16 grouped GEMM
+ * out[r, :] = A[r, :] . B[g]^T for the rows of every row tile, fp32 accumulate on
+ * the tensor cores (tcgen05 kind::f16), output in the input dtype.  A [a_rows, K]
+ * and B [groups * N, K] are K-major.  row_tiles holds int32 quadruples
+ * (group, first row, valid rows, rows to store) of at most 128 rows each: rows
+ * past "valid" are written as zero up to "store", rows past "store" are not
+ * written, a negative group marks an unused entry (read on the device only).
+ * Replaces the device work of grouped_gemm_deepgemm
+ * (pretuned_kernels/grouped_gemm_deepgemm/grouped_gemm_deepgemm.py:172-224),
+ * moe_matmul_ogs (examples/moe_matmul_ogs.py:31-85) and grouped_gemm_jagged
+ * (examples/grouped_gemm.py:52-104).  K % 8 == 0. */
+int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_t* row_tiles,
+                           int64_t num_row_tiles, int64_t a_rows, int64_t n, int64_t k, int64_t groups,
+                           int64_t ldc, int is_bf16, void* stream);
+
+/* Row tiles of a jagged layout from device-resident group offsets [groups + 1]
+ * (no host read): one entry per 128 rows of every group, unused entries marked.
+ * max_tiles >= total_rows / 128 + groups always suffices. */
+int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
+                          void* stream);
+
 /* Sticky device-side status: HB200_OK, or HB200_ERR_DEVICE_TIMEOUT once a
  * kernel gave up a bounded wait (its outputs are then undefined).  reset != 0
  * clears it.  Synchronises the device; not for use on the hot path.  (No
