@@ -42,6 +42,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_quantize_rows": [_P, _P, _P, _P, _I64, _I64, _I64, _P, c_int, _P, _P, c_int, _P],
     "hb200_grouped_gemm_f16": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_int, _P],
     "hb200_build_row_tiles": [_P, _I64, _P, _I64, _P],
+    "hb200_moe_gather_rows": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _I64, _I64, _P],
     "hb200_moe_combine": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p}

@@ -38,7 +38,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kGemmThreads = 256;  // producer, MMA issuer, scale copier, idle, four epilogue warps
+constexpr int kGemmThreads = 640;  // producer, MMA issuer, scale copier, idle, sixteen epilogue warps
 constexpr int kTmemCols = 512;
 
 struct GemmArgs {
@@ -137,7 +137,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 16);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -275,7 +275,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // idle: keeps the epilogue warps' lane-quarter mapping (warp % 4) aligned with warps 4..7
   } else {
     // ------------------------------------------------------------ epilogue
-    const int quarter = warp & 3;  // the tensor-memory lane quarter this warp may read
+    // Sixteen warps: warp w reads lane quarter w % 4 (the only one it may) and a quarter of the tile's
+    // columns.  A warp pulls its share of the accumulator into registers and hands the accumulator back
+    // at once; scaling, conversion and the stores then run beside the next tile's MMAs.
+    const int quarter = warp & 3, cgroup = (warp - 4) >> 2;
+    constexpr int CW = BLOCK_N / 4;  // columns per warp
     OutT* out = static_cast<OutT*>(g.out);
     const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
     uint32_t tc = 0;
@@ -295,38 +299,40 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       float alpha = g.alpha;
       if (g.group_alpha != nullptr) alpha *= g.group_alpha[t.group];
       if (g.row_scale != nullptr && row_ok) alpha *= g.row_scale[row];
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BLOCK_N;
-      if constexpr (BLOCK_N >= 32) {
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int col = n_blk * BLOCK_N + c * 32;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BLOCK_N + cgroup * CW;
+      if constexpr (CW >= 32) {
+        uint32_t r[CW / 32][32];
+#pragma unroll
+        for (int c = 0; c < CW / 32; ++c) tmem_ld_32x32b_x32(taddr + c * 32, r[c]);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+#pragma unroll
+        for (int c = 0; c < CW / 32; ++c) {
+          const int col = n_blk * BLOCK_N + cgroup * CW + c * 32;
           if (row_ok && col < g.n)
-            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r, alpha, g.n - col, vec_ok);
+            store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r[c], alpha, g.n - col, vec_ok);
         }
       } else {
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 8; ++c) {
-          uint32_t r8[8];
-          tmem_ld_32x32b_x8(taddr + c * 8, r8);
-          tmem_ld_wait();
-          const int col = n_blk * BLOCK_N + c * 8;
-          if (row_ok) {
+        uint32_t r8[8];
+        if (cgroup * CW < BLOCK_N) tmem_ld_32x32b_x8(taddr, r8);
+        tmem_ld_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        const int col = n_blk * BLOCK_N + cgroup * CW;
+        if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (col + j < g.n) {
-                const float v = __uint_as_float(r8[j]) * alpha;
-                if constexpr (sizeof(OutT) == 4) out[int64_t(row) * g.ldc + col + j] = v;
-                else if constexpr (std::is_same<OutT, __half>::value) out[int64_t(row) * g.ldc + col + j] = __float2half_rn(v);
-                else out[int64_t(row) * g.ldc + col + j] = __float2bfloat16_rn(v);
-              }
-          }
+          for (int j = 0; j < 8; ++j)
+            if (j < CW && col + j < g.n) {
+              const float v = __uint_as_float(r8[j]) * alpha;
+              if constexpr (sizeof(OutT) == 4) out[int64_t(row) * g.ldc + col + j] = v;
+              else if constexpr (std::is_same<OutT, __half>::value) out[int64_t(row) * g.ldc + col + j] = __float2half_rn(v);
+              else out[int64_t(row) * g.ldc + col + j] = __float2bfloat16_rn(v);
+            }
         }
       }
-      tcgen05_fence_before();
-      mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
   }
 

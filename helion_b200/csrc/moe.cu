@@ -13,9 +13,8 @@ namespace {
 //   row_of_sorted[p]  : padded row of sorted position p
 //   row_of_pair[pair] : padded row of a (token, slot) pair
 __global__ void __launch_bounds__(1024)
-moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, const int32_t* __restrict__ sorted_pairs,
-                    int pairs, int32_t* __restrict__ padded_offsets, int2* __restrict__ tile_info, int max_tiles,
-                    int32_t* __restrict__ row_of_sorted, int32_t* __restrict__ row_of_pair) {
+moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __restrict__ padded_offsets,
+                    int2* __restrict__ tile_info, int max_tiles) {
   extern __shared__ int32_t sh[];  // offsets[experts + 1], padded[experts + 1]
   int32_t* off = sh;
   int32_t* pad = sh + experts + 1;
@@ -47,16 +46,62 @@ moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, const int32
     }
     tile_info[t] = info;
   }
-  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-    int lo = 0, hi = experts;  // last e with off[e] <= p (experts with zero tokens share an offset)
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (off[mid] <= p) lo = mid; else hi = mid;
+}
+
+// Padded row of every sorted position / pair; every CTA rebuilds the two offset tables from the counts.
+__global__ void __launch_bounds__(256)
+moe_row_map_kernel(const int32_t* __restrict__ counts, int experts, const int32_t* __restrict__ sorted_pairs,
+                   int pairs, int32_t* __restrict__ row_of_sorted, int32_t* __restrict__ row_of_pair) {
+  extern __shared__ int32_t sh[];
+  int32_t* off = sh;
+  int32_t* pad = sh + experts + 1;
+  if (threadIdx.x == 0) {
+    int32_t o = 0, q = 0;
+    for (int e = 0; e < experts; ++e) {
+      off[e] = o;
+      pad[e] = q;
+      const int32_t c = max(counts[e], 0);
+      o += c;
+      q += (c + 127) / 128 * 128;
     }
-    const int32_t row = pad[lo] + (p - off[lo]);
-    row_of_sorted[p] = row;
-    row_of_pair[sorted_pairs[p]] = row;
+    off[experts] = o;
+    pad[experts] = q;
   }
+  __syncthreads();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= pairs) return;
+  int lo = 0, hi = experts;  // last e with off[e] <= p (experts with zero tokens share an offset)
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (off[mid] <= p) lo = mid; else hi = mid;
+  }
+  const int32_t row = pad[lo] + (p - off[lo]);
+  row_of_sorted[p] = row;
+  row_of_pair[sorted_pairs[p]] = row;
+}
+
+// Copies quantised token rows into the expert-sorted padded layout: codes [*, k/2], the row's scale bytes
+// (re-swizzled for the destination row) and its global scale.  A warp per destination row.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint8_t* __restrict__ codes_in, const uint8_t* __restrict__ scales_in,
+                       const float* __restrict__ g_in, uint8_t* __restrict__ codes_out,
+                       uint8_t* __restrict__ scales_out, float* __restrict__ g_out,
+                       const int32_t* __restrict__ src_pair, int src_div, const int32_t* __restrict__ dst_row,
+                       int64_t items, int64_t k) {
+  const int64_t item = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t src = int64_t(src_pair[item]) / src_div, dst = dst_row[item];
+  const int64_t k_bytes = k >> 1, col_tiles = ((k >> 4) + 3) >> 2;
+  const uint4* ci = reinterpret_cast<const uint4*>(codes_in + src * k_bytes);
+  uint4* co = reinterpret_cast<uint4*>(codes_out + dst * k_bytes);
+  for (int64_t c = lane; c < (k_bytes >> 4); c += 32) co[c] = ci[c];
+  // the four scales of a row inside one column tile are one aligned 32-bit word
+  const int64_t so = (src >> 7) * col_tiles * 512 + (src & 31) * 16 + ((src & 127) >> 5) * 4;
+  const int64_t d_o = (dst >> 7) * col_tiles * 512 + (dst & 31) * 16 + ((dst & 127) >> 5) * 4;
+  for (int64_t t = lane; t < col_tiles; t += 32)
+    *reinterpret_cast<uint32_t*>(scales_out + d_o + t * 512) = *reinterpret_cast<const uint32_t*>(scales_in + so + t * 512);
+  if (lane == 0) g_out[dst] = g_in[src];
 }
 
 // out[t, :] = bf16(sum over the token's top_k slots, in slot order, of w * o[row_of_pair[t*top_k + s], :]) in fp32,
@@ -108,9 +153,32 @@ extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, 
     return HB200_ERR_INVALID_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(tile_info) % 8) return HB200_ERR_INVALID_ARGUMENT;
   const size_t smem = size_t(2 * (experts + 1)) * sizeof(int32_t);
-  moe_schedule_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
-      counts, int(experts), sorted_pairs, int(pairs), padded_offsets, reinterpret_cast<int2*>(tile_info),
-      int(max_tiles), row_of_sorted, row_of_pair);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  moe_schedule_kernel<<<1, 1024, smem, s>>>(counts, int(experts), padded_offsets, reinterpret_cast<int2*>(tile_info),
+                                           int(max_tiles));
+  if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
+  if (pairs > 0)
+    moe_row_map_kernel<<<unsigned(ceil_div64(pairs, 256)), 256, smem, s>>>(counts, int(experts), sorted_pairs,
+                                                                          int(pairs), row_of_sorted, row_of_pair);
+  return launch_status();
+}
+
+// Copies per-token NVFP4 rows (codes, swizzled scales, global scale) into the expert-sorted padded layout:
+// item i reads token src_pair[i] / src_div and writes row dst_row[i].  No reference counterpart.
+extern "C" int hb200_moe_gather_rows(const void* codes_in, const void* scales_in, const float* g_in, void* codes_out,
+                                     void* scales_out, float* g_out, const int32_t* src_pair, int src_div,
+                                     const int32_t* dst_row, int64_t items, int64_t k, void* stream) {
+  using namespace hb200;
+  if (!codes_in || !scales_in || !g_in || !codes_out || !scales_out || !g_out || !src_pair || !dst_row)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (items < 0 || k <= 0 || (k % 32) != 0 || src_div <= 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(codes_in) % 16 || reinterpret_cast<uintptr_t>(codes_out) % 16 ||
+      reinterpret_cast<uintptr_t>(scales_in) % 4 || reinterpret_cast<uintptr_t>(scales_out) % 4)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (items == 0) return HB200_OK;
+  moe_gather_rows_kernel<<<unsigned(ceil_div64(items, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(codes_in), static_cast<const uint8_t*>(scales_in), g_in,
+      static_cast<uint8_t*>(codes_out), static_cast<uint8_t*>(scales_out), g_out, src_pair, src_div, dst_row, items, k);
   return launch_status();
 }
 

@@ -129,6 +129,29 @@ def _quantize_rows(x: Tensor, k: int, sched: MoeSchedule, src_div: int, item_sca
     return codes, scales, gscale
 
 
+def _quantize_and_gather(x: Tensor, sched: MoeSchedule, top_k: int):
+    """Quantise every token row once (per-token global scale), then copy the packed rows into the
+    expert-sorted padded layout -- an eighth of the arithmetic of quantising every (token, slot) pair."""
+    from .ops import nvfp4_quantize
+
+    t, k = x.shape
+    if k % 32:
+        return _quantize_rows(x, k, sched, top_k, None, False, gather=True)
+    codes_t, scales_t, g_t = nvfp4_quantize(x)
+    rows = sched.max_tiles * 128
+    dev = x.device
+    codes = torch.empty(rows, k // 2, dtype=torch.uint8, device=dev)
+    scales = torch.empty(swizzled_scale_numel(rows, k // 16), dtype=torch.uint8, device=dev)
+    gscale = torch.zeros(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call(
+            "hb200_moe_gather_rows", codes_t.data_ptr(), scales_t.data_ptr(), g_t.data_ptr(), codes.data_ptr(),
+            scales.data_ptr(), gscale.data_ptr(), sched.sorted_pairs.data_ptr(), top_k,
+            sched.row_of_sorted.data_ptr(), sched.sorted_pairs.numel(), k, _stream(),
+        )
+    return codes, scales, gscale
+
+
 def grouped_matmul(a_codes: Tensor, a_scales: Tensor, w: GroupedNvfp4Weight, sched: MoeSchedule,
                    row_scale: Tensor | None, out_dtype: torch.dtype = torch.bfloat16) -> Tensor:
     """``out[r] = row_scale[r] * w.global_scale[g(r)] * A[r] @ W[g(r)]^T`` over the padded row layout."""
@@ -160,7 +183,7 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
     sched = build_schedule(experts, e)
     # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
     w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()
-    a1, sf1, g1 = _quantize_rows(x, h, sched, top_k, None, False, gather=True)
+    a1, sf1, g1 = _quantize_and_gather(x, sched, top_k)
     h1 = grouped_matmul(a1, sf1, w_gate_up, sched, g1)
     a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, w_sorted, True, gather=False)
     o = grouped_matmul(a2, sf2, w_down, sched, g2)

@@ -160,6 +160,14 @@ int hb200_nvfp4_quantize_rows(const void* x_bf16, void* codes, void* scales_swiz
                               int64_t items, int64_t k, int64_t ldx, const int32_t* src_idx, int src_div,
                               const int32_t* dst_idx, const float* item_scale, int silu_mul, void* stream);
 
+/* Copies per-token NVFP4 rows (codes [*, K/2], swizzled scales, global scale) into the
+ * expert-sorted padded layout: item i reads token src_pair[i] / src_div and writes row
+ * dst_row[i] (scales are re-swizzled for the destination row).  K % 32 == 0.  No
+ * reference counterpart. */
+int hb200_moe_gather_rows(const void* codes_in, const void* scales_in, const float* g_in, void* codes_out,
+                          void* scales_out, float* g_out, const int32_t* src_pair, int src_div,
+                          const int32_t* dst_row, int64_t items, int64_t k, void* stream);
+
 /* out[t, :] = bf16(sum_s w[t, s] * expert_out[row_of_pair[t * top_k + s], :]) in
  * fp32, slot order; w = pair_weight (fp32 [tokens * top_k]) or 1 when null.  No
  * reference counterpart (the reference has no top-k combine). */
