@@ -167,6 +167,18 @@ def graphed(fn, warmup: int = 3):
     return g.replay, out
 
 
+def graphed_ring(fn, turns: int = 2):
+    """One graph per buffer of an output ring (``fn`` advances the ring by one per call); replays alternate."""
+    replays = [graphed(fn, warmup=turns)[0] for _ in range(turns)]
+    state = {"i": 0}
+
+    def replay():
+        replays[state["i"]]()
+        state["i"] = (state["i"] + 1) % turns
+
+    return replay
+
+
 def rel_err(y, ref) -> float:
     y, ref = y.detach().float().cpu(), ref.detach().float().cpu()
     floor = ref.pow(2).mean().sqrt().clamp(min=1e-30)
@@ -308,9 +320,15 @@ def wl_gemm(args, dev, rank, world, timer):
     def gemm_only():
         return hb.nvfp4_scaled_matmul(a_codes, b_codes.t(), a_scales, b_scales, alpha=alpha)
 
+    tp = ring = None
+    if world > 1:
+        tp = D.TensorParallel(dev)
+        ring = tp.gathered_output(m, n, torch.bfloat16)
+
     def step():
-        y = gemm_only()
-        return D.all_gather_columns(y) if world > 1 else y
+        if world > 1:  # the GEMM's epilogue stores its columns into every rank's buffer; then a barrier kernel
+            return tp.matmul(a_codes, a_scales, b_codes, b_scales, ring, alpha)
+        return gemm_only()
 
     # parity on a slice, against the oracle
     y = gemm_only()
@@ -318,22 +336,26 @@ def wl_gemm(args, dev, rank, world, timer):
                                 b_scales[: 256 * (k // 16)].cpu(), torch.float32, alpha=alpha)
     parity = rel_err(y[:256, :256], ref)
 
-    replay = step if world > 1 else graphed(step)[0]
+    extra = {}
+    if world > 1:
+        extra["fused_equals_collective"] = bool(torch.equal(step(), D.all_gather_columns(y)))
+    replay = graphed_ring(step) if world > 1 else graphed(step)[0]
     ms = timer.run(replay, args.steps, args.warmup)
     flops = 2 * m * n * k
-    extra = {}
     if world > 1:
         ms_gemm = timer.run(graphed(gemm_only)[0], args.steps, args.warmup)
         extra["gemm_only_ms"] = ms_gemm
+        extra["nccl_gather_ms"] = timer.run(lambda: D.all_gather_columns(gemm_only()), max(3, args.steps // 4), 3)
 
     host_out = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step():
         a = host_a.to(dev, non_blocking=True)
         c, s, _ = hb.nvfp4_quantize(a, ga)
-        y = hb.nvfp4_scaled_matmul(c, b_codes.t(), s, b_scales, alpha=alpha)
         if world > 1:
-            y = D.all_gather_columns(y)
+            y = tp.matmul(c, s, b_codes, b_scales, ring, alpha)
+        else:
+            y = hb.nvfp4_scaled_matmul(c, b_codes.t(), s, b_scales, alpha=alpha)
         host_out.copy_(y, non_blocking=True)
 
     e2e_ms = timer.run(e2e_step, max(3, args.steps // 10), 3)
@@ -374,11 +396,20 @@ def wl_gemv(args, dev, rank, world, timer):
             return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g).reshape(1, -1)
         return hb.nvfp4_gemv_bf16in_batched(c, x, s, g)
 
+    tp = None
+    rings = {}
+    if world > 1:
+        tp = D.TensorParallel(dev)
+        rings = {nm: tp.gathered_output(batch, n, torch.bfloat16) for nm, (n, _) in LAYER_70B.items()}
+
     def layer(xs):
         outs = {}
         for name in mats:
-            y = one(name, xs[name])
-            outs[name] = D.all_gather_columns(y) if world > 1 else y
+            if world > 1:  # the kernel stores its slice into every rank's buffer; a barrier kernel follows
+                c, s, g, n, k = mats[name]
+                outs[name] = tp.gemv(c, s, xs[name], rings[name], g)
+            else:
+                outs[name] = one(name, xs[name])
         return outs
 
     c, s, g, n, k = mats["o"]
@@ -387,7 +418,12 @@ def wl_gemv(args, dev, rank, world, timer):
         O.nvfp4_gemm_bf16in(c[:256].cpu(), host_x["o"], s[: 256 * (k // 16)].cpu(), g)[0]
     parity = rel_err(y, ref)
 
-    step = (lambda: layer(dev_x)) if world > 1 else graphed(lambda: layer(dev_x))[0]
+    extra = {}
+    if world > 1:
+        fused = layer(dev_x)
+        extra["fused_equals_collective"] = all(
+            bool(torch.equal(fused[nm], D.all_gather_columns(one(nm, dev_x[nm])))) for nm in mats)
+    step = graphed_ring(lambda: layer(dev_x)) if world > 1 else graphed(lambda: layer(dev_x))[0]
     ms = timer.run(step, args.steps, args.warmup)
     layer_bytes = sum(gemv_bytes(n, k, batch) for n, k in LAYER_70B.values())
 
@@ -417,7 +453,7 @@ def wl_gemv(args, dev, rank, world, timer):
     return dict(value=layer_bytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=layer_bytes / (e2e_ms * 1e-3) / 1e12,
                 e2e_ms=e2e_ms, h2d=sum(2 * batch * k for _, k in LAYER_70B.values()),
                 d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * (2 if world > 1 else 1),
-                roofline=roof, parity=parity, extra={"per_matrix": per_matrix},
+                roofline=roof, parity=parity, extra={"per_matrix": per_matrix, **extra},
                 dtype="fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
                 config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
                         "batch": batch, "parallelism": f"column-tp{world}" if world > 1 else "single",

@@ -19,6 +19,11 @@ import threading
 LIB_PATH = Path(__file__).resolve().parent / "libhelion_b200.so"
 
 HB200_OK = 0
+HB200_ERR_INVALID_ARGUMENT = -1
+HB200_ERR_UNSUPPORTED = -2
+HB200_ERR_CUDA = -3
+HB200_ERR_DEVICE_TIMEOUT = -4
+HB200_ERR_WORKSPACE = -5
 ABI_VERSION = 1
 
 _P = c_void_p
@@ -44,6 +49,9 @@ SIGNATURES: dict[str, list] = {
     "hb200_build_row_tiles": [_P, _I64, _P, _I64, _P],
     "hb200_moe_gather_rows": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, _I64, _I64, _P],
     "hb200_moe_combine": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _P],
+    "hb200_nvfp4_gemv_bf16in_tp": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P],
+    "hb200_nvfp4_scaled_matmul_tp": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_float, c_int, _P],
+    "hb200_peer_barrier": [_P, _I64, _I64, _P, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p}
 

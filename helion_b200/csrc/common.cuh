@@ -24,6 +24,15 @@ __host__ __device__ inline int64_t swizzled_scale_offset(int64_t row, int64_t co
   return ((row / 128) * col_tiles + col / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + col % 4;
 }
 
+// Where a kernel writes its bf16 result rows: one buffer, or the same place in the buffer of every rank of a
+// tensor-parallel group (peer-mapped pointers), at column col0 of rows of ld elements.
+struct OutSpec {
+  __nv_bfloat16* ptr[8];
+  int count;
+  int64_t ld;
+  int64_t col0;
+};
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;

@@ -400,8 +400,7 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
     return cudaMemset2DAsync(out, size_t(ldc) * elt, 0, size_t(n) * elt, size_t(m), s) == cudaSuccess ? HB200_OK
                                                                                                       : HB200_ERR_CUDA;
   }
-  static const bool no_pair = getenv("HB200_GEMM_NO_PAIR") != nullptr;
-  if (!no_pair) {
+  {
     const int rc = pair::launch_gemm_pair(a_packed, b_packed, scale_a, scale_b, out, m, n, k, ldc, alpha, out_dtype, s);
     if (rc != HB200_ERR_UNSUPPORTED) return rc;
   }
@@ -412,6 +411,37 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
     case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, 1, s);
     default: return dispatch_gemm<float>(a_packed, b_packed, g, 1, s);
   }
+}
+
+// Column-parallel form: this rank computes columns [col0, col0 + n) of the [m, n_total] result and writes them
+// into the buffer of every rank (out_ptrs[0..world), peer-mapped pointers of one symmetric allocation; entry
+// `rank` is this rank's own).  The local copy goes out through TMA, the remote ones as 16-byte stores over
+// NVLink from the same staging box.  Follow with hb200_peer_barrier before any rank reads its buffer.
+extern "C" int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, const void* scale_a,
+                                            const void* scale_b, void* const* out_ptrs, int64_t world, int64_t rank,
+                                            int64_t m, int64_t n, int64_t k, int64_t n_total, int64_t col0,
+                                            float alpha, int out_dtype, void* stream) {
+  using namespace hb200;
+  if (!a_packed || !b_packed || !scale_a || !scale_b || !out_ptrs) return HB200_ERR_INVALID_ARGUMENT;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return HB200_ERR_INVALID_ARGUMENT;
+  if (m < 0 || n < 0 || k < 0 || col0 < 0 || col0 + n > n_total || out_dtype < 0 || out_dtype > 1)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if ((k % 16) != 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a_packed) % 16 || reinterpret_cast<uintptr_t>(b_packed) % 16 ||
+      reinterpret_cast<uintptr_t>(scale_a) % 16 || reinterpret_cast<uintptr_t>(scale_b) % 16)
+    return HB200_ERR_INVALID_ARGUMENT;
+  pair::PeerOut peers;
+  peers.n_total = n_total;
+  peers.col0 = col0;
+  for (int i = 0; i < world; ++i) {
+    if (!out_ptrs[i] || reinterpret_cast<uintptr_t>(out_ptrs[i]) % 16) return HB200_ERR_INVALID_ARGUMENT;
+    if (i != rank) peers.ptr[peers.n_peers++] = out_ptrs[i];
+  }
+  if (m == 0 || n == 0) return HB200_OK;
+  if (k == 0 || (k % 32) != 0 || (n_total % 8) != 0) return HB200_ERR_UNSUPPORTED;
+  if (m > 0x7fffff00 || n_total > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  return pair::launch_gemm_pair(a_packed, b_packed, scale_a, scale_b, out_ptrs[rank], m, n, k, n_total, alpha,
+                                out_dtype, static_cast<cudaStream_t>(stream), peers);
 }
 
 extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_packed, const void* scale_a,
@@ -447,6 +477,7 @@ extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_pa
 // bounded waits ran out.  Synchronises the device.
 namespace hb200 {
 int f16_device_status(int reset);
+int peer_device_status(int reset);
 }
 
 extern "C" int hb200_device_status(int reset) {
@@ -457,5 +488,6 @@ extern "C" int hb200_device_status(int reset) {
     if (cudaMemcpyToSymbol(hb200::g_device_status, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
   }
   const int w = hb200::f16_device_status(reset);
-  return v != 0 ? v : w;
+  const int p = hb200::peer_device_status(reset);
+  return v != 0 ? v : (w != 0 ? w : p);
 }

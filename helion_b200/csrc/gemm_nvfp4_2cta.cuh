@@ -50,7 +50,11 @@ struct PairArgs {
   int m, n, k;
   float alpha;
   int m_tiles, n_tiles;  // 256 x 256 tiles
-  int debug;
+  // Tensor-parallel form: the tile columns start at col0 of the (wider) output, and every tile is also
+  // written to the same place of each peer's buffer with plain stores over NVLink.
+  int col0;
+  int n_peers;
+  void* peer_out[7];
 };
 
 template <typename OutT>
@@ -150,7 +154,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + kBOff2);
           const uint32_t sf_col = tmem_base + kSfBase2 + s * kSfCols2;
           if (elect_one()) {
-            if (!(g.debug & 4))
             for (int a = 0; a < atoms; ++a) {
               const uint64_t adesc = make_smem_desc(a_addr + a * 32, 16, 1024, kSwizzle128B);
               const uint64_t bdesc = make_smem_desc(b_addr + a * 32, 16, 1024, kSwizzle128B);
@@ -183,7 +186,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const uint32_t sfa_addr = smem_u32(st + kSfaOff2), sfb_addr = smem_u32(st + kSfbOff2);
           const uint32_t sf_col = tmem_base + kSfBase2 + s * kSfCols2;
           if (elect_one()) {
-            if (!(g.debug & 2) || kb == 0)
             for (int a = 0; a < atoms; ++a) {
               tcgen05_cp_32x128b_warpx4_pair(sf_col + a * 4, make_smem_desc(sfa_addr + a * kAtomBytes, 0, 128, kSwizzleNone));
               tcgen05_cp_32x128b_warpx4_pair(sf_col + 16 + a * 8,
@@ -219,15 +221,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + cgroup * 64;
       uint32_t r[2][32];
-      if (!(g.debug & 1)) {
-        tmem_ld_32x32b_x32(taddr, r[0]);
-        tmem_ld_32x32b_x32(taddr + 32, r[1]);
-        tmem_ld_wait();
-      }
+      tmem_ld_32x32b_x32(taddr, r[0]);
+      tmem_ld_32x32b_x32(taddr + 32, r[1]);
+      tmem_ld_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(free_bar);
-      if (g.debug & 1) continue;
       const int col = n_blk * kTileN + cgroup * 64;
       if constexpr (sizeof(OutT) == 2) {
         // two boxes of 32 columns (64 bytes per row, 64-byte swizzle) through this warp's staging buffer
@@ -259,6 +258,20 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             tma_store_2d(&tmap_out, col + h * 32, row0, smem_u32(box));
             bulk_commit_group();
           }
+          if (g.n_peers > 0) {
+            // the same box to every peer: 4 lanes cover the 64 bytes of a row, 8 rows per pass
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rl = i * 8 + (lane >> 2), c = lane & 3;
+              const uint4 v = *reinterpret_cast<const uint4*>(box + rl * 64 + ((c ^ ((rl >> 1) & 3)) << 4));
+              const int cc = col + h * 32 + c * 8;
+              if (row0 + rl < g.m && cc < g.n) {
+                const int64_t off = int64_t(row0 + rl) * g.ldc + g.col0 + cc;
+                for (int p = 0; p < g.n_peers; ++p) stg_stream_u4(static_cast<OutT*>(g.peer_out[p]) + off, v);
+              }
+            }
+            __syncwarp();
+          }
         }
       } else {
         if (row < g.m && col < g.n)
@@ -282,9 +295,19 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 
 // Dense GEMM on CTA pairs; returns HB200_ERR_UNSUPPORTED for shapes it does not take
 // (the caller then uses the single-CTA kernel).
+struct PeerOut {
+  int64_t n_total = 0;  // columns of the gathered output (0: not tensor parallel)
+  int64_t col0 = 0;
+  int n_peers = 0;
+  void* ptr[7] = {};
+};
+
 inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const void* sfb, void* out, int64_t m, int64_t n,
-                     int64_t k, int64_t ldc, float alpha, int out_dtype, cudaStream_t stream) {
+                     int64_t k, int64_t ldc, float alpha, int out_dtype, cudaStream_t stream,
+                     const PeerOut& peers = PeerOut()) {
   if (m < 256 || n < 256 || (k % 32) != 0) return HB200_ERR_UNSUPPORTED;
+  const bool tp = peers.n_total > 0;
+  if (tp && (out_dtype == 2 || (n % 8) != 0 || (peers.col0 % 8) != 0)) return HB200_ERR_UNSUPPORTED;
   CUtensorMap ta, tb, tsa, tsb;
   const int64_t col_tiles = (k / 16 + 3) / 4;
   if (!make_operand_map(&ta, a, m, k / 2, 128) || !make_operand_map(&tb, b, n, k / 2, 128)) return HB200_ERR_CUDA;
@@ -294,11 +317,18 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
   CUtensorMap tout;
   if (out_dtype != 2) {
     if ((ldc % 8) != 0 || reinterpret_cast<uintptr_t>(out) % 16) return HB200_ERR_UNSUPPORTED;
-    if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
+    // tensor parallel: the map spans this rank's columns only, so partial tiles are clipped at their end
+    void* base = tp ? static_cast<void*>(static_cast<uint16_t*>(out) + peers.col0) : out;
+    if (!make_output_map16(&tout, base, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
   } else {
     tout = ta;  // unused by the fp32 epilogue
   }
-  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), getenv("HB200_GEMM_DEBUG") ? atoi(getenv("HB200_GEMM_DEBUG")) : 0};
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, 0, {}};
+  if (tp) {
+    g.col0 = int(peers.col0);
+    g.n_peers = peers.n_peers;
+    for (int i = 0; i < peers.n_peers; ++i) g.peer_out[i] = peers.ptr[i];
+  }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = g.m_tiles * g.n_tiles;

@@ -93,7 +93,7 @@ struct GemvArgs {
   const void* x;           // bf16 [K] or packed e2m1 [K/2]
   const uint8_t* w_scale;  // swizzled [N, K/16]
   const uint8_t* x_scale;  // swizzled [1, K/16] (fp4 input only)
-  __nv_bfloat16* out;      // [N]
+  OutSpec out;             // [N] (one buffer, or one per tensor-parallel rank)
   int64_t n, k;
   int iters_per_split;     // 256-element iterations handled by one CTA of the cluster
   float alpha;
@@ -202,7 +202,10 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
   acc += __shfl_xor_sync(0xffffffffu, acc, 4);
 
   if (n_split == 1) {
-    if (j == 0 && row_ok) a.out[row] = __float2bfloat16_rn(acc * a.alpha);
+    if (j == 0 && row_ok) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(acc * a.alpha);
+      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][a.out.col0 + row] = v;
+    }
     return;
   }
   // split-K: every CTA deposits its 32 partial sums in the leader's shared
@@ -219,7 +222,10 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
     const int64_t r = tile * 128 + ((blockIdx.x & 3) << 3) + w2 + 32 * q2;
     float s = 0.f;
     for (int i = 0; i < n_split; ++i) s += part[i][threadIdx.x];
-    if (r < a.n) a.out[r] = __float2bfloat16_rn(s * a.alpha);
+    if (r < a.n) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(s * a.alpha);
+      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][a.out.col0 + r] = v;
+    }
   }
 }
 
@@ -273,10 +279,9 @@ int dispatch_gemv(const GemvArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-int gemv_bf16in_batch1(const void* w, const void* x, const void* ws, void* out, int64_t n, int64_t k, float alpha,
-                       cudaStream_t stream) {
-  GemvArgs a{static_cast<const uint8_t*>(w), x, static_cast<const uint8_t*>(ws), nullptr,
-             static_cast<__nv_bfloat16*>(out), n, k, 0, alpha};
+int gemv_bf16in_batch1(const void* w, const void* x, const void* ws, const OutSpec& out, int64_t n, int64_t k,
+                       float alpha, cudaStream_t stream) {
+  GemvArgs a{static_cast<const uint8_t*>(w), x, static_cast<const uint8_t*>(ws), nullptr, out, n, k, 0, alpha};
   return dispatch_gemv<false>(a, stream);
 }
 
@@ -290,8 +295,12 @@ extern "C" int hb200_nvfp4_gemv_fp4in(const void* weight_packed, const void* x_p
   if (reinterpret_cast<uintptr_t>(weight_packed) % 8 || reinterpret_cast<uintptr_t>(x_packed) % 4)
     return HB200_ERR_INVALID_ARGUMENT;
   if (n == 0) return HB200_OK;
+  hb200::OutSpec o{};
+  o.ptr[0] = static_cast<__nv_bfloat16*>(out_bf16);
+  o.count = 1;
+  o.ld = n;
+  o.col0 = 0;
   hb200::GemvArgs a{static_cast<const uint8_t*>(weight_packed), x_packed,
-                    static_cast<const uint8_t*>(weight_scale), static_cast<const uint8_t*>(x_scale),
-                    static_cast<__nv_bfloat16*>(out_bf16), n, k, 0, alpha};
+                    static_cast<const uint8_t*>(weight_scale), static_cast<const uint8_t*>(x_scale), o, n, k, 0, alpha};
   return hb200::dispatch_gemv<true>(a, static_cast<cudaStream_t>(stream));
 }

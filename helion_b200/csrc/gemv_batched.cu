@@ -41,7 +41,7 @@ struct BatchedArgs {
   const uint8_t* w;
   const __nv_bfloat16* x;  // [batch, K]
   const uint8_t* w_scale;
-  __nv_bfloat16* out;      // [batch, N]
+  OutSpec out;             // [batch, N] (one buffer, or one per tensor-parallel rank)
   int64_t n, k;
   int batch;
   int iters_per_split;     // 128-element iterations per CTA of the cluster
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(kThreads) nvfp4_gemv_batched_kernel(const Batc
       if (r >= a.n) continue;
       float s = 0.f;
       for (int i = 0; i < n_split; ++i) s += buf[size_t(i) * (NT * 8 * kRows) + e];
-      a.out[int64_t(b) * a.n + r] = __float2bfloat16_rn(s * a.alpha);
+      const __nv_bfloat16 v = __float2bfloat16_rn(s * a.alpha);
+      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][int64_t(b) * a.out.ld + a.out.col0 + r] = v;
     }
   }
 }
@@ -262,30 +263,46 @@ int dispatch_batched(const BatchedArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-int gemv_bf16in_batch1(const void* w, const void* x, const void* ws, void* out, int64_t n, int64_t k, float alpha,
-                       cudaStream_t stream);
+int gemv_bf16in_batch1(const void* w, const void* x, const void* ws, const OutSpec& out, int64_t n, int64_t k,
+                       float alpha, cudaStream_t stream);
+
+namespace {
+int gemv_dispatch_all(const void* w, const void* x, const void* ws, const OutSpec& out, int64_t n, int64_t k,
+                      int64_t batch, float alpha, bool force_mma, cudaStream_t s) {
+  if (batch == 1 && !force_mma) return gemv_bf16in_batch1(w, x, ws, out, n, k, alpha, s);
+  BatchedArgs a{static_cast<const uint8_t*>(w), static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(ws),
+                out, n, k, int(batch), 0, 0, alpha};
+  if (batch <= 8) return dispatch_batched<1>(a, s);
+  if (batch <= 16) return dispatch_batched<2>(a, s);
+  return dispatch_batched<4>(a, s);
+}
+}  // namespace
 
 }  // namespace hb200
+
+namespace {
+int check_gemv_args(const void* w, const void* x, const void* ws, int64_t n, int64_t k, int64_t batch) {
+  if (!w || !x || !ws) return HB200_ERR_INVALID_ARGUMENT;
+  if (n < 0 || k < 0 || (k % 16) != 0 || batch < 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (batch > 32) return HB200_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(w) % 8 || reinterpret_cast<uintptr_t>(x) % 16) return HB200_ERR_INVALID_ARGUMENT;
+  return HB200_OK;
+}
+}  // namespace
 
 extern "C" int hb200_nvfp4_gemv_bf16in(const void* weight_packed, const void* x_bf16, const void* weight_scale,
                                        void* out_bf16, int64_t n, int64_t k, int64_t batch, float alpha,
                                        void* stream) {
-  if (!weight_packed || !x_bf16 || !weight_scale || !out_bf16) return HB200_ERR_INVALID_ARGUMENT;
-  if (n < 0 || k < 0 || (k % 16) != 0 || batch < 0) return HB200_ERR_INVALID_ARGUMENT;
-  if (batch > 32) return HB200_ERR_UNSUPPORTED;
-  if (reinterpret_cast<uintptr_t>(weight_packed) % 8 || reinterpret_cast<uintptr_t>(x_bf16) % 16 ||
-      reinterpret_cast<uintptr_t>(out_bf16) % 2)
-    return HB200_ERR_INVALID_ARGUMENT;
+  if (!out_bf16) return HB200_ERR_INVALID_ARGUMENT;
+  const int rc = check_gemv_args(weight_packed, x_bf16, weight_scale, n, k, batch);
+  if (rc != HB200_OK) return rc;
   if (n == 0 || batch == 0) return HB200_OK;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (batch == 1) return hb200::gemv_bf16in_batch1(weight_packed, x_bf16, weight_scale, out_bf16, n, k, alpha, s);
-  if ((k % 8) != 0) return HB200_ERR_INVALID_ARGUMENT;
-  hb200::BatchedArgs a{static_cast<const uint8_t*>(weight_packed), static_cast<const __nv_bfloat16*>(x_bf16),
-                       static_cast<const uint8_t*>(weight_scale), static_cast<__nv_bfloat16*>(out_bf16),
-                       n, k, int(batch), 0, 0, alpha};
-  if (batch <= 8) return hb200::dispatch_batched<1>(a, s);
-  if (batch <= 16) return hb200::dispatch_batched<2>(a, s);
-  return hb200::dispatch_batched<4>(a, s);
+  hb200::OutSpec o{};
+  o.ptr[0] = static_cast<__nv_bfloat16*>(out_bf16);
+  o.count = 1;
+  o.ld = n;
+  return hb200::gemv_dispatch_all(weight_packed, x_bf16, weight_scale, o, n, k, batch, alpha, false,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 // Same arithmetic as the batched kernel for a single activation row (fp32
@@ -293,16 +310,36 @@ extern "C" int hb200_nvfp4_gemv_bf16in(const void* weight_packed, const void* x_
 extern "C" int hb200_nvfp4_gemv_bf16in_mma(const void* weight_packed, const void* x_bf16, const void* weight_scale,
                                            void* out_bf16, int64_t n, int64_t k, int64_t batch, float alpha,
                                            void* stream) {
-  if (!weight_packed || !x_bf16 || !weight_scale || !out_bf16) return HB200_ERR_INVALID_ARGUMENT;
-  if (n < 0 || k < 0 || (k % 16) != 0 || batch < 1 || batch > 32) return HB200_ERR_INVALID_ARGUMENT;
-  if (reinterpret_cast<uintptr_t>(weight_packed) % 8 || reinterpret_cast<uintptr_t>(x_bf16) % 16)
-    return HB200_ERR_INVALID_ARGUMENT;
+  if (!out_bf16 || batch < 1) return HB200_ERR_INVALID_ARGUMENT;
+  const int rc = check_gemv_args(weight_packed, x_bf16, weight_scale, n, k, batch);
+  if (rc != HB200_OK) return rc;
   if (n == 0) return HB200_OK;
-  hb200::BatchedArgs a{static_cast<const uint8_t*>(weight_packed), static_cast<const __nv_bfloat16*>(x_bf16),
-                       static_cast<const uint8_t*>(weight_scale), static_cast<__nv_bfloat16*>(out_bf16),
-                       n, k, int(batch), 0, 0, alpha};
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (batch <= 8) return hb200::dispatch_batched<1>(a, s);
-  if (batch <= 16) return hb200::dispatch_batched<2>(a, s);
-  return hb200::dispatch_batched<4>(a, s);
+  hb200::OutSpec o{};
+  o.ptr[0] = static_cast<__nv_bfloat16*>(out_bf16);
+  o.count = 1;
+  o.ld = n;
+  return hb200::gemv_dispatch_all(weight_packed, x_bf16, weight_scale, o, n, k, batch, alpha, true,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+// Column-parallel form: this rank owns weight rows (output columns) [col0, col0 + n) of n_total and writes
+// its slice of the result into the [batch, n_total] buffer of every rank (out_ptrs[0..world), peer-mapped
+// device pointers of a symmetric allocation).  Follow with hb200_peer_barrier before reading the buffer.
+extern "C" int hb200_nvfp4_gemv_bf16in_tp(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                                          void* const* out_ptrs, int64_t world, int64_t n, int64_t k, int64_t batch,
+                                          int64_t n_total, int64_t col0, float alpha, void* stream) {
+  if (!out_ptrs || world < 1 || world > 8 || col0 < 0 || col0 + n > n_total) return HB200_ERR_INVALID_ARGUMENT;
+  const int rc = check_gemv_args(weight_packed, x_bf16, weight_scale, n, k, batch);
+  if (rc != HB200_OK) return rc;
+  if (n == 0 || batch == 0) return HB200_OK;
+  hb200::OutSpec o{};
+  for (int i = 0; i < world; ++i) {
+    if (!out_ptrs[i]) return HB200_ERR_INVALID_ARGUMENT;
+    o.ptr[i] = static_cast<__nv_bfloat16*>(out_ptrs[i]);
+  }
+  o.count = int(world);
+  o.ld = n_total;
+  o.col0 = col0;
+  return hb200::gemv_dispatch_all(weight_packed, x_bf16, weight_scale, o, n, k, batch, alpha, false,
+                                  static_cast<cudaStream_t>(stream));
 }

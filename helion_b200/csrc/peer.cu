@@ -1,0 +1,84 @@
+// Barrier between the ranks of a tensor-parallel group, as a kernel on the caller's stream.
+//
+// Every rank owns a small flag array in a symmetric allocation (flags[i] is written by rank i only).  A call
+// takes the next epoch from a counter in this rank's own memory, publishes it into flags[rank] of every rank
+// with a system-scope release store, and waits (system-scope acquire loads) until every entry of its own
+// array has reached that epoch.  Stores that kernels earlier on the stream made to peer buffers are ordered
+// before the release by a system-scope fence, so after the barrier every rank may read what the others
+// pushed into its buffer.  All ranks must call it the same number of times; the kernel keeps no host state,
+// so a CUDA graph that contains it can be replayed.
+//
+// The wait is bounded (about two seconds of SM clock): on expiry the kernel records a sticky
+// HB200_ERR_DEVICE_TIMEOUT, readable through hb200_device_status, and returns.
+#include "common.cuh"
+
+namespace hb200 {
+
+__device__ int g_device_status_peer = 0;
+
+namespace {
+
+struct BarrierArgs {
+  uint32_t* flags[8];  // flags[i]: rank i's array, as mapped into this process
+  uint32_t* epoch;     // this rank's counter (local memory)
+  int rank, world;
+};
+
+constexpr long long kWaitCycles = 4000000000ll;
+
+__global__ void peer_barrier_kernel(const BarrierArgs a) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) {
+    epoch_s = *a.epoch + 1;
+    *a.epoch = epoch_s;
+  }
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const int peer = threadIdx.x;
+  if (peer >= a.world) return;
+  __threadfence_system();
+  uint32_t* remote = a.flags[peer] + a.rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" : : "l"(remote), "r"(epoch) : "memory");
+  const uint32_t* mine = a.flags[a.rank] + peer;
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (int32_t(v - epoch) >= 0) break;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicMin(&g_device_status_peer, HB200_ERR_DEVICE_TIMEOUT);
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+
+}  // namespace
+
+int peer_device_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_status_peer, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  if (reset && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_device_status_peer, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  }
+  return v;
+}
+
+}  // namespace hb200
+
+extern "C" int hb200_peer_barrier(void* const* flag_ptrs, int64_t world, int64_t rank, void* epoch_counter,
+                                  void* stream) {
+  if (!flag_ptrs || !epoch_counter || world < 1 || world > 8 || rank < 0 || rank >= world)
+    return HB200_ERR_INVALID_ARGUMENT;
+  hb200::BarrierArgs a{};
+  for (int i = 0; i < world; ++i) {
+    if (!flag_ptrs[i] || reinterpret_cast<uintptr_t>(flag_ptrs[i]) % 4) return HB200_ERR_INVALID_ARGUMENT;
+    a.flags[i] = static_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  a.epoch = static_cast<uint32_t*>(epoch_counter);
+  a.rank = int(rank);
+  a.world = int(world);
+  hb200::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return hb200::launch_status();
+}

@@ -79,6 +79,132 @@ def column_parallel_matmul(a_packed: Tensor, scale_a: Tensor, b_local: Tensor, s
     return all_gather_columns(y, group)
 
 
+# ------------------------------------------------------------------ fused column parallelism
+class GatheredOutput:
+    """A ring of ``[rows, n_total]`` output buffers in symmetric memory, mapped into every rank.
+
+    Two buffers alternate so that a rank may still read the result of one step while its peers already
+    push the next one; ``hb200_peer_barrier`` after every step is the only synchronisation needed.
+    """
+
+    def __init__(self, locals_: list[Tensor], ptr_arrays: list):
+        self.locals = locals_
+        self.ptr_arrays = ptr_arrays
+        self.turn = 0
+
+    def next(self):
+        i = self.turn
+        self.turn = (i + 1) % len(self.locals)
+        return self.locals[i], self.ptr_arrays[i]
+
+
+class TensorParallel:
+    """Column-parallel GEMV / GEMM whose kernels store their output slice straight into every rank's buffer
+    over NVLink, followed by a barrier kernel: no collective call and no host involvement per step, so a whole
+    step can be captured in a CUDA graph.  With one rank (or no process group) it degenerates to the plain
+    kernels writing a local buffer.
+
+    The symmetric allocation and the peer mapping come from ``torch.distributed._symmetric_memory``
+    (the allocator the reference's distributed examples use, examples/distributed/all_gather_matmul.py:90-130).
+    """
+
+    def __init__(self, device: torch.device, group=None):
+        import ctypes
+
+        self._ct = ctypes
+        self.device = device
+        self.group = group
+        active = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if active else 1
+        self.rank = dist.get_rank(group) if active else 0
+        self._handles = []  # keeps the rendezvous handles (and so the peer mappings) alive
+        flags = self._symmetric(64, torch.int32)
+        self.flag_ptrs = flags[1]
+        self._flags = flags[0]
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self._sync_all()
+
+    # -- allocation
+    def _symmetric(self, numel: int, dtype: torch.dtype):
+        """Zeroed symmetric tensor of ``numel`` elements -> (local tensor, ctypes array of per-rank pointers)."""
+        ct = self._ct
+        if self.world == 1:
+            t = torch.zeros(numel, dtype=dtype, device=self.device)
+            ptrs = [t.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+            t.zero_()
+            g = self.group if self.group is not None else dist.group.WORLD
+            hdl = symm_mem.rendezvous(t, g.group_name)
+            self._handles.append(hdl)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+        arr = (ct.c_void_p * len(ptrs))(*ptrs)
+        return t, arr
+
+    def _sync_all(self):
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def gathered_output(self, rows: int, n_total: int, dtype: torch.dtype = torch.bfloat16, buffers: int = 2) -> GatheredOutput:
+        locals_, arrays = [], []
+        for _ in range(buffers):
+            t, arr = self._symmetric(rows * n_total, dtype)
+            locals_.append(t.view(rows, n_total))
+            arrays.append(arr)
+        self._sync_all()  # every rank's zero-fill is done before anybody pushes
+        return GatheredOutput(locals_, arrays)
+
+    # -- steps
+    def barrier(self) -> None:
+        from . import _lib
+
+        _lib.call("hb200_peer_barrier", self.flag_ptrs, self.world, self.rank, self._epoch.data_ptr(),
+                  torch.cuda.current_stream(self.device).cuda_stream)
+
+    def gemv(self, weight_local: Tensor, scale_local: Tensor, x: Tensor, out: GatheredOutput, alpha: float = 1.0,
+             barrier: bool = True) -> Tensor:
+        """``x [M, K]`` bf16 (replicated, 1 <= M <= 32) against this rank's weight rows; every rank ends up with
+        the full ``[M, N]`` in its buffer (returned)."""
+        from . import _lib
+
+        m, k = x.shape
+        n_local = weight_local.shape[0]
+        buf, ptrs = out.next()
+        if buf.shape[0] < m or buf.shape[1] != n_local * self.world or buf.dtype != torch.bfloat16:
+            raise ValueError("output ring does not match [M, N_local * world] bf16")
+        if weight_local.shape[1] * 2 != k:
+            raise ValueError("weight and activation disagree on K")
+        _lib.call("hb200_nvfp4_gemv_bf16in_tp", weight_local.data_ptr(), x.data_ptr(), scale_local.data_ptr(), ptrs,
+                  self.world, n_local, k, m, buf.shape[1], self.rank * n_local, float(alpha),
+                  torch.cuda.current_stream(self.device).cuda_stream)
+        if barrier:
+            self.barrier()
+        return buf[:m]
+
+    def matmul(self, a_packed: Tensor, scale_a: Tensor, b_local: Tensor, scale_b_local: Tensor, out: GatheredOutput,
+               alpha: float = 1.0, barrier: bool = True) -> Tensor:
+        """Block-scaled GEMM, B's rows ``[N_local, K/2]`` (output columns) owned by this rank, A replicated."""
+        from . import _lib
+
+        m, kb = a_packed.shape
+        n_local = b_local.shape[0]
+        buf, ptrs = out.next()
+        if buf.shape[0] != m or buf.shape[1] != n_local * self.world:
+            raise ValueError("output ring does not match [M, N_local * world]")
+        if buf.dtype not in (torch.bfloat16, torch.float16):
+            raise TypeError("fused column-parallel matmul writes bf16 or fp16")
+        _lib.call("hb200_nvfp4_scaled_matmul_tp", a_packed.data_ptr(), b_local.data_ptr(), scale_a.data_ptr(),
+                  scale_b_local.data_ptr(), ptrs, self.world, self.rank, m, n_local, 2 * kb, buf.shape[1],
+                  self.rank * n_local, float(alpha), 0 if buf.dtype == torch.bfloat16 else 1,
+                  torch.cuda.current_stream(self.device).cuda_stream)
+        if barrier:
+            self.barrier()
+        return buf
+
+
 # ------------------------------------------------------------------ expert parallelism
 @dataclass
 class DispatchPlan:

@@ -196,6 +196,33 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* ---- tensor-parallel forms (one process per GPU, outputs in symmetric memory) ----
+ *
+ * The reference's distributed examples push results to peers from inside the kernel through symmetric
+ * memory and signal pads (examples/distributed/all_gather_matmul.py:36-87,
+ * helion/runtime/triton/dist_utils.py:291-406); these entry points are the same idea for the column-parallel
+ * GEMV and GEMM: rank r owns weight rows [col0, col0 + n) of n_total, computes that slice of the output and
+ * stores it into the [rows, n_total] buffer of every rank.  out_ptrs[i] is rank i's buffer as mapped into
+ * this process (CUDA peer mapping of one symmetric allocation).  Plain stores only; no TMA load or
+ * multicast touches peer memory. */
+int hb200_nvfp4_gemv_bf16in_tp(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                               void* const* out_ptrs, int64_t world, int64_t n, int64_t k, int64_t batch,
+                               int64_t n_total, int64_t col0, float alpha, void* stream);
+
+/* out_dtype 0 = bf16, 1 = fp16.  Needs m >= 256, n >= 256, K % 32 == 0, n_total % 8 == 0, col0 % 8 == 0
+ * (HB200_ERR_UNSUPPORTED otherwise: compute locally and gather with a collective). */
+int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, const void* scale_a,
+                                 const void* scale_b, void* const* out_ptrs, int64_t world, int64_t rank,
+                                 int64_t m, int64_t n, int64_t k, int64_t n_total, int64_t col0, float alpha,
+                                 int out_dtype, void* stream);
+
+/* Barrier between the ranks as a kernel on `stream`: flag_ptrs[i] is rank i's array of >= world uint32
+ * (zero-initialised symmetric memory), epoch_counter one uint32 in this rank's own memory (zero-initialised,
+ * owned by the barrier).  Orders every earlier peer store on the stream before the other ranks' later reads.
+ * The wait is bounded; on expiry hb200_device_status reports HB200_ERR_DEVICE_TIMEOUT.  Replaces the
+ * signal-pad barrier of helion/runtime/triton/dist_utils.py:291-406. */
+int hb200_peer_barrier(void* const* flag_ptrs, int64_t world, int64_t rank, void* epoch_counter, void* stream);
+
 /* Sticky device-side status: HB200_OK, or HB200_ERR_DEVICE_TIMEOUT once a
  * kernel gave up a bounded wait (its outputs are then undefined).  reset != 0
  * clears it.  Synchronises the device; not for use on the hot path.  (No
