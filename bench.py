@@ -112,16 +112,25 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline kernels, from the
+# `ncu --set full` captures summarised under profiles/ (same bench command, same sizes).
+NCU_TRAFFIC = {
+    "gemm_8192": 220.3e6,           # profiles/nvfp4_gemm_pair_kernel_8192x8192x8192.md
+    "gemv_gate_up_m1": 268.0e6,     # profiles/nvfp4_gemv_kernels_70b_decode_layer.md
+    "gemv_gate_up_m8": 268.6e6,
+    "rms_norm_16384x7168": 314.4e6,      # profiles/quant_producers_16384_tokens.md
+}
+
+
 def ncu_traffic(key: str):
-    """DRAM bytes per launch recorded from an ncu capture (profiles/traffic.json), or None."""
-    p = ROOT / "profiles" / "traffic.json"
-    if p.exists():
-        return json.loads(p.read_text()).get(key)
-    return None
+    return NCU_TRAFFIC.get(key)
 
 
 # ------------------------------------------------------------------ timing
 class Timer:
+    profile_region = 0  # index of the timed region bracketed by cudaProfilerStart/Stop (--profile-region)
+    regions_seen = 0
+
     def __init__(self, dev, world: int):
         self.dev = dev
         self.world = world
@@ -140,12 +149,18 @@ class Timer:
             step()
         self.sync()
         pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        profiled = Timer.profile_region == Timer.regions_seen  # `ncu --profile-from-start off` sees this region only
+        Timer.regions_seen += 1
+        if profiled:
+            torch.cuda.profiler.start()
         for s, e in pairs:
             self.flush_buf.zero_()
             s.record()
             step()
             e.record()
         self.sync()
+        if profiled:
+            torch.cuda.profiler.stop()
         ms = sum(s.elapsed_time(e) for s, e in pairs) / steps
         if self.world > 1:
             import torch.distributed as dist
@@ -628,7 +643,11 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--profile-region", type=int, default=0,
+                    help="which timed region (0 = the headline one) cudaProfilerStart/Stop brackets, for "
+                         "`ncu --profile-from-start off`")
     args = ap.parse_args()
+    Timer.profile_region = args.profile_region
     if args.impl == "reference":
         run_reference(args)
         return
