@@ -52,8 +52,11 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_bf16in_tp": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P],
     "hb200_nvfp4_scaled_matmul_tp": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_float, c_int, _P],
     "hb200_peer_barrier": [_P, _I64, _I64, _P, _P],
+    "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],
+    "hb200_nvfp4_gemv_bf16in_tc": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P, _I64, _P],
+    "hb200_nvfp4_gemv_fp4in_tc": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P, _I64, _P],
 }
-_RESTYPES = {"hb200_error_string": c_char_p}
+_RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64}
 
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None

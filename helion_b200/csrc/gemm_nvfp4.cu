@@ -478,6 +478,7 @@ extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_pa
 namespace hb200 {
 int f16_device_status(int reset);
 int peer_device_status(int reset);
+int gemv_tc_device_status(int reset);
 }
 
 extern "C" int hb200_device_status(int reset) {
@@ -489,5 +490,6 @@ extern "C" int hb200_device_status(int reset) {
   }
   const int w = hb200::f16_device_status(reset);
   const int p = hb200::peer_device_status(reset);
-  return v != 0 ? v : (w != 0 ? w : p);
+  const int t = hb200::gemv_tc_device_status(reset);
+  return v != 0 ? v : (w != 0 ? w : (p != 0 ? p : t));
 }

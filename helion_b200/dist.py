@@ -177,9 +177,18 @@ class TensorParallel:
             raise ValueError("output ring does not match [M, N_local * world] bf16")
         if weight_local.shape[1] * 2 != k:
             raise ValueError("weight and activation disagree on K")
-        _lib.call("hb200_nvfp4_gemv_bf16in_tp", weight_local.data_ptr(), x.data_ptr(), scale_local.data_ptr(), ptrs,
-                  self.world, n_local, k, m, buf.shape[1], self.rank * n_local, float(alpha),
-                  torch.cuda.current_stream(self.device).cuda_stream)
+        from . import ops
+
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        if ops._gemv_path("auto", n_local, k, m) == "tc":
+            need = _lib.load().hb200_nvfp4_gemv_tc_workspace_bytes(n_local, k, m, 4)
+            ws = ops.tc_workspace(self.device, need)
+            _lib.call("hb200_nvfp4_gemv_bf16in_tc", weight_local.data_ptr(), x.data_ptr(), scale_local.data_ptr(), ptrs,
+                      self.world, n_local, k, m, buf.shape[1], self.rank * n_local, float(alpha), ws.data_ptr(),
+                      ws.numel(), stream)
+        else:
+            _lib.call("hb200_nvfp4_gemv_bf16in_tp", weight_local.data_ptr(), x.data_ptr(), scale_local.data_ptr(), ptrs,
+                      self.world, n_local, k, m, buf.shape[1], self.rank * n_local, float(alpha), stream)
         if barrier:
             self.barrier()
         return buf[:m]

@@ -10,6 +10,8 @@ CUDA stream.  There is no CPU or eager fallback: non-CUDA tensors raise.
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 from torch import Tensor
 
@@ -66,47 +68,100 @@ def _check_numel(name: str, t: Tensor, expected: int) -> None:
 
 
 # ------------------------------------------------------------------ custom ops
+# Workspace of the tensor-core GEMV (activation terms, split-K partials, tile counters): one zero-filled
+# buffer per (device, stream), grown on demand.  Calls on one stream are ordered, so they can share it.
+_TC_WORKSPACES: dict[tuple[int, int], Tensor] = {}
+_TC_MIN_WEIGHT_ELEMS = 1 << 21  # below this a launch is latency-bound and the SIMT kernels do as well
+
+
+def tc_workspace(device: torch.device, nbytes: int) -> Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream() or 0)
+    ws = _TC_WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
+        _TC_WORKSPACES[key] = ws
+    return ws
+
+
+def _tc_eligible(n: int, k: int, batch: int) -> bool:
+    return k % 32 == 0 and n >= 128 and 1 <= batch <= 32 and n * k >= _TC_MIN_WEIGHT_ELEMS
+
+
+def _gemv_path(path: str, n: int, k: int, batch: int) -> str:
+    if path == "auto":
+        # One activation row: the SIMT kernel streams as fast as the tensor-core one and takes the bf16
+        # activation exactly.  From two rows on the tensor-core kernel wins (its cost barely grows with rows).
+        return "tc" if batch >= 2 and _tc_eligible(n, k, batch) else "simt"
+    if path not in ("simt", "mma", "tc"):
+        raise ValueError(f"path must be 'auto', 'simt', 'mma' or 'tc'; got {path!r}")
+    return path
+
+
 @torch.library.custom_op("helion_b200::nvfp4_gemv_bf16in", mutates_args=())
-def _gemv_bf16in_op(weight_bytes: Tensor, x: Tensor, weight_scale: Tensor, alpha: float, use_mma: bool) -> Tensor:
+def _gemv_bf16in_op(weight_bytes: Tensor, x: Tensor, weight_scale: Tensor, alpha: float, path: str) -> Tensor:
     _require_cuda(weight_bytes, x, weight_scale)
     n, k_bytes = weight_bytes.shape
     k = k_bytes * 2
     batch = x.numel() // k if k else 1
     out = torch.empty((batch, n), dtype=torch.bfloat16, device=weight_bytes.device)
     if n and batch:
+        path = _gemv_path(path, n, k, batch)
         with torch.cuda.device(weight_bytes.device):
-            _lib.call(
-                "hb200_nvfp4_gemv_bf16in_mma" if use_mma else "hb200_nvfp4_gemv_bf16in",
-                weight_bytes.data_ptr(), x.data_ptr(), weight_scale.data_ptr(), out.data_ptr(),
-                n, k, batch, float(alpha), _stream(),
-            )
+            if path == "tc":
+                need = _lib.load().hb200_nvfp4_gemv_tc_workspace_bytes(n, k, batch, 4)
+                if need < 0:
+                    _lib.check(int(need), "hb200_nvfp4_gemv_tc_workspace_bytes")
+                ws = tc_workspace(weight_bytes.device, need)
+                ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
+                _lib.call(
+                    "hb200_nvfp4_gemv_bf16in_tc", weight_bytes.data_ptr(), x.data_ptr(), weight_scale.data_ptr(), ptrs, 1,
+                    n, k, batch, n, 0, float(alpha), ws.data_ptr(), ws.numel(), _stream(),
+                )
+            else:
+                _lib.call(
+                    "hb200_nvfp4_gemv_bf16in_mma" if path == "mma" else "hb200_nvfp4_gemv_bf16in",
+                    weight_bytes.data_ptr(), x.data_ptr(), weight_scale.data_ptr(), out.data_ptr(),
+                    n, k, batch, float(alpha), _stream(),
+                )
     return out
 
 
 @_gemv_bf16in_op.register_fake
-def _(weight_bytes, x, weight_scale, alpha, use_mma):
+def _(weight_bytes, x, weight_scale, alpha, path):
     k = weight_bytes.shape[1] * 2
     batch = x.numel() // k if k else 1
     return weight_bytes.new_empty((batch, weight_bytes.shape[0]), dtype=torch.bfloat16)
 
 
 @torch.library.custom_op("helion_b200::nvfp4_gemv_fp4in", mutates_args=())
-def _gemv_fp4in_op(weight_bytes: Tensor, x_bytes: Tensor, weight_scale: Tensor, x_scale: Tensor, alpha: float) -> Tensor:
+def _gemv_fp4in_op(weight_bytes: Tensor, x_bytes: Tensor, weight_scale: Tensor, x_scale: Tensor, alpha: float,
+                   path: str) -> Tensor:
     _require_cuda(weight_bytes, x_bytes, weight_scale, x_scale)
     n, k_bytes = weight_bytes.shape
     out = torch.empty((n,), dtype=torch.bfloat16, device=weight_bytes.device)
     if n:
+        path = _gemv_path(path, n, k_bytes * 2, 1)
         with torch.cuda.device(weight_bytes.device):
-            _lib.call(
-                "hb200_nvfp4_gemv_fp4in",
-                weight_bytes.data_ptr(), x_bytes.data_ptr(), weight_scale.data_ptr(), x_scale.data_ptr(),
-                out.data_ptr(), n, k_bytes * 2, float(alpha), _stream(),
-            )
+            if path == "tc":
+                need = _lib.load().hb200_nvfp4_gemv_tc_workspace_bytes(n, k_bytes * 2, 1, 1)
+                if need < 0:
+                    _lib.check(int(need), "hb200_nvfp4_gemv_tc_workspace_bytes")
+                ws = tc_workspace(weight_bytes.device, need)
+                _lib.call(
+                    "hb200_nvfp4_gemv_fp4in_tc", weight_bytes.data_ptr(), x_bytes.data_ptr(), weight_scale.data_ptr(),
+                    x_scale.data_ptr(), out.data_ptr(), n, k_bytes * 2, float(alpha), ws.data_ptr(), ws.numel(), _stream(),
+                )
+            else:
+                _lib.call(
+                    "hb200_nvfp4_gemv_fp4in",
+                    weight_bytes.data_ptr(), x_bytes.data_ptr(), weight_scale.data_ptr(), x_scale.data_ptr(),
+                    out.data_ptr(), n, k_bytes * 2, float(alpha), _stream(),
+                )
     return out
 
 
 @_gemv_fp4in_op.register_fake
-def _(weight_bytes, x_bytes, weight_scale, x_scale, alpha):
+def _(weight_bytes, x_bytes, weight_scale, x_scale, alpha, path):
     return weight_bytes.new_empty((weight_bytes.shape[0],), dtype=torch.bfloat16)
 
 
@@ -230,12 +285,16 @@ def _(a_bytes, b_bytes, scale_a, scale_b, alpha, out_dtype):
 
 # ---------------------------------------------------------------- public entry points
 def nvfp4_gemv_bf16in(
-    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, backend: str | None = None
+    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, backend: str | None = None,
+    path: str = "auto",
 ) -> Tensor:
     """``weight_packed @ x_bf16`` for NVFP4 weights and a BF16 vector; returns bf16 ``[N]``.
 
     Drop-in for ``nvfp4_gemv_bf16in`` (examples/nvfp4_gemv.py:432-476).  ``backend`` is
-    accepted for signature compatibility and ignored: there is one implementation.
+    accepted for signature compatibility and ignored.  ``path`` picks the kernel: ``"simt"`` (bf16 activations
+    taken exactly, fp16 products; what ``"auto"`` uses for a single activation row), ``"tc"`` (tcgen05 on the
+    packed weights, the activation expanded into four NVFP4 residual terms; what ``"auto"`` uses for 2..32
+    rows when K % 32 == 0 and the weight has at least 2M elements) or ``"mma"``.
     """
     _check_contiguous("weight_packed", weight_packed)
     _check_contiguous("x_bf16", x_bf16)
@@ -245,15 +304,17 @@ def nvfp4_gemv_bf16in(
     _check_swizzled_scales("weight_scale", weight_scale, weight_bytes.shape[0], weight_bytes.shape[1] // 8)
     if x_bf16.dtype is not torch.bfloat16:
         raise TypeError(f"x_bf16 must be torch.bfloat16, got {x_bf16.dtype}")
-    out = _gemv_bf16in_op(weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, False)
+    out = _gemv_bf16in_op(weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, path)
     return out.reshape(weight_bytes.shape[0])
 
 
 def nvfp4_gemv_bf16in_batched(
-    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, use_mma: bool | None = None
+    weight_packed: Tensor, x_bf16: Tensor, weight_scale: Tensor, alpha: float = 1.0, *, use_mma: bool | None = None,
+    path: str = "auto",
 ) -> Tensor:
     """Decode-batch extension of :func:`nvfp4_gemv_bf16in`: ``x_bf16`` is ``[M, K]`` with 1 <= M <= 32,
-    the result is bf16 ``[M, N]``.  ``use_mma`` forces the tensor-core formulation for M == 1."""
+    the result is bf16 ``[M, N]``.  ``path`` as in :func:`nvfp4_gemv_bf16in`; ``use_mma=True`` is the same as
+    ``path="mma"`` (warp-level MMA on decoded weights, also for M == 1)."""
     _check_contiguous("weight_packed", weight_packed)
     _check_contiguous("x_bf16", x_bf16)
     weight_bytes = fp4_storage(weight_packed)
@@ -265,14 +326,14 @@ def nvfp4_gemv_bf16in_batched(
     _check_swizzled_scales("weight_scale", weight_scale, weight_bytes.shape[0], weight_bytes.shape[1] // 8)
     if x_bf16.dtype is not torch.bfloat16:
         raise TypeError(f"x_bf16 must be torch.bfloat16, got {x_bf16.dtype}")
-    return _gemv_bf16in_op(
-        weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, bool(use_mma)
-    )
+    if use_mma:
+        path = "mma"
+    return _gemv_bf16in_op(weight_bytes, _aligned(x_bf16), weight_scale.reshape(-1).view(torch.uint8), alpha, path)
 
 
 def nvfp4_gemv_fp4in(
     weight_packed: Tensor, x_packed: Tensor, weight_scale: Tensor, x_scale: Tensor, alpha: float = 1.0,
-    *, backend: str | None = None,
+    *, backend: str | None = None, path: str = "auto",
 ) -> Tensor:
     """``weight_packed @ x_packed`` for NVFP4 weights and an NVFP4 vector; returns bf16 ``[N]``.
 
@@ -289,7 +350,7 @@ def nvfp4_gemv_fp4in(
     _check_swizzled_scales("x_scale", x_scale, 1, scale_cols)
     return _gemv_fp4in_op(
         weight_bytes, _aligned(x_bytes), weight_scale.reshape(-1).view(torch.uint8),
-        x_scale.reshape(-1).view(torch.uint8), alpha,
+        x_scale.reshape(-1).view(torch.uint8), alpha, path,
     )
 
 
@@ -388,7 +449,7 @@ def nvfp4_w4a16_matmul(A: Tensor, B_packed: Tensor, weight_scale: Tensor, alpha:
     out = torch.empty(m, n, dtype=torch.bfloat16, device=A.device)
     for r0 in range(0, m, 32):
         r1 = min(m, r0 + 32)
-        out[r0:r1] = _gemv_bf16in_op(w, _aligned(a[r0:r1]), sc, alpha, r1 - r0 == 1 and False)
+        out[r0:r1] = _gemv_bf16in_op(w, _aligned(a[r0:r1]), sc, alpha, "auto")
     return out
 
 

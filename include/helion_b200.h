@@ -196,6 +196,28 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* ---- tensor-core GEMV / decode-batch skinny GEMM ----
+ *
+ * Same operators as hb200_nvfp4_gemv_bf16in / _fp4in (examples/nvfp4_gemv.py:432-525, batch rows 1..32 as in
+ * the decode sweep), computed with tcgen05.mma on the packed weights so that no thread decodes a weight
+ * byte.  bf16 activations are expanded into four NVFP4 residual terms first (error below 1e-3 of a
+ * 16-element block's maximum, checked against the fp32 reference in the tests); NVFP4 activations are
+ * used as they are.  Needs K % 32 == 0 (HB200_ERR_UNSUPPORTED otherwise: use the entry points above).
+ *
+ * `workspace` is caller-owned device memory of at least hb200_nvfp4_gemv_tc_workspace_bytes(...) bytes,
+ * 256-byte aligned, zero-filled once before its first use (the kernels leave the part that must be zero
+ * at zero again).  Calls that share a workspace must not overlap (same stream, or ordered by events);
+ * HB200_ERR_WORKSPACE if it is too small.  out_ptrs / world / n_total / col0 as in the tensor-parallel
+ * forms below; for a single GPU pass one pointer, world = 1, n_total = n, col0 = 0. */
+int64_t hb200_nvfp4_gemv_tc_workspace_bytes(int64_t n, int64_t k, int64_t batch, int64_t terms);
+int hb200_nvfp4_gemv_bf16in_tc(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                               void* const* out_ptrs, int64_t world, int64_t n, int64_t k, int64_t batch,
+                               int64_t n_total, int64_t col0, float alpha, void* workspace,
+                               int64_t workspace_bytes, void* stream);
+int hb200_nvfp4_gemv_fp4in_tc(const void* weight_packed, const void* x_packed, const void* weight_scale,
+                              const void* x_scale, void* out_bf16, int64_t n, int64_t k, float alpha,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- tensor-parallel forms (one process per GPU, outputs in symmetric memory) ----
  *
  * The reference's distributed examples push results to peers from inside the kernel through symmetric

@@ -111,7 +111,7 @@ def test_custom_ops_registered_with_fake_impls():
         w = torch.empty(64, 128, dtype=torch.uint8, device="cuda")
         x = torch.empty(2, 256, dtype=torch.bfloat16, device="cuda")
         s = torch.empty(2048, dtype=torch.uint8, device="cuda")
-        y = torch.ops.helion_b200.nvfp4_gemv_bf16in(w, x, s, 1.0, False)
+        y = torch.ops.helion_b200.nvfp4_gemv_bf16in(w, x, s, 1.0, "auto")
         assert y.shape == (2, 64) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
         y = torch.ops.helion_b200.nvfp4_gemv_fp4in(w, torch.empty(128, dtype=torch.uint8, device="cuda"), s, s, 1.0)
         assert y.shape == (64,)
