@@ -113,7 +113,7 @@ def test_custom_ops_registered_with_fake_impls():
         s = torch.empty(2048, dtype=torch.uint8, device="cuda")
         y = torch.ops.helion_b200.nvfp4_gemv_bf16in(w, x, s, 1.0, "auto")
         assert y.shape == (2, 64) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
-        y = torch.ops.helion_b200.nvfp4_gemv_fp4in(w, torch.empty(128, dtype=torch.uint8, device="cuda"), s, s, 1.0)
+        y = torch.ops.helion_b200.nvfp4_gemv_fp4in(w, torch.empty(128, dtype=torch.uint8, device="cuda"), s, s, 1.0, "auto")
         assert y.shape == (64,)
         c, sc, g = torch.ops.helion_b200.nvfp4_quantize(x, None)
         assert c.shape == (2, 128) and sc.numel() == 128 * 16 and g.shape == (2,)
