@@ -443,7 +443,12 @@ expand_terms_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ c
     }
     const int rowi = b * TERMS + t;
     *reinterpret_cast<uint2*>(codes + int64_t(rowi) * k_bytes + int64_t(blk) * 8) = make_uint2(packed[0], packed[1]);
-    sf[(int64_t(blk >> 2)) * kAtomBytes + (rowi & 31) * 16 + (rowi >> 5) * 4 + (blk & 3)] = uint8_t(sbyte);
+    uint8_t* sf_row = sf + (int64_t(blk >> 2)) * kAtomBytes + (rowi & 31) * 16 + (rowi >> 5) * 4;
+    sf_row[blk & 3] = uint8_t(sbyte);
+    // the scale columns that pad the last 64-element atom multiply zero codes: they must be finite (the
+    // workspace is reused between shapes and may hold any bytes there, the e4m3 NaN patterns included)
+    if (blk == k / 16 - 1)
+      for (int c = (blk & 3) + 1; c < 4; ++c) sf_row[c] = 0;
   }
 }
 

@@ -136,3 +136,24 @@ def test_workspace_too_small_is_rejected():
     assert rc == 0 and device_status_ok()
     ref = O.nvfp4_gemm_bf16in(packed, x, scales, gs)
     assert float(rel_err(out, ref).max()) <= REL_TOL
+
+
+def test_dirty_workspace_outside_the_counters_is_harmless():
+    """Only the counter region has to be zero: everything else may hold any bytes from earlier shapes."""
+    n, k, batch = 1000, 2080, 3  # K ends inside a 64-element scale atom: its padding columns multiply zero codes
+    packed, scales, gs, x = make_case(n, k, batch, seed=21)
+    w, s, xd = packed.to(DEV), scales.to(DEV).view(torch.uint8), x.to(DEV)
+    lib = _lib.load()
+    need = lib.hb200_nvfp4_gemv_tc_workspace_bytes(n, k, batch, 4)
+    outs = []
+    for fill in (0x00, 0xFF, 0x7F):
+        ws = torch.full((need,), fill, dtype=torch.uint8, device=DEV)
+        ws[: 4 * 4096] = 0
+        out = torch.empty(batch, n, dtype=torch.bfloat16, device=DEV)
+        ptrs = (ctypes.c_void_p * 1)(out.data_ptr())
+        rc = lib.hb200_nvfp4_gemv_bf16in_tc(w.data_ptr(), xd.data_ptr(), s.data_ptr(), ptrs, 1, n, k, batch, n, 0, gs,
+                                            ws.data_ptr(), need, None)
+        assert rc == 0 and device_status_ok()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert float(rel_err(outs[0], O.nvfp4_gemm_bf16in(packed, x, scales, gs)).max()) <= REL_TOL
