@@ -24,6 +24,7 @@ HB200_ERR_UNSUPPORTED = -2
 HB200_ERR_CUDA = -3
 HB200_ERR_DEVICE_TIMEOUT = -4
 HB200_ERR_WORKSPACE = -5
+HB200_ERR_SCRATCH_LIMIT = -6
 ABI_VERSION = 1
 
 _P = c_void_p
@@ -55,6 +56,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],
     "hb200_nvfp4_gemv_bf16in_tc": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P, _I64, _P],
     "hb200_nvfp4_gemv_fp4in_tc": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P, _I64, _P],
+    "hb200_nvfp4_gemv_bf16in_tc_builtin_scratch": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64}
 

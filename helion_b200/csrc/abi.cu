@@ -11,6 +11,9 @@ extern "C" const char* hb200_error_string(int code) {
     case HB200_ERR_CUDA: return "CUDA runtime call failed";
     case HB200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
     case HB200_ERR_WORKSPACE: return "workspace missing or too small";
+    case HB200_ERR_SCRATCH_LIMIT:
+      return "shape exceeds the 8 MiB built-in scratch (at most 8 activation rows and K <= 65536 always fit); "
+             "use the entry point that takes a caller workspace";
     default: return "unknown error code";
   }
 }

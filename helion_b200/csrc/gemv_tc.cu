@@ -29,6 +29,8 @@
 #include "tcgen05.cuh"
 #include "gemm_common.cuh"
 
+#include <mutex>
+
 namespace hb200 {
 
 __device__ int g_device_status_gemv_tc = 0;
@@ -640,4 +642,68 @@ extern "C" int hb200_nvfp4_gemv_fp4in_tc(const void* weight_packed, const void* 
     return HB200_ERR_CUDA;
   return run_tc(weight_packed, weight_scale, ws + p.off_codes, static_cast<const uint8_t*>(x_scale), nullptr, o, n, k, 1, 1,
                 alpha, p, ws, s);
+}
+
+// ------------------------------------------------------------------ built-in scratch
+// hb200_nvfp4_gemv_bf16in_tc for callers that cannot hand over a workspace: the scratch is this array in
+// the library's own device image, one per device, so the call allocates nothing, neither here nor in the
+// caller.  8 MiB holds every shape with at most 8 activation rows and K <= 65536; larger requests are
+// refused with HB200_ERR_SCRATCH_LIMIT.
+namespace hb200 {
+namespace {
+
+constexpr size_t kBuiltinScratchBytes = size_t(8) << 20;
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+std::mutex g_builtin_mutex;
+void* g_builtin_ptr[kMaxDevices] = {};  // device address of g_builtin_scratch on every device seen so far
+
+// First call on a device (that device current): look the array's address up and clear the part that has to
+// start at zero, the tile arrival counters, on the caller's stream.  Later calls only read the cached address.
+int builtin_scratch(cudaStream_t stream, void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HB200_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return HB200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_builtin_mutex);
+  if (g_builtin_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_builtin_scratch) != cudaSuccess || ptr == nullptr)
+      return HB200_ERR_CUDA;
+    if (cudaMemsetAsync(ptr, 0, size_t(kMaxRowTiles) * 4, stream) != cudaSuccess) return HB200_ERR_CUDA;
+    g_builtin_ptr[dev] = ptr;
+  }
+  *out = g_builtin_ptr[dev];
+  return HB200_OK;
+}
+
+}  // namespace
+}  // namespace hb200
+
+extern "C" int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_packed, const void* x_bf16,
+                                                          const void* weight_scale, void* out_bf16, int64_t n,
+                                                          int64_t k, int64_t batch, float alpha, void* stream) {
+  using namespace hb200;
+  if (!out_bf16) return HB200_ERR_INVALID_ARGUMENT;
+  const int rc = check_common(weight_packed, x_bf16, weight_scale, n, k, batch);
+  if (rc != HB200_OK) return rc;
+  TcPlan p;
+  if (!make_plan(n, k, batch, 4, &p)) return HB200_ERR_UNSUPPORTED;
+  if (p.bytes > kBuiltinScratchBytes) return HB200_ERR_SCRATCH_LIMIT;  // more rows or a longer K than the array holds
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* scratch = nullptr;
+  const int rs = builtin_scratch(s, &scratch);
+  if (rs != HB200_OK) return rs;
+  uint8_t* ws = static_cast<uint8_t*>(scratch);
+  OutSpec o{};
+  o.ptr[0] = static_cast<__nv_bfloat16*>(out_bf16);
+  o.count = 1;
+  o.ld = n;
+  const dim3 egrid(unsigned(ceil_div64(k / 16, kExpandThreads)), unsigned(batch), 1);
+  expand_terms_kernel<4><<<egrid, kExpandThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), ws + p.off_codes,
+                                                          ws + p.off_sf, reinterpret_cast<float*>(ws + p.off_cs), int(k));
+  if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
+  return run_tc(weight_packed, weight_scale, ws + p.off_codes, ws + p.off_sf, reinterpret_cast<const float*>(ws + p.off_cs),
+                o, n, k, batch, 4, alpha, p, ws, s);
 }

@@ -33,6 +33,7 @@ extern "C" {
 #define HB200_ERR_CUDA (-3)             /* a CUDA runtime/driver call failed     */
 #define HB200_ERR_DEVICE_TIMEOUT (-4)   /* a bounded device-side wait ran out    */
 #define HB200_ERR_WORKSPACE (-5)        /* caller workspace missing or too small */
+#define HB200_ERR_SCRATCH_LIMIT (-6)    /* shape needs more than the library's built-in scratch */
 
 #define HB200_ABI_VERSION 1
 
@@ -217,6 +218,20 @@ int hb200_nvfp4_gemv_bf16in_tc(const void* weight_packed, const void* x_bf16, co
 int hb200_nvfp4_gemv_fp4in_tc(const void* weight_packed, const void* x_packed, const void* weight_scale,
                               const void* x_scale, void* out_bf16, int64_t n, int64_t k, float alpha,
                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* hb200_nvfp4_gemv_bf16in_tc for one GPU without a workspace argument, for callers that have no way to
+ * obtain device memory at the point of the call.  The scratch is an 8 MiB array inside the library's device
+ * image (one per device); this entry point and everything it calls allocate and free nothing, on the
+ * device or through the caller's framework.  Limits: at most 8 activation rows and K <= 65536 always fit;
+ * a shape whose workspace would exceed 8 MiB is refused with HB200_ERR_SCRATCH_LIMIT before anything runs.
+ * The first call on a device (with that device current) looks the array up and clears its arrival counters
+ * on `stream`: make that call during start-up, before any stream capture.  Calls on one device share the
+ * array, so they must not overlap: issue them on one stream or order them with events, as two overlapping
+ * calls would corrupt each other's partial sums.  Results are bit-identical to hb200_nvfp4_gemv_bf16in_tc.
+ * No counterpart in the reference, whose kernels get their temporaries from torch's caching allocator. */
+int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_packed, const void* x_bf16,
+                                               const void* weight_scale, void* out_bf16, int64_t n, int64_t k,
+                                               int64_t batch, float alpha, void* stream);
 
 /* ---- tensor-parallel forms (one process per GPU, outputs in symmetric memory) ----
  *
