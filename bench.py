@@ -548,7 +548,8 @@ def wl_moe(args, dev, rank, world, timer):
         return M.GroupedNvfp4Weight(codes.reshape(e_local, n, k // 2), scales.reshape(e_local, per),
                                     torch.full((e_local,), g, dtype=torch.float32, device=dev))
 
-    w_gu = bundle(2 * c["inter"], c["hidden"], 3000 + rank)
+    # gate/up rows interleaved in blocks of 128: the first expert GEMM applies SiLU-mul in its epilogue
+    w_gu = M.interleave_gate_up(bundle(2 * c["inter"], c["hidden"], 3000 + rank))
     w_d = bundle(c["hidden"], c["inter"], 3500 + rank)
     g = torch.Generator().manual_seed(3 + 97 * rank)
     host_x = torch.randn(t_local, c["hidden"], generator=g).to(torch.bfloat16).pin_memory()

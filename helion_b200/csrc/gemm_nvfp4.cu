@@ -57,6 +57,10 @@ struct GemmArgs {
   int64_t sfb_group_stride;
   const float* row_scale;    // optional fp32 factor per row of A
   const float* group_alpha;  // optional fp32 factor per group
+  // SiLU-mul epilogue (grouped bf16 only, BLOCK_N = 256): the 256 columns of a tile are 128 gate columns
+  // followed by the 128 up columns of the same outputs; the kernel writes y = bf16(silu(gate) * up)
+  // [rows, n / 2] and folds every row's max |y| into row_amax (fp32 bits, compared as integers).
+  float* row_amax;
 };
 
 struct Tile {
@@ -302,12 +306,52 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BLOCK_N + cgroup * CW;
       if constexpr (CW >= 32) {
         uint32_t r[CW / 32][32];
+        bool silu = false;
+        if constexpr (BLOCK_N == 256 && std::is_same<OutT, __nv_bfloat16>::value) silu = g.row_amax != nullptr;
+        if (silu) {
+          // 32 gate columns and the 32 up columns of the same outputs
+          const uint32_t tbase = taddr - cgroup * CW;
+          tmem_ld_32x32b_x32(tbase + cgroup * 32, r[0]);
+          tmem_ld_32x32b_x32(tbase + 128 + cgroup * 32, r[CW / 32 - 1]);
+        } else {
 #pragma unroll
-        for (int c = 0; c < CW / 32; ++c) tmem_ld_32x32b_x32(taddr + c * 32, r[c]);
+          for (int c = 0; c < CW / 32; ++c) tmem_ld_32x32b_x32(taddr + c * 32, r[c]);
+        }
         tmem_ld_wait();
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        if constexpr (BLOCK_N == 256 && std::is_same<OutT, __nv_bfloat16>::value) {
+          if (silu) {
+            if (row_ok) {
+              uint32_t packed[16];
+              float amax = 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float y[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  // gate and up rounded to bf16 first, as a bf16 activation pipeline holds them
+                  const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[0][2 * j + h]) * alpha));
+                  const float uv =
+                      __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[CW / 32 - 1][2 * j + h]) * alpha));
+                  y[h] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
+                }
+                const __nv_bfloat162 p = __floats2bfloat162_rn(y[0], y[1]);
+                packed[j] = *reinterpret_cast<const uint32_t*>(&p);
+                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(packed[j] << 16)),
+                                         fabsf(__uint_as_float(packed[j] & 0xffff0000u))));
+              }
+              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + int64_t(row) * g.ldc + n_blk * 128 + cgroup * 32;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                *reinterpret_cast<uint4*>(dst + v * 8) =
+                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+              atomicMax(reinterpret_cast<int*>(g.row_amax + row), __float_as_int(amax));
+            }
+            continue;
+          }
+        }
 #pragma unroll
         for (int c = 0; c < CW / 32; ++c) {
           const int col = n_blk * BLOCK_N + cgroup * CW + c * 32;
@@ -405,7 +449,7 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
     if (rc != HB200_ERR_UNSUPPORTED) return rc;
   }
   GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
-             int(m), int(n), int(k), alpha, 0, 0, nullptr, 0, nullptr, nullptr};
+             int(m), int(n), int(k), alpha, 0, 0, nullptr, 0, nullptr, nullptr, nullptr};
   switch (out_dtype) {
     case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, 1, s);
     case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, 1, s);
@@ -464,13 +508,47 @@ extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_pa
   const int64_t sfb_stride = round_up64(n, 128) * round_up64(k / 16, 4);
   GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), out, ldc,
              int(max_m_tiles * 128), int(n), int(k), alpha, int(max_m_tiles), 0,
-             reinterpret_cast<const int2*>(tile_info), sfb_stride, row_scale, group_alpha};
+             reinterpret_cast<const int2*>(tile_info), sfb_stride, row_scale, group_alpha, nullptr};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (out_dtype) {
     case 0: return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, int(groups), s);
     case 1: return dispatch_gemm<__half>(a_packed, b_packed, g, int(groups), s);
     default: return dispatch_gemm<float>(a_packed, b_packed, g, int(groups), s);
   }
+}
+
+// The first expert GEMM of an NVFP4 MoE layer with SiLU-mul in the epilogue.  The weight rows are gate/up
+// interleaved in blocks of 128 (rows [256 j, 256 j + 128) = gate outputs [128 j, 128 j + 128), the next 128
+// rows the up rows of the same outputs), n counts all of them; y = bf16(silu(gate) * up) is written to
+// y_out [rows, n / 2] (leading dimension ldy) and row_amax[r] receives max |y[r, :]| (cleared here first,
+// on the stream).  Same value, bit for bit, as hb200_nvfp4_grouped_matmul followed by the SiLU-mul of
+// hb200_nvfp4_quantize_rows.  No counterpart in the reference (its MoE example is a bf16 top-1 GEMM,
+// examples/moe_matmul_ogs.py:31-85); the gate-first convention is silu_and_mul_per_block_quant's.
+extern "C" int hb200_nvfp4_grouped_matmul_silu(const void* a_packed, const void* b_packed, const void* scale_a,
+                                               const void* scale_b, void* y_out, float* row_amax,
+                                               const int32_t* tile_info, int64_t max_m_tiles, int64_t n, int64_t k,
+                                               int64_t groups, int64_t ldy, const float* row_scale,
+                                               const float* group_alpha, float alpha, void* stream) {
+  using namespace hb200;
+  if (!a_packed || !b_packed || !scale_a || !scale_b || !y_out || !row_amax || !tile_info)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles < 0 || n <= 0 || k <= 0 || groups <= 0 || (n % 256) != 0 || ldy < n / 2 || (ldy % 8) != 0)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if ((k % 16) != 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a_packed) % 16 || reinterpret_cast<uintptr_t>(b_packed) % 16 ||
+      reinterpret_cast<uintptr_t>(scale_a) % 16 || reinterpret_cast<uintptr_t>(scale_b) % 16 ||
+      reinterpret_cast<uintptr_t>(tile_info) % 8 || reinterpret_cast<uintptr_t>(y_out) % 16)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles == 0) return HB200_OK;
+  if ((k % 32) != 0) return HB200_ERR_UNSUPPORTED;
+  if (max_m_tiles * 128 > 0x7fffff00 || n * groups > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(row_amax, 0, size_t(max_m_tiles) * 128 * sizeof(float), s) != cudaSuccess) return HB200_ERR_CUDA;
+  const int64_t sfb_stride = round_up64(n, 128) * round_up64(k / 16, 4);
+  GemmArgs g{static_cast<const uint8_t*>(scale_a), static_cast<const uint8_t*>(scale_b), y_out, ldy,
+             int(max_m_tiles * 128), int(n), int(k), alpha, int(max_m_tiles), 0,
+             reinterpret_cast<const int2*>(tile_info), sfb_stride, row_scale, group_alpha, row_amax};
+  return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, int(groups), s);
 }
 
 // Reads (and optionally clears) the sticky device status set by kernels whose

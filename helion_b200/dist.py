@@ -298,8 +298,12 @@ def make_nvfp4_expert_fn(w_gate_up, w_down) -> ExpertFn:
             return rows.new_empty(0, w_down.n)
         sched = M.build_schedule(local_expert.reshape(-1, 1), w_gate_up.experts)
         a1, sf1, g1 = M._quantize_rows(rows.contiguous(), w_gate_up.k, sched, 1, None, False, gather=True)
-        h1 = M.grouped_matmul(a1, sf1, w_gate_up, sched, g1)
-        a2, sf2, g2 = M._quantize_rows(h1, w_down.k, sched, 1, None, True, gather=False)
+        if w_gate_up.gate_up_interleaved:
+            y, row_amax = M.grouped_matmul_silu(a1, sf1, w_gate_up, sched, g1)
+            a2, sf2, g2 = M._quantize_rows_amax(y, row_amax, w_down.k, sched, None)
+        else:
+            h1 = M.grouped_matmul(a1, sf1, w_gate_up, sched, g1)
+            a2, sf2, g2 = M._quantize_rows(h1, w_down.k, sched, 1, None, True, gather=False)
         o = M.grouped_matmul(a2, sf2, w_down, sched, g2)
         return o[sched.row_of_pair.long()]
 

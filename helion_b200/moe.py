@@ -38,6 +38,9 @@ class GroupedNvfp4Weight:
     packed: Tensor
     scales: Tensor
     global_scale: Tensor
+    # rows interleave gate and up in blocks of 128 (see interleave_gate_up); lets the first expert GEMM
+    # apply SiLU-mul in its epilogue
+    gate_up_interleaved: bool = False
 
     @property
     def experts(self) -> int:
@@ -67,6 +70,23 @@ def quantize_expert_weights(w: Tensor) -> GroupedNvfp4Weight:
         c, s, _ = nvfp4_quantize(wb, g)
         packed[i], scales[i], gs[i] = c, s.view(torch.uint8), g[0]
     return GroupedNvfp4Weight(packed, scales.view(torch.float8_e4m3fn), gs)
+
+
+def interleave_gate_up(w: GroupedNvfp4Weight) -> GroupedNvfp4Weight:
+    """Reorder the rows of a gate||up weight ``[E, 2I, K]`` (gate rows first, as the reference's
+    silu_and_mul kernels expect) into blocks of 128 gate rows followed by the 128 up rows of the same
+    outputs, codes and scale tiles alike (a 128-row block is one scale row-tile, so whole tiles move)."""
+    if w.gate_up_interleaved:
+        return w
+    e, n, kb = w.packed.shape
+    inter = n // 2
+    if n % 256:
+        raise ValueError(f"gate||up rows ({n}) must be a multiple of 256 to interleave in blocks of 128")
+    packed = w.packed.view(e, 2, inter // 128, 128, kb).permute(0, 2, 1, 3, 4).reshape(e, n, kb).contiguous()
+    tile_bytes = w.scales.numel() // (e * (n // 128))
+    scales = (w.scales.view(torch.uint8).view(e, 2, inter // 128, tile_bytes).permute(0, 2, 1, 3)
+              .reshape(e, -1).contiguous().view(torch.float8_e4m3fn))
+    return GroupedNvfp4Weight(packed, scales, w.global_scale, True)
 
 
 def route_top_k(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
@@ -168,6 +188,40 @@ def grouped_matmul(a_codes: Tensor, a_scales: Tensor, w: GroupedNvfp4Weight, sch
     return out
 
 
+def grouped_matmul_silu(a_codes: Tensor, a_scales: Tensor, w: GroupedNvfp4Weight, sched: MoeSchedule,
+                        row_scale: Tensor | None) -> tuple[Tensor, Tensor]:
+    """First expert GEMM with SiLU-mul in the epilogue (``w`` gate/up interleaved): returns
+    ``y = bf16(silu(gate) * up) [rows, N/2]`` and every row's ``max |y|``."""
+    if not w.gate_up_interleaved:
+        raise ValueError("the SiLU-mul epilogue needs a gate/up weight interleaved with interleave_gate_up()")
+    rows = sched.max_tiles * 128
+    y = torch.empty(rows, w.n // 2, dtype=torch.bfloat16, device=a_codes.device)
+    row_amax = torch.empty(rows, dtype=torch.float32, device=a_codes.device)
+    with torch.cuda.device(a_codes.device):
+        _lib.call(
+            "hb200_nvfp4_grouped_matmul_silu", a_codes.data_ptr(), w.packed.data_ptr(), a_scales.data_ptr(),
+            w.scales.data_ptr(), y.data_ptr(), row_amax.data_ptr(), sched.tile_info.data_ptr(), sched.max_tiles, w.n,
+            w.k, w.experts, w.n // 2, None if row_scale is None else row_scale.data_ptr(),
+            w.global_scale.data_ptr(), 1.0, _stream(),
+        )
+    return y, row_amax
+
+
+def _quantize_rows_amax(y: Tensor, row_amax: Tensor, k: int, sched: MoeSchedule, item_scale: Tensor | None):
+    rows = sched.max_tiles * 128
+    dev = y.device
+    codes = torch.empty(rows, k // 2, dtype=torch.uint8, device=dev)
+    scales = torch.empty(swizzled_scale_numel(rows, k // 16), dtype=torch.uint8, device=dev)
+    gscale = torch.zeros(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call(
+            "hb200_nvfp4_quantize_rows_amax", y.data_ptr(), codes.data_ptr(), scales.data_ptr(), gscale.data_ptr(),
+            row_amax.data_ptr(), sched.sorted_pairs.numel(), k, y.stride(0), sched.row_of_sorted.data_ptr(),
+            None if item_scale is None else item_scale.data_ptr(), _stream(),
+        )
+    return codes, scales, gscale
+
+
 def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNvfp4Weight,
               w_down: GroupedNvfp4Weight) -> Tensor:
     """NVFP4 MoE layer: ``x [T, H]`` bf16, ``router_logits [T, E]`` -> bf16 ``[T, H]``."""
@@ -184,8 +238,13 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
     # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
     w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()
     a1, sf1, g1 = _quantize_and_gather(x, sched, top_k)
-    h1 = grouped_matmul(a1, sf1, w_gate_up, sched, g1)
-    a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, w_sorted, True, gather=False)
+    if w_gate_up.gate_up_interleaved:
+        # SiLU-mul in the GEMM's epilogue: the [rows, 2I] intermediate never reaches memory
+        y, row_amax = grouped_matmul_silu(a1, sf1, w_gate_up, sched, g1)
+        a2, sf2, g2 = _quantize_rows_amax(y, row_amax, inter, sched, w_sorted)
+    else:
+        h1 = grouped_matmul(a1, sf1, w_gate_up, sched, g1)
+        a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, w_sorted, True, gather=False)
     o = grouped_matmul(a2, sf2, w_down, sched, g2)
     out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):

@@ -197,6 +197,27 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* First expert GEMM of an NVFP4 MoE layer with the SiLU-mul in its epilogue (arguments as
+ * hb200_nvfp4_grouped_matmul).  b_packed holds, per expert, n rows that interleave gate and up in blocks of
+ * 128: rows [256 j, 256 j + 128) are gate outputs [128 j, 128 j + 128), rows [256 j + 128, 256 j + 256) the up
+ * rows of the same outputs (n % 256 == 0).  Writes y = bf16(silu(gate) * up) to y_out [rows, n / 2] (leading
+ * dimension ldy) and max |y[r, :]| to row_amax[r] (fp32 [max_m_tiles * 128], cleared by this call on the
+ * stream).  Bit-identical to hb200_nvfp4_grouped_matmul + the silu_mul form of hb200_nvfp4_quantize_rows; it
+ * saves writing and re-reading the [rows, n] intermediate.  The reference has no NVFP4 MoE
+ * (examples/moe_matmul_ogs.py:31-85 is a bf16 top-1 GEMM); gate-first as in
+ * pretuned_kernels/silu_and_mul_per_block_quant/silu_and_mul_per_block_quant.py:97-105. */
+int hb200_nvfp4_grouped_matmul_silu(const void* a_packed, const void* b_packed, const void* scale_a,
+                                    const void* scale_b, void* y_out, float* row_amax, const int32_t* tile_info,
+                                    int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups, int64_t ldy,
+                                    const float* row_scale, const float* group_alpha, float alpha, void* stream);
+
+/* Per-token NVFP4 quantisation of rows whose maxima are already known (row_amax from the call above): row
+ * r = row_idx[i] (i when null) of x [*, ldx] -> codes, swizzled scales, global_scale[r] = row_amax[r] / (6 * 448)
+ * (times item_scale[i] in the stored copy).  Same codes and scales as hb200_nvfp4_quantize_rows. */
+int hb200_nvfp4_quantize_rows_amax(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
+                                   const float* row_amax, int64_t items, int64_t k, int64_t ldx,
+                                   const int32_t* row_idx, const float* item_scale, void* stream);
+
 /* ---- tensor-core GEMV / decode-batch skinny GEMM ----
  *
  * Same operators as hb200_nvfp4_gemv_bf16in / _fp4in (examples/nvfp4_gemv.py:432-525, batch rows 1..32 as in

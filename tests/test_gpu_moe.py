@@ -91,8 +91,9 @@ def test_grouped_matmul_against_oracle():
     assert rel_err(out.cpu()[rows], ref) <= 1e-4
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("t,h,inter,e,k", [(64, 256, 128, 8, 2), (300, 512, 384, 16, 4), (128, 256, 256, 4, 1)])
-def test_moe_layer_against_oracle(t, h, inter, e, k):
+def test_moe_layer_against_oracle(t, h, inter, e, k, interleaved):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(t, h, generator=g).to(torch.bfloat16)
     logits = torch.randn(t, e, generator=g)
@@ -101,6 +102,8 @@ def test_moe_layer_against_oracle(t, h, inter, e, k):
     gp, gsc, gg, gu_bundle = oracle_weights(w_gu)
     dp, dsc, dg, d_bundle = oracle_weights(w_d)
     ref = O.nvfp4_moe(x, logits, k, gp, gsc, gg, dp, dsc, dg)
+    if interleaved:  # SiLU-mul inside the first GEMM's epilogue
+        gu_bundle = M.interleave_gate_up(gu_bundle)
     y = M.nvfp4_moe(x.to(DEV), logits.to(DEV), k, gu_bundle, d_bundle)
     torch.cuda.synchronize()
     assert _lib.load().hb200_device_status(1) == 0
@@ -112,6 +115,31 @@ def test_moe_layer_against_oracle(t, h, inter, e, k):
     assert rel_err(y, ref) <= 2e-2
     yc, rc = y.float().cpu(), ref.float()
     assert float((yc - rc).pow(2).mean().sqrt() / rc.pow(2).mean().sqrt()) <= 5e-3
+
+
+def test_silu_epilogue_is_bit_identical_to_the_two_kernel_form():
+    t, h, inter, e, k = 512, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16).to(DEV)
+    logits = torch.randn(t, e, generator=g).to(DEV)
+    w_gu = M.quantize_expert_weights((torch.randn(e, 2 * inter, h, generator=g) * 0.02).to(DEV))
+    w_d = M.quantize_expert_weights((torch.randn(e, h, inter, generator=g) * 0.02).to(DEV))
+    plain = M.nvfp4_moe(x, logits, k, w_gu, w_d)
+    fused = M.nvfp4_moe(x, logits, k, M.interleave_gate_up(w_gu), w_d)
+    torch.cuda.synchronize()
+    assert _lib.load().hb200_device_status(1) == 0
+    assert torch.equal(plain, fused)
+    # and the pieces: y and the row maxima against the SiLU-mul of the quantiser kernel
+    _, experts = M.route_top_k(logits, k)
+    sched = M.build_schedule(experts, e)
+    a1, sf1, g1 = M._quantize_and_gather(x, sched, k)
+    h1 = M.grouped_matmul(a1, sf1, w_gu, sched, g1)
+    y, amax = M.grouped_matmul_silu(a1, sf1, M.interleave_gate_up(w_gu), sched, g1)
+    rows = sched.row_of_pair.long()
+    hg, hu = h1[rows, :inter].float(), h1[rows, inter:].float()
+    want = ((hg / (1.0 + torch.exp(-hg))) * hu).to(torch.bfloat16)
+    assert torch.equal(y[rows], want)
+    assert torch.equal(amax[rows], want.float().abs().amax(dim=1))
 
 
 def test_device_weight_quantiser_matches_oracle():
