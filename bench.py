@@ -408,8 +408,8 @@ def wl_gemv(args, dev, rank, world, timer):
     def one(name, x):
         c, s, g, n, k = mats[name]
         if batch == 1:
-            return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g).reshape(1, -1)
-        return hb.nvfp4_gemv_bf16in_batched(c, x, s, g)
+            return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g, path=args.path).reshape(1, -1)
+        return hb.nvfp4_gemv_bf16in_batched(c, x, s, g, path=args.path)
 
     tp = None
     rings = {}
@@ -471,7 +471,7 @@ def wl_gemv(args, dev, rank, world, timer):
                 roofline=roof, parity=parity, extra={"per_matrix": per_matrix, **extra},
                 dtype="fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
                 config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
-                        "batch": batch, "parallelism": f"column-tp{world}" if world > 1 else "single",
+                        "batch": batch, "path": args.path, "parallelism": f"column-tp{world}" if world > 1 else "single",
                         "l2": "flushed between steps; 481 MB of weights per step", "bytes_per_step": layer_bytes})
 
 
@@ -644,6 +644,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "mma", "tc"],
+                    help="GEMV kernel family (gemv workload): auto = SIMT for one row, tensor cores for 2..32")
     ap.add_argument("--profile-region", type=int, default=0,
                     help="which timed region (0 = the headline one) cudaProfilerStart/Stop brackets, for "
                          "`ncu --profile-from-start off`")

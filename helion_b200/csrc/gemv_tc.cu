@@ -137,6 +137,11 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Kernels queued behind this one as programmatic dependents (the next call's expansion and, behind it, its
+  // GEMV) may be scheduled from now on.  They become eligible only once every CTA of this grid has got here,
+  // i.e. is resident, so they can only take what this grid's CTAs free when they exit; and they wait for
+  // this grid's completion (griddepcontrol.wait) before they touch anything it uses.
+  if (threadIdx.x == 0) griddep_launch_dependents();
 
   // activation terms and their scales of K block kb into stage s (the stage's barrier already expects the bytes)
   auto issue_x = [&](uint32_t s, int kb) {
@@ -379,8 +384,11 @@ __global__ void __launch_bounds__(kExpandThreads)
 expand_terms_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
                     float* __restrict__ col_scale, int k) {
   __shared__ float red[kExpandThreads / 32];
-  // the GEMV that consumes the terms may start its prologue and its weight prefetch now
+  // the GEMV that consumes the terms may start its prologue and its weight prefetch now; this kernel itself
+  // must not overwrite the terms before the GEMV of the previous call (its prerequisite when launched as a
+  // programmatic dependent; a no-op otherwise) has finished reading them
   griddep_launch_dependents();
+  griddep_wait();
   const int b = blockIdx.y, tid = threadIdx.x;
   const __nv_bfloat16* xr = x + int64_t(b) * k;
 
@@ -464,6 +472,24 @@ int sm_count_tc() {
     cached = n;
   }
   return cached;
+}
+
+// The expansion is launched as a programmatic dependent of whatever kernel precedes it on the stream: it is
+// resident early, waits for that kernel's completion, and lets its own dependent (the GEMV) be scheduled.
+int launch_expand(const __nv_bfloat16* x, uint8_t* codes, uint8_t* sf, float* col_scale, int64_t k, int64_t batch,
+                  cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(ceil_div64(k / 16, kExpandThreads)), unsigned(batch), 1);
+  cfg.blockDim = dim3(kExpandThreads, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, expand_terms_kernel<4>, x, codes, sf, col_scale, int(k)) != cudaSuccess) return HB200_ERR_CUDA;
+  return HB200_OK;
 }
 
 struct TcPlan {
@@ -611,10 +637,9 @@ extern "C" int hb200_nvfp4_gemv_bf16in_tc(const void* weight_packed, const void*
   o.col0 = col0;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 egrid(unsigned(ceil_div64(k / 16, kExpandThreads)), unsigned(batch), 1);
-  expand_terms_kernel<4><<<egrid, kExpandThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), ws + p.off_codes,
-                                                          ws + p.off_sf, reinterpret_cast<float*>(ws + p.off_cs), int(k));
-  if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
+  if (launch_expand(static_cast<const __nv_bfloat16*>(x_bf16), ws + p.off_codes, ws + p.off_sf,
+                    reinterpret_cast<float*>(ws + p.off_cs), k, batch, s) != HB200_OK)
+    return HB200_ERR_CUDA;
   return run_tc(weight_packed, weight_scale, ws + p.off_codes, ws + p.off_sf, reinterpret_cast<const float*>(ws + p.off_cs),
                 o, n, k, batch, 4, alpha, p, ws, s);
 }
@@ -700,10 +725,9 @@ extern "C" int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_pac
   o.ptr[0] = static_cast<__nv_bfloat16*>(out_bf16);
   o.count = 1;
   o.ld = n;
-  const dim3 egrid(unsigned(ceil_div64(k / 16, kExpandThreads)), unsigned(batch), 1);
-  expand_terms_kernel<4><<<egrid, kExpandThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x_bf16), ws + p.off_codes,
-                                                          ws + p.off_sf, reinterpret_cast<float*>(ws + p.off_cs), int(k));
-  if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
+  if (launch_expand(static_cast<const __nv_bfloat16*>(x_bf16), ws + p.off_codes, ws + p.off_sf,
+                    reinterpret_cast<float*>(ws + p.off_cs), k, batch, s) != HB200_OK)
+    return HB200_ERR_CUDA;
   return run_tc(weight_packed, weight_scale, ws + p.off_codes, ws + p.off_sf, reinterpret_cast<const float*>(ws + p.off_cs),
                 o, n, k, batch, 4, alpha, p, ws, s);
 }
