@@ -124,16 +124,19 @@ inline bool make_scale_map(CUtensorMap* map, const void* base, int64_t atoms) {
 
 // Row-major 2-byte output [rows, cols] (leading dimension ldc elements) for the epilogue's TMA stores:
 // box = 32 columns (64 bytes) x 32 rows, 64-byte swizzle.
-inline bool make_output_map16(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldc, bool is_bf16) {
+// Output boxes of 32 rows: 32 columns (64-byte rows, 64-byte swizzle) or, wide, 64 columns (128-byte rows,
+// 128-byte swizzle: longer contiguous writes, which is what a store over NVLink wants).
+inline bool make_output_map16(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldc, bool is_bf16,
+                              bool wide = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(ldc) * 2};
-  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
-            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace hb200

@@ -50,26 +50,33 @@ struct PairArgs {
   int m, n, k;
   float alpha;
   int m_tiles, n_tiles;  // 256 x 256 tiles
-  // Tensor-parallel form: the tile columns start at col0 of the (wider) output, and every tile is also
-  // written to the same place of each peer's buffer with plain stores over NVLink.
-  int col0;
+  // Tensor-parallel form: every tile is also written to the same place of each peer's buffer (TMA stores
+  // through the peers' own tensor maps; stores only, nothing is ever loaded from peer memory).
   int n_peers;
-  void* peer_out[7];
 };
 
-template <typename OutT>
+struct PeerMaps {
+  CUtensorMap m[7];
+};
+
+// TP: the tensor-parallel form (every tile also goes to the peers).  It trades one stage of the operand ring
+// for output staging boxes twice as wide, so that a store over NVLink writes 128 contiguous bytes per row.
+template <typename OutT, bool TP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                       const __grid_constant__ CUtensorMap tmap_out, const PairArgs g) {
+                       const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PeerMaps peer_maps,
+                       const PairArgs g) {
+  constexpr int kS = TP ? kStages2 - 1 : kStages2;
+  constexpr int kBoxBytes = TP ? 4096 : 2048;  // one staging box per epilogue warp
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_out = smem + kStages2 * kStageBytes2;  // 8 warps x 4 KB, 1024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + kOutStageBytes);
+  uint8_t* stage_out = smem + kS * kStageBytes2;  // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + 16 * kBoxBytes);
   uint64_t* full_bar = bars;                 // used in the leader only
-  uint64_t* empty_bar = bars + kStages2;     // one set per CTA
-  uint64_t* sf_full_bar = bars + 2 * kStages2;   // scales of a stage are in tensor memory (leader only)
-  uint64_t* tmem_full_bar = bars + 3 * kStages2;
+  uint64_t* empty_bar = bars + kS;     // one set per CTA
+  uint64_t* sf_full_bar = bars + 2 * kS;   // scales of a stage are in tensor memory (leader only)
+  uint64_t* tmem_full_bar = bars + 3 * kS;
   uint64_t* tmem_empty_bar = tmem_full_bar + 1;  // used in the leader only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -83,7 +90,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   const int num_tiles = g.m_tiles * g.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages2; ++s) {
+    for (int s = 0; s < kS; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);   // the leader's producer arms it; bytes come from both CTAs
       mbar_init(smem_u32(&empty_bar[s]), 1);  // the leader's commit, multicast to both CTAs
       mbar_init(smem_u32(&sf_full_bar[s]), 1);
@@ -117,8 +124,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const int a_row = m_blk * 256 + int(rank) * 128;
       const int b_row = n_blk * kTileN + int(rank) * 128;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % kStages2;
-        const uint32_t ph = (it / kStages2) & 1;
+        const int s = it % kS;
+        const uint32_t ph = (it / kS) & 1;
         if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag)) { ok = false; break; }
         uint8_t* st = smem + s * kStageBytes2;
         const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);  // always the leader's barrier
@@ -145,8 +152,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (!mbar_wait(smem_u32(tmem_empty_bar), (tc & 1) ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kStages2;
-          const uint32_t ph = (it / kStages2) & 1;
+          const int s = it % kS;
+          const uint32_t ph = (it / kS) & 1;
           if (!mbar_wait(smem_u32(&sf_full_bar[s]), ph, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
@@ -177,8 +184,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       uint32_t it = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kStages2;
-          const uint32_t ph = (it / kStages2) & 1;
+          const int s = it % kS;
+          const uint32_t ph = (it / kS) & 1;
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const int atoms = min(kAtomsPerStage, col_tiles - kb * kAtomsPerStage);
@@ -210,7 +217,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     OutT* out = static_cast<OutT*>(g.out);
     const bool vec_ok = (g.ldc * sizeof(OutT)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
     const uint32_t free_bar = map_to_cta(smem_u32(tmem_empty_bar), 0);
-    uint8_t* box = stage_out + (warp - 4) * 2048;
+    uint8_t* box = stage_out + (warp - 4) * kBoxBytes;
     uint32_t tc = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
@@ -228,7 +235,39 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(free_bar);
       const int col = n_blk * kTileN + cgroup * 64;
-      if constexpr (sizeof(OutT) == 2) {
+      if constexpr (sizeof(OutT) == 2 && TP) {
+        // one box of 64 columns (128 bytes per row, 128-byte swizzle), stored to this rank and to every peer
+        if (lane == 0) bulk_wait_group_read0();
+        __syncwarp();
+        uint8_t* rowp = box + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * g.alpha;
+              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * g.alpha;
+              if constexpr (std::is_same<OutT, __half>::value) {
+                p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
+              } else {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
+                p[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+            }
+            // 128-byte swizzle: 16-byte chunk index xor the row's low three bits
+            *reinterpret_cast<uint4*>(rowp + (((h * 4 + v) ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmap_out, col, row0, smem_u32(box));
+          for (int p = 0; p < g.n_peers; ++p) tma_store_2d(&peer_maps.m[p], col, row0, smem_u32(box));
+          bulk_commit_group();
+        }
+      } else if constexpr (sizeof(OutT) == 2) {
         // two boxes of 32 columns (64 bytes per row, 64-byte swizzle) through this warp's staging buffer
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -258,20 +297,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             tma_store_2d(&tmap_out, col + h * 32, row0, smem_u32(box));
             bulk_commit_group();
           }
-          if (g.n_peers > 0) {
-            // the same box to every peer: 4 lanes cover the 64 bytes of a row, 8 rows per pass
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rl = i * 8 + (lane >> 2), c = lane & 3;
-              const uint4 v = *reinterpret_cast<const uint4*>(box + rl * 64 + ((c ^ ((rl >> 1) & 3)) << 4));
-              const int cc = col + h * 32 + c * 8;
-              if (row0 + rl < g.m && cc < g.n) {
-                const int64_t off = int64_t(row0 + rl) * g.ldc + g.col0 + cc;
-                for (int p = 0; p < g.n_peers; ++p) stg_stream_u4(static_cast<OutT*>(g.peer_out[p]) + off, v);
-              }
-            }
-            __syncwarp();
-          }
         }
       } else {
         if (row < g.m && col < g.n)
@@ -280,7 +305,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r[1], g.alpha, g.n - col - 32, vec_ok);
       }
     }
-    if (lane == 0) bulk_wait_group_read0();
+    // peers read the result right after the barrier kernel that follows: wait for the writes themselves
+    if (lane == 0) {
+      if constexpr (TP) bulk_wait_group0(); else bulk_wait_group_read0();
+    }
   }
 
   tcgen05_fence_before();
@@ -319,32 +347,42 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
     if ((ldc % 8) != 0 || reinterpret_cast<uintptr_t>(out) % 16) return HB200_ERR_UNSUPPORTED;
     // tensor parallel: the map spans this rank's columns only, so partial tiles are clipped at their end
     void* base = tp ? static_cast<void*>(static_cast<uint16_t*>(out) + peers.col0) : out;
-    if (!make_output_map16(&tout, base, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
+    if (!make_output_map16(&tout, base, m, n, ldc, out_dtype == 0, tp)) return HB200_ERR_CUDA;
   } else {
     tout = ta;  // unused by the fp32 epilogue
   }
-  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, 0, {}};
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0};
+  PeerMaps pm;
+  for (int i = 0; i < 7; ++i) pm.m[i] = tout;
   if (tp) {
-    g.col0 = int(peers.col0);
     g.n_peers = peers.n_peers;
-    for (int i = 0; i < peers.n_peers; ++i) g.peer_out[i] = peers.ptr[i];
+    for (int i = 0; i < peers.n_peers; ++i) {
+      void* base = static_cast<void*>(static_cast<uint16_t*>(peers.ptr[i]) + peers.col0);
+      if (!make_output_map16(&pm.m[i], base, m, n, ldc, out_dtype == 0, true)) return HB200_ERR_CUDA;
+    }
   }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = g.m_tiles * g.n_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   constexpr size_t smem = size_t(kStages2) * kStageBytes2 + kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
-  static_assert(smem <= 232448, "shared memory budget exceeded");
-#define HB200_PAIR(T)                                                                                         \
+  constexpr size_t smem_tp = size_t(kStages2 - 1) * kStageBytes2 + 2 * kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
+  static_assert(smem <= 232448 && smem_tp <= 232448, "shared memory budget exceeded");
+#define HB200_PAIR(T, TPV, SMEM)                                                                              \
   do {                                                                                                        \
-    auto kernel = nvfp4_gemm_pair_kernel<T>;                                                                  \
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)  \
+    auto kernel = nvfp4_gemm_pair_kernel<T, TPV>;                                                             \
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)) != cudaSuccess)  \
       return HB200_ERR_CUDA;                                                                                  \
-    kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);                                      \
+    kernel<<<2 * pairs, kThreads2, SMEM, stream>>>(ta, tb, tsa, tsb, tout, pm, g);                            \
   } while (0)
-  if (out_dtype == 0) HB200_PAIR(__nv_bfloat16);
-  else if (out_dtype == 1) HB200_PAIR(__half);
-  else HB200_PAIR(float);
+  if (tp) {
+    if (out_dtype == 0) HB200_PAIR(__nv_bfloat16, true, smem_tp);
+    else HB200_PAIR(__half, true, smem_tp);
+  } else {
+    if (out_dtype == 0) HB200_PAIR(__nv_bfloat16, false, smem);
+    else if (out_dtype == 1) HB200_PAIR(__half, false, smem);
+    else HB200_PAIR(float, false, smem);
+  }
 #undef HB200_PAIR
   return launch_status();
 }

@@ -112,6 +112,9 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All bulk groups of this thread have finished READING their shared-memory source.
+// all bulk stores of this thread have been written (not only read out of shared memory)
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // All but the most recent bulk group of this thread have finished reading shared memory.
 __device__ __forceinline__ void bulk_wait_group_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
