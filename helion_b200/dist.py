@@ -281,7 +281,21 @@ def expert_parallel_moe(x: Tensor, router_logits: Tensor, top_k: int, num_expert
     rows = exchange_rows(x[token_of_pair], plan.send_counts, plan.recv_counts, group)
     o = expert_fn(rows, plan.local_expert)
     back = exchange_rows(o, plan.recv_counts, plan.send_counts, group)
-    # `back` is in sorted-pair order; weight every row and sum the top_k rows of each token in fp32
+    # `back` is in sorted-pair order: row p belongs to pair order[p]
+    if x.is_cuda and back.dtype is torch.bfloat16 and x.shape[1] % 8 == 0:
+        # weighted sum of every token's top_k rows in one pass (fp32 accumulation), on the device kernel
+        from . import _lib
+
+        pairs = plan.order.numel()
+        row_of_pair = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        row_of_pair[plan.order] = torch.arange(pairs, dtype=torch.int32, device=x.device)
+        w = weights.reshape(-1).to(torch.float32).contiguous()
+        back = back.contiguous()
+        out = torch.empty(x.shape[0], x.shape[1], dtype=torch.bfloat16, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.call("hb200_moe_combine", back.data_ptr(), back.stride(0), row_of_pair.data_ptr(), w.data_ptr(),
+                      out.data_ptr(), x.shape[0], top_k, x.shape[1], torch.cuda.current_stream(x.device).cuda_stream)
+        return out
     w_sorted = weights.reshape(-1)[plan.order].to(torch.float32)
     out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32, device=x.device)
     out.index_add_(0, token_of_pair, back.to(torch.float32) * w_sorted[:, None])
