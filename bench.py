@@ -115,10 +115,10 @@ def measured_peaks() -> dict:
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline kernels, from the
 # `ncu --set full` captures summarised under profiles/ (same bench command, same sizes).
 NCU_TRAFFIC = {
-    "gemm_8192": 220.3e6,           # profiles/nvfp4_gemm_pair_kernel_8192x8192x8192.md
-    "gemv_gate_up_m1": 268.0e6,     # profiles/nvfp4_gemv_kernels_70b_decode_layer.md
-    "gemv_gate_up_m8": 268.6e6,
-    "rms_norm_16384x7168": 314.4e6,      # profiles/quant_producers_16384_tokens.md
+    "gemm_8192": 212.1e6,           # profiles/nvfp4_gemm_pair_kernel_8192x8192x8192.md
+    "gemv_gate_up_m1": 268.5e6,     # profiles/nvfp4_gemv_kernels_70b_decode_layer.md
+    "gemv_gate_up_m8": 274.9e6,     # tensor-core kernel
+    "rms_norm_16384x7168": 315.0e6,      # profiles/quant_producers_16384_tokens.md
 }
 
 
@@ -461,13 +461,14 @@ def wl_gemv(args, dev, rank, world, timer):
     roof = None
     if per_matrix:
         ach = per_matrix["gate_up"]["GBps"]
-        roof = {"bound": "hbm", "kernel": "nvfp4_gemv_kernel" if batch == 1 else "nvfp4_gemv_batched_kernel",
+        roof = {"bound": "hbm", "kernel": {"simt": "nvfp4_gemv_kernel", "mma": "nvfp4_gemv_batched_kernel", "tc": "nvfp4_gemv_tc_kernel"}[
+                    hb.ops._gemv_path(args.path, 57344, 8192, batch)] if not (batch > 1 and args.path == "simt") else "nvfp4_gemv_batched_kernel",
                 "launch": f"gate_up 57344x8192 M={batch}", "achieved": ach, "peak": peaks["hbm_gbs"],
                 "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 "traffic": ncu_traffic(f"gemv_gate_up_m{batch}")}
     return dict(value=layer_bytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=layer_bytes / (e2e_ms * 1e-3) / 1e12,
                 e2e_ms=e2e_ms, h2d=sum(2 * batch * k for _, k in LAYER_70B.values()),
-                d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * (2 if world > 1 else 1),
+                d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * ((2 if world > 1 else 1) + (1 if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc" else 0)),
                 roofline=roof, parity=parity, extra={"per_matrix": per_matrix, **extra},
                 dtype="fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
                 config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
@@ -586,7 +587,7 @@ def wl_moe(args, dev, rank, world, timer):
             "achieved": ach, "peak": 4 * peaks["bf16_tflops"], "peak_kind": f"4 x {peaks['kind']} dense bf16 burst",
             "unit": "TFLOP/s", "frac": ach / (4 * peaks["bf16_tflops"]), "traffic": None}
     return dict(value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s", ms=ms, e2e_value=flops / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
-                h2d=host_x.numel() * 2 + host_l.numel() * 4, d2h=host_out.numel() * 2, launches=7, roofline=roof,
+                h2d=host_x.numel() * 2 + host_l.numel() * 4, d2h=host_out.numel() * 2, launches=8, roofline=roof,
                 parity=parity, extra={}, dtype="e2m1 x e2m1 with e4m3 block scales, fp32 accumulate, bf16 activations",
                 config={"workload": "moe", **c, "parallelism": f"ep{world}" if world > 1 else "single", "l2": "flushed between steps"})
 
