@@ -80,6 +80,79 @@ moe_row_map_kernel(const int32_t* __restrict__ counts, int experts, const int32_
   row_of_pair[sorted_pairs[p]] = row;
 }
 
+// ---- stable counting sort of the (token, slot) pairs by expert: three small launches instead of a radix sort.
+constexpr int kSortThreads = 1024;
+
+// Pass 1: every CTA counts the experts of its 1024 pairs.  block_hist is [blocks][experts].
+template <typename IdxT>
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_hist_kernel(const IdxT* __restrict__ expert_of_pair, int pairs, int experts, int32_t* __restrict__ block_hist) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < experts; e += kSortThreads) hist[e] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kSortThreads + threadIdx.x;
+  if (p < pairs) {
+    const int e = int(expert_of_pair[p]);
+    if (e >= 0 && e < experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += kSortThreads) block_hist[blockIdx.x * experts + e] = hist[e];
+}
+
+// Pass 2 (one CTA): counts per expert, and block_hist turned in place into the first sorted position of every
+// (block, expert) bucket: expert-major, block-minor, which is what makes the sort stable.
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_scan_kernel(int32_t* __restrict__ block_hist, int blocks, int experts, int32_t* __restrict__ counts) {
+  extern __shared__ int32_t base[];  // [experts + 1]
+  for (int e = threadIdx.x; e < experts; e += kSortThreads) {
+    int32_t c = 0;
+    for (int b = 0; b < blocks; ++b) c += block_hist[b * experts + e];
+    counts[e] = c;
+    base[e + 1] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    base[0] = 0;
+    for (int e = 0; e < experts; ++e) base[e + 1] += base[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += kSortThreads) {
+    int32_t run = base[e];
+    for (int b = 0; b < blocks; ++b) {
+      const int32_t c = block_hist[b * experts + e];
+      block_hist[b * experts + e] = run;
+      run += c;
+    }
+  }
+}
+
+// Pass 3: a pair's rank inside its (block, expert) bucket is the number of earlier threads of the block with
+// the same expert: lanes before it in the warp (match + popc) plus the same expert's totals of the warps before.
+template <typename IdxT>
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_scatter_kernel(const IdxT* __restrict__ expert_of_pair, int pairs, int experts,
+                        const int32_t* __restrict__ bucket_start, int32_t* __restrict__ sorted_pairs) {
+  extern __shared__ int32_t warp_cnt[];  // [32 warps][experts]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * experts; i += kSortThreads) warp_cnt[i] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kSortThreads + threadIdx.x;
+  int e = -1;
+  if (p < pairs) {
+    e = int(expert_of_pair[p]);
+    if (e < 0 || e >= experts) e = -1;
+  }
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int before = __popc(same & ((1u << lane) - 1u));
+  if (e >= 0 && before == 0) warp_cnt[warp * experts + e] = __popc(same);  // one writer per (warp, expert)
+  __syncthreads();
+  if (e >= 0) {
+    int rank = before;
+    for (int w = 0; w < warp; ++w) rank += warp_cnt[w * experts + e];
+    sorted_pairs[bucket_start[blockIdx.x * experts + e] + rank] = p;
+  }
+}
+
 // Copies quantised token rows into the expert-sorted padded layout: codes [*, k/2], the row's scale bytes
 // (re-swizzled for the destination row) and its global scale.  A warp per destination row.
 __global__ void __launch_bounds__(256)
@@ -202,5 +275,46 @@ extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const 
   moe_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(expert_out_bf16), ld, row_of_pair, pair_weight,
       static_cast<__nv_bfloat16*>(out_bf16), tokens, int(top_k), hidden);
+  return launch_status();
+}
+
+// Stable sort of the (token, slot) pairs by expert and the per-expert counts, replacing the argsort and the
+// bincount of moe_matmul_ogs_helion_kernel_args_gen (examples/moe_matmul_ogs.py:96-117) without a host read.
+// expert_of_pair: int64 (idx_is_i64 != 0, what torch.topk returns) or int32, one entry per pair; entries outside
+// [0, experts) are dropped.  scratch: at least ceil(pairs / 1024) * experts int32.  experts <= 1024.
+extern "C" int hb200_moe_sort_pairs(const void* expert_of_pair, int idx_is_i64, int64_t pairs, int64_t experts,
+                                    int32_t* sorted_pairs, int32_t* counts, int32_t* scratch, void* stream) {
+  using namespace hb200;
+  if (!expert_of_pair || !sorted_pairs || !counts || !scratch) return HB200_ERR_INVALID_ARGUMENT;
+  if (pairs < 0 || experts <= 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (experts > 1024 || pairs > 0x7fffffff) return HB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = int(ceil_div64(pairs, kSortThreads));
+  const int e = int(experts), np = int(pairs);
+  if (blocks == 0) {
+    return cudaMemsetAsync(counts, 0, size_t(e) * 4, s) == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
+  }
+  const size_t scatter_smem = size_t(32) * e * 4;
+  if (idx_is_i64) {
+    auto scatter = moe_sort_scatter_kernel<long long>;
+    if (scatter_smem > 48 * 1024 &&
+        cudaFuncSetAttribute(scatter, cudaFuncAttributeMaxDynamicSharedMemorySize, int(scatter_smem)) != cudaSuccess)
+      return HB200_ERR_CUDA;
+    moe_sort_hist_kernel<long long><<<blocks, kSortThreads, size_t(e) * 4, s>>>(
+        static_cast<const long long*>(expert_of_pair), np, e, scratch);
+    moe_sort_scan_kernel<<<1, kSortThreads, size_t(e + 1) * 4, s>>>(scratch, blocks, e, counts);
+    scatter<<<blocks, kSortThreads, scatter_smem, s>>>(static_cast<const long long*>(expert_of_pair), np, e, scratch,
+                                                       sorted_pairs);
+  } else {
+    auto scatter = moe_sort_scatter_kernel<int32_t>;
+    if (scatter_smem > 48 * 1024 &&
+        cudaFuncSetAttribute(scatter, cudaFuncAttributeMaxDynamicSharedMemorySize, int(scatter_smem)) != cudaSuccess)
+      return HB200_ERR_CUDA;
+    moe_sort_hist_kernel<int32_t><<<blocks, kSortThreads, size_t(e) * 4, s>>>(
+        static_cast<const int32_t*>(expert_of_pair), np, e, scratch);
+    moe_sort_scan_kernel<<<1, kSortThreads, size_t(e + 1) * 4, s>>>(scratch, blocks, e, counts);
+    scatter<<<blocks, kSortThreads, scatter_smem, s>>>(static_cast<const int32_t*>(expert_of_pair), np, e, scratch,
+                                                       sorted_pairs);
+  }
   return launch_status();
 }

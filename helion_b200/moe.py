@@ -109,14 +109,19 @@ def build_schedule(experts_per_token: Tensor, num_experts: int) -> MoeSchedule:
     """Sort the (token, slot) pairs by expert (stable, as examples/moe_matmul_ogs.py:107-109 does for
     top-1) and lay the experts out in 128-row padded groups; all on the device."""
     _require_cuda(experts_per_token)
-    flat = experts_per_token.reshape(-1)
+    flat = experts_per_token.reshape(-1).contiguous()
     pairs = flat.numel()
-    sorted_pairs = torch.argsort(flat, stable=True).to(torch.int32)
-    # (torch.bincount would read the maximum back to the host)
-    counts = torch.zeros(num_experts, dtype=torch.int32, device=flat.device)
-    counts.index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
-    max_tiles = ceil_div(pairs, 128) + num_experts  # bound that does not depend on the routing
     dev = flat.device
+    if flat.dtype not in (torch.int64, torch.int32):
+        flat = flat.to(torch.int64)
+    # stable counting sort + per-expert counts in three small launches (no radix sort, no host read)
+    sorted_pairs = torch.empty(pairs, dtype=torch.int32, device=dev)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(1, ceil_div(pairs, 1024)) * num_experts, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("hb200_moe_sort_pairs", flat.data_ptr(), int(flat.dtype is torch.int64), pairs, num_experts,
+                  sorted_pairs.data_ptr(), counts.data_ptr(), scratch.data_ptr(), _stream())
+    max_tiles = ceil_div(pairs, 128) + num_experts  # bound that does not depend on the routing
     tile_info = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
     padded_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     row_of_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)

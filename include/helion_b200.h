@@ -197,6 +197,14 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* Stable sort of the (token, slot) pairs by expert plus the per-expert counts, on the device: what
+ * moe_matmul_ogs_helion_kernel_args_gen computes with bincount + argsort and a host read
+ * (examples/moe_matmul_ogs.py:96-117).  expert_of_pair: one entry per pair, int64 when idx_is_i64 != 0 (what
+ * torch.topk returns), else int32; entries outside [0, experts) are dropped.  sorted_pairs [pairs] and
+ * counts [experts] are written; scratch needs ceil(pairs / 1024) * experts int32.  experts <= 1024. */
+int hb200_moe_sort_pairs(const void* expert_of_pair, int idx_is_i64, int64_t pairs, int64_t experts,
+                         int32_t* sorted_pairs, int32_t* counts, int32_t* scratch, void* stream);
+
 /* First expert GEMM of an NVFP4 MoE layer with the SiLU-mul in its epilogue (arguments as
  * hb200_nvfp4_grouped_matmul).  b_packed holds, per expert, n rows that interleave gate and up in blocks of
  * 128: rows [256 j, 256 j + 128) are gate outputs [128 j, 128 j + 128), rows [256 j + 128, 256 j + 256) the up
