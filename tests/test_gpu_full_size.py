@@ -1,0 +1,131 @@
+"""BASELINE-size runs checked through properties that do not need a full-size oracle: slices against the CPU
+oracle, invariance under permuting independent rows, symmetry, the largest code of every quantisation group,
+and run-to-run bit identity."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helion_b200 as hb
+from helion_b200 import _lib
+from helion_b200 import moe as M
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FP8 = torch.float8_e4m3fn
+
+
+def device_status_ok():
+    torch.cuda.synchronize()
+    return _lib.load().hb200_device_status(1) == 0
+
+
+def random_operand(rows, k, seed):
+    """Random packed codes and block scales in [0.5, 1.5), generated on the device."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    codes = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=DEV, generator=g)
+    logical = (torch.rand(rows, k // 16, device=DEV, generator=g) + 0.5).to(FP8)
+    return codes, hb.swizzle_fp8_scales(logical)
+
+
+def test_gemm_8192_cubed_slices_symmetry_and_determinism():
+    m = n = k = 8192
+    a, sa = random_operand(m, k, 1)
+    b, sb = random_operand(n, k, 2)
+    d = hb.nvfp4_scaled_matmul(a, b.t(), sa, sb, alpha=2.0**-8)
+    assert device_status_ok()
+    assert d.shape == (m, n) and d.dtype is torch.bfloat16 and torch.isfinite(d.float()).all()
+    # bit-identical from run to run, and D(A, B)^T == D(B, A): both operands ride the same MMA K loop
+    assert torch.equal(d, hb.nvfp4_scaled_matmul(a, b.t(), sa, sb, alpha=2.0**-8))
+    assert torch.equal(d.t(), hb.nvfp4_scaled_matmul(b, a.t(), sb, sa, alpha=2.0**-8))
+    # 128 x 128 tiles of the result against the oracle on the operands' row slices
+    col_tiles = k // 64
+    for r0, c0 in [(0, 0), (8064, 8064), (3456, 128), (128, 7040)]:
+        sa_tile = sa.reshape(-1)[(r0 // 128) * col_tiles * 512 : (r0 // 128 + 1) * col_tiles * 512]
+        sb_tile = sb.reshape(-1)[(c0 // 128) * col_tiles * 512 : (c0 // 128 + 1) * col_tiles * 512]
+        ref = O.nvfp4_scaled_matmul(a[r0 : r0 + 128].cpu(), b[c0 : c0 + 128].cpu(), sa_tile.cpu(), sb_tile.cpu(),
+                                    torch.float32, alpha=2.0**-8)
+        got = d[r0 : r0 + 128, c0 : c0 + 128].float().cpu()
+        floor = ref.pow(2).mean().sqrt()
+        assert float(((got - ref).abs() / torch.maximum(ref.abs(), floor)).max()) <= 1e-2
+
+
+def _largest_code_is_448(q, s, group, min_scale):
+    """Every group whose scale is amax / 448 (not the floor) holds at least one code of magnitude 448."""
+    t, h = q.shape
+    top = q.view(torch.uint8).view(t, h // group, group).bitwise_and(0x7F).amax(dim=2)  # e4m3 magnitude bits
+    free = s.reshape(t, -1) > min_scale
+    return bool((top[free] == 0x7E).all())  # 0x7E is 448
+
+
+def test_rms_quant_16384_tokens_properties():
+    t, h = 16384, 7168
+    g = torch.Generator(device=DEV).manual_seed(2)
+    x = torch.randn(t, h, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.rand(h, device=DEV, generator=g) + 0.5).to(torch.bfloat16)
+    q = torch.empty(t, h, dtype=FP8, device=DEV)
+    s = torch.empty(t, 1, dtype=torch.float32, device=DEV)
+    hb.rms_norm_dynamic_per_token_quant(q, x, w, s, 1e-6)
+    assert device_status_ok()
+    assert _largest_code_is_448(q, s, h, 1.0 / (448.0 * 512.0))
+    # tokens are independent: a permuted batch gives the permuted codes and scales, bit for bit
+    perm = torch.randperm(t, device=DEV, generator=g)
+    q2, s2 = torch.empty_like(q), torch.empty_like(s)
+    hb.rms_norm_dynamic_per_token_quant(q2, x[perm].contiguous(), w, s2, 1e-6)
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)[perm]) and torch.equal(s2, s[perm])
+    # the first rows against the CPU oracle (codes may move where the row's rms moved by an ulp)
+    qo, so, _ = O.rms_norm_dynamic_per_token_quant(x[:128].cpu(), w.cpu(), 1e-6)
+    same = (q[:128].cpu().view(torch.uint8) == qo.view(torch.uint8)).float().mean()
+    assert float(same) >= 0.999 and torch.allclose(s[:128].cpu(), so, rtol=1e-6, atol=0)
+
+
+def test_silu_and_group_quant_16384_tokens_properties():
+    t, inter, gs = 16384, 18432, 128
+    g = torch.Generator(device=DEV).manual_seed(22)
+    x = torch.randn(t, 2 * inter, device=DEV, generator=g, dtype=torch.bfloat16)
+    q = torch.empty(t, inter, dtype=FP8, device=DEV)
+    s = torch.empty(t, inter // gs, dtype=torch.float32, device=DEV)
+    hb.silu_and_mul_per_block_quant(q, x, s, gs)
+    assert device_status_ok()
+    assert _largest_code_is_448(q, s, gs, 1.0 / (448.0 * 512.0))
+    # a slice of rows against the reference function evaluated by torch on the same device (bit-exact)
+    qo, so = O.silu_and_mul_per_block_quant(x[:256], gs)
+    assert torch.equal(q[:256].view(torch.uint8), qo.view(torch.uint8)) and torch.equal(s[:256], so)
+    del x, q, s
+    h = 7168
+    y = torch.randn(t, h, device=DEV, generator=g, dtype=torch.bfloat16)
+    qg = torch.empty(t, h, dtype=FP8, device=DEV)
+    sg = torch.empty(t, h // gs, dtype=torch.float32, device=DEV)
+    hb.per_token_group_fp8_quant(y, qg, sg, gs, 1e-10, -448.0, 448.0, False)
+    assert device_status_ok()
+    assert _largest_code_is_448(qg, sg, gs, 0.0)
+    qo, so = O.per_token_group_fp8_quant(y[:256].cpu(), gs, 1e-10, -448.0, 448.0, False)
+    assert torch.equal(qg[:256].cpu().view(torch.uint8), qo.view(torch.uint8)) and torch.equal(sg[:256].cpu(), so)
+
+
+def test_moe_8192_tokens_permutation_invariance():
+    t, h, inter, e, k = 8192, 4096, 1536, 128, 8
+    g = torch.Generator(device=DEV).manual_seed(3)
+
+    def bundle(n, kk, seed):
+        codes, scales = random_operand(e * n, kk, seed)
+        per = hb.swizzled_scale_numel(n, kk // 16)
+        # random_operand swizzles all experts' rows as one matrix: n is a multiple of 128, so every expert's
+        # scale tiles are a contiguous block of it
+        return M.GroupedNvfp4Weight(codes.reshape(e, n, kk // 2), scales.reshape(e, per),
+                                    torch.full((e,), 2.0**-12, dtype=torch.float32, device=DEV))
+
+    w_gu = M.interleave_gate_up(bundle(2 * inter, h, 31))
+    w_d = bundle(h, inter, 32)
+    x = torch.randn(t, h, device=DEV, generator=g).to(torch.bfloat16)
+    logits = torch.randn(t, e, device=DEV, generator=g)
+    y = M.nvfp4_moe(x, logits, k, w_gu, w_d)
+    assert device_status_ok()
+    assert y.shape == (t, h) and torch.isfinite(y.float()).all() and float(y.float().abs().mean()) > 0
+    # tokens are independent (per-token quantisation, row-wise GEMMs, per-token combine in slot order)
+    perm = torch.randperm(t, device=DEV, generator=g)
+    y2 = M.nvfp4_moe(x[perm].contiguous(), logits[perm].contiguous(), k, w_gu, w_d)
+    assert device_status_ok()
+    assert torch.equal(y2, y[perm])

@@ -117,6 +117,21 @@ def test_moe_layer_against_oracle(t, h, inter, e, k, interleaved):
     assert float((yc - rc).pow(2).mean().sqrt() / rc.pow(2).mean().sqrt()) <= 5e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+@pytest.mark.parametrize("pairs,experts", [(0, 4), (1, 1), (1000, 7), (70000, 128), (5000, 1024), (3333, 3)])
+def test_device_sort_matches_stable_argsort(pairs, experts, dtype):
+    g = torch.Generator().manual_seed(pairs + experts)
+    e = torch.randint(0, experts, (pairs,), generator=g).to(dtype).to(DEV)
+    sorted_pairs = torch.full((pairs,), -1, dtype=torch.int32, device=DEV)
+    counts = torch.full((experts,), -1, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(max(1, -(-pairs // 1024)) * experts, dtype=torch.int32, device=DEV)
+    _lib.call("hb200_moe_sort_pairs", e.data_ptr(), int(dtype is torch.int64), pairs, experts, sorted_pairs.data_ptr(),
+              counts.data_ptr(), scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(sorted_pairs.cpu().long(), torch.argsort(e.cpu().long(), stable=True))
+    assert torch.equal(counts.cpu().long(), torch.bincount(e.cpu().long(), minlength=experts))
+
+
 def test_silu_epilogue_is_bit_identical_to_the_two_kernel_form():
     t, h, inter, e, k = 512, 512, 256, 8, 2
     g = torch.Generator().manual_seed(11)

@@ -117,3 +117,29 @@ def test_custom_ops_registered_with_fake_impls():
         assert y.shape == (64,)
         c, sc, g = torch.ops.helion_b200.nvfp4_quantize(x, None)
         assert c.shape == (2, 128) and sc.numel() == 128 * 16 and g.shape == (2,)
+
+
+def test_interleave_gate_up_moves_whole_128_row_tiles():
+    """Host-side weight preparation for the SiLU-mul epilogue: codes and scale tiles move together."""
+    from helion_b200 import moe as M
+
+    e, inter, k = 2, 256, 64
+    n = 2 * inter
+    g = torch.Generator().manual_seed(0)
+    packed = torch.randint(0, 256, (e, n, k // 2), dtype=torch.uint8, generator=g)
+    logical = [(torch.rand(n, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn) for _ in range(e)]
+    scales = torch.stack([L.swizzle_fp8_scales(s).view(torch.uint8) for s in logical]).view(torch.float8_e4m3fn)
+    w = M.GroupedNvfp4Weight(packed, scales, torch.ones(e))
+    wi = M.interleave_gate_up(w)
+    assert wi.gate_up_interleaved and M.interleave_gate_up(wi) is wi
+    for i in range(e):
+        un = L.unswizzle_fp8_scales(wi.scales[i], n, k // 16).view(torch.uint8)
+        for j in range(inter // 128):
+            rows_g = slice(256 * j, 256 * j + 128)
+            rows_u = slice(256 * j + 128, 256 * j + 256)
+            assert torch.equal(wi.packed[i, rows_g], packed[i, 128 * j : 128 * j + 128])
+            assert torch.equal(wi.packed[i, rows_u], packed[i, inter + 128 * j : inter + 128 * j + 128])
+            assert torch.equal(un[rows_g], logical[i][128 * j : 128 * j + 128].view(torch.uint8))
+            assert torch.equal(un[rows_u], logical[i][inter + 128 * j : inter + 128 * j + 128].view(torch.uint8))
+    with pytest.raises(ValueError, match="multiple of 256"):
+        M.interleave_gate_up(M.GroupedNvfp4Weight(packed[:, :384], scales, torch.ones(e)))
