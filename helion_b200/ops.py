@@ -205,6 +205,44 @@ def _(result, input, weight, scale, epsilon, scale_ub, residual):  # noqa: A002
     return None
 
 
+@torch.library.custom_op("helion_b200::rms_norm_per_block_quant", mutates_args=("result", "scale", "residual"))
+def _rms_block_quant_op(
+    result: Tensor, input: Tensor, weight: Tensor, scale: Tensor, epsilon: float,  # noqa: A002
+    scale_ub: Tensor | None, residual: Tensor | None, group_size: int,
+) -> None:
+    _require_cuda(result, input, weight, scale, scale_ub, residual)
+    tokens, hidden = input.shape
+    with torch.cuda.device(input.device):
+        _lib.call(
+            "hb200_rms_norm_per_block_quant",
+            result.data_ptr(), input.data_ptr(), weight.data_ptr(), scale.data_ptr(), tokens, hidden,
+            float(epsilon), _ptr(scale_ub), _ptr(residual), group_size, scale.stride(0), scale.stride(1),
+            int(input.dtype == torch.float16), int(result.dtype == torch.int8), _stream(),
+        )
+
+
+@_rms_block_quant_op.register_fake
+def _(result, input, weight, scale, epsilon, scale_ub, residual, group_size):  # noqa: A002
+    return None
+
+
+@torch.library.custom_op("helion_b200::dynamic_per_token_scaled_fp8_quant", mutates_args=("result", "scale"))
+def _dyn_token_quant_op(result: Tensor, input: Tensor, scale: Tensor, scale_ub: Tensor | None) -> None:  # noqa: A002
+    _require_cuda(result, input, scale, scale_ub)
+    tokens, hidden = input.shape
+    with torch.cuda.device(input.device):
+        _lib.call(
+            "hb200_dynamic_per_token_scaled_fp8_quant",
+            result.data_ptr(), input.data_ptr(), scale.data_ptr(), tokens, hidden, _ptr(scale_ub),
+            int(input.dtype == torch.float16), _stream(),
+        )
+
+
+@_dyn_token_quant_op.register_fake
+def _(result, input, scale, scale_ub):  # noqa: A002
+    return None
+
+
 @torch.library.custom_op("helion_b200::per_token_group_fp8_quant", mutates_args=("output_q", "output_s"))
 def _group_quant_op(
     input: Tensor, output_q: Tensor, output_s: Tensor, group_size: int, eps: float,  # noqa: A002
@@ -520,6 +558,66 @@ def rms_norm_dynamic_per_token_quant(
     if not (scale.is_contiguous() and weight.is_contiguous()):
         raise ValueError("scale and weight must be contiguous")
     _rms_quant_op(result, input, weight, scale, epsilon, scale_ub, residual)
+
+
+def rms_norm_per_block_quant(
+    result: Tensor, input: Tensor, weight: Tensor, scale: Tensor, epsilon: float,  # noqa: A002
+    scale_ub: Tensor | None, residual: Tensor | None, group_size: int, is_scale_transposed: bool,
+) -> None:
+    """RMSNorm(weight) (+ optional residual add, written back) then one dynamic scale per ``group_size`` block.
+
+    Drop-in for ``rms_norm_per_block_quant``
+    (pretuned_kernels/rms_norm_per_block_quant/rms_norm_per_block_quant.py:38-140); ``scale`` may be a
+    transposed view (``is_scale_transposed``), as there.
+    """
+    assert input.ndim == 2
+    num_tokens, hidden_size = input.shape
+    groups_per_row = scale.shape[1]
+    assert hidden_size % group_size == 0 and hidden_size // group_size == groups_per_row
+    assert scale.shape[0] == num_tokens
+    assert scale.dtype == torch.float32
+    if scale.stride(1) > 1:
+        assert is_scale_transposed
+    assert result.dtype in [_FP8, torch.int8]
+    assert result.is_contiguous() and input.is_contiguous()
+    if scale_ub is not None:
+        assert result.dtype == _FP8
+        assert scale_ub.dtype == torch.float32
+    assert input.dtype == weight.dtype
+    if residual is not None:
+        assert residual.dtype == input.dtype
+        if not residual.is_contiguous():
+            raise ValueError("residual must be contiguous")
+    assert group_size in [64, 128]
+    if input.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"input must be bfloat16 or float16, got {input.dtype}")
+    if not weight.is_contiguous():
+        raise ValueError("weight must be contiguous")
+    _rms_block_quant_op(result, input, weight, scale, epsilon, scale_ub, residual, group_size)
+
+
+def dynamic_per_token_scaled_fp8_quant(
+    result: Tensor, input: Tensor, scale: Tensor, scale_ub: Tensor | None = None,  # noqa: A002
+) -> None:
+    """Per-token dynamic FP8 quantisation ``result = fp8(input * (1 / scale))``, ``scale = amax / 448``, in place.
+
+    Drop-in for ``dynamic_per_token_scaled_fp8_quant``
+    (pretuned_kernels/dynamic_per_token_scaled_fp8_quant/dynamic_per_token_scaled_fp8_quant.py:32-72).
+    """
+    assert input.ndim == 2
+    num_tokens, _hidden = input.shape
+    assert result.shape == input.shape
+    assert scale.shape[0] == num_tokens
+    assert scale.dtype == torch.float32
+    assert input.stride()[-1] == 1
+    assert result.stride()[-1] == 1
+    if input.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"input must be bfloat16 or float16, got {input.dtype}")
+    if result.dtype is not _FP8:
+        raise TypeError(f"result must be float8_e4m3fn, got {result.dtype}")
+    if not (result.is_contiguous() and scale.is_contiguous()):
+        raise ValueError("result and scale must be contiguous")
+    _dyn_token_quant_op(result, input.contiguous(), scale, scale_ub)
 
 
 def per_token_group_fp8_quant(

@@ -197,6 +197,22 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* rms_norm_per_block_quant (pretuned_kernels/rms_norm_per_block_quant/rms_norm_per_block_quant.py:38-140):
+ * the RMSNorm of hb200_rms_norm_dynamic_per_token_quant with one scale per group of 64 or 128 elements of the
+ * hidden dimension (true division for fp8, reciprocal multiply and round for int8).  Scale (t, g) is written at
+ * scale[t * scale_stride_t + g * scale_stride_g] (fp32 elements), which covers the transposed scale layout. */
+int hb200_rms_norm_per_block_quant(void* result, const void* input, const void* weight, void* scale, int64_t tokens,
+                                   int64_t hidden, float epsilon, const float* scale_ub, void* residual,
+                                   int group_size, int64_t scale_stride_t, int64_t scale_stride_g, int in_is_fp16,
+                                   int out_is_int8, void* stream);
+
+/* dynamic_per_token_scaled_fp8_quant
+ * (pretuned_kernels/dynamic_per_token_scaled_fp8_quant/dynamic_per_token_scaled_fp8_quant.py:32-72):
+ * scale[t] = max(min(amax_t, *scale_ub) * (1/448), 1/(448*512)), result = e4m3(clamp(x * (1 / scale[t]))).
+ * input bf16 (or fp16) [tokens, hidden] contiguous, hidden % 8 == 0, hidden <= 32768. */
+int hb200_dynamic_per_token_scaled_fp8_quant(void* result, const void* input, void* scale, int64_t tokens,
+                                             int64_t hidden, const float* scale_ub, int in_is_fp16, void* stream);
+
 /* Stable sort of the (token, slot) pairs by expert plus the per-expert counts, on the device: what
  * moe_matmul_ogs_helion_kernel_args_gen computes with bincount + argsort and a host read
  * (examples/moe_matmul_ogs.py:96-117).  expert_of_pair: one entry per pair, int64 when idx_is_i64 != 0 (what

@@ -246,6 +246,47 @@ def rms_norm_dynamic_per_token_quant(
     return q, s, new_res
 
 
+def dynamic_per_token_scaled_fp8_quant(x: Tensor, scale_ub: Tensor | None = None):
+    """_dynamic_per_token_scaled_fp8_quant_torch
+    (pretuned_kernels/dynamic_per_token_scaled_fp8_quant/dynamic_per_token_scaled_fp8_quant.py:77-99):
+    per-row ``s = clamp(amax * (1/448), min=1/(448*512))``, ``q = fp8(clamp(x * (1/s)))`` -- a multiply by
+    the reciprocal, not a division.  Returns ``(codes [T, H], scale [T, 1])``."""
+    xf = x.to(torch.float32)
+    s = xf.abs().amax(dim=-1)
+    if scale_ub is not None:
+        s = s.clamp(max=float(scale_ub))
+    s = (s * (1.0 / FP8_MAX)).clamp(min=FP8_MIN_SCALE)
+    y = xf * (1.0 / s[:, None])
+    return y.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s[:, None]
+
+
+def rms_norm_per_block_quant(
+    x: Tensor, weight: Tensor, epsilon: float, group_size: int, scale_ub: Tensor | None = None,
+    residual: Tensor | None = None, rms_ulp_nudge: Tensor | None = None,
+):
+    """_rms_norm_per_block_quant_torch
+    (pretuned_kernels/rms_norm_per_block_quant/rms_norm_per_block_quant.py:134-173): RMSNorm as in
+    rms_norm_dynamic_per_token_quant, then one scale per ``group_size`` block of the hidden dimension and a
+    true division.  Returns ``(codes [T, H], scale [T, H/group], new_residual or None)``; ``rms_ulp_nudge`` as in
+    :func:`rms_norm_dynamic_per_token_quant`."""
+    t, h = x.shape
+    xf = x.to(torch.float32)
+    new_res = None
+    if residual is not None:
+        xf = xf + residual.to(torch.float32)
+        new_res = xf.to(residual.dtype)
+    rms = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + epsilon)
+    if rms_ulp_nudge is not None:
+        rms = (rms.view(torch.int32) + rms_ulp_nudge.reshape(-1, 1).to(torch.int32)).view(torch.float32)
+    normed = ((xf * rms).to(x.dtype) * weight[None, :]).to(torch.float32).reshape(t, h // group_size, group_size)
+    s = normed.abs().amax(dim=-1)
+    if scale_ub is not None:
+        s = s.clamp(max=float(scale_ub))
+    s = (s * (1.0 / FP8_MAX)).clamp(min=FP8_MIN_SCALE)
+    q = (normed / s[:, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(t, h).to(torch.float8_e4m3fn)
+    return q, s, new_res
+
+
 def rms_norm_row_rms(x: Tensor, epsilon: float, residual: Tensor | None = None) -> Tensor:
     """The fp32 ``rms`` factor of each row as the function above computes it (test helper)."""
     xf = x.to(torch.float32)

@@ -153,6 +153,33 @@ def main(ref_root: str) -> None:
     out["grp_x"] = _np(xg)
     np.savez_compressed(HERE / "quant_producers.npz", **out)
 
+    # ---- sibling quant producers ------------------------------------------------------------------
+    dyn = _load(pk / "dynamic_per_token_scaled_fp8_quant" / "dynamic_per_token_scaled_fp8_quant.py", "ref_dyn")
+    rpb = _load(pk / "rms_norm_per_block_quant" / "rms_norm_per_block_quant.py", "ref_rpb")
+    out = {}
+    torch.manual_seed(21)
+    xd = (torch.randn(24, 384) * torch.logspace(-3, 2, 24)[:, None]).to(torch.bfloat16)
+    xd[5] = 0  # an all-zero row: the scale floor
+    for tag, ub in (("", None), ("_ub", torch.tensor(0.01))):
+        q = torch.zeros(24, 384, dtype=torch.float8_e4m3fn)
+        sc = torch.zeros(24, 1)
+        dyn._dynamic_per_token_scaled_fp8_quant_torch(q, xd, sc, ub)
+        out[f"dyn_q{tag}"], out[f"dyn_s{tag}"] = _np(q), _np(sc)
+    out["dyn_x"] = _np(xd)
+    xr = torch.randn(20, 512).to(torch.bfloat16)
+    wr = (torch.rand(512) + 0.5).to(torch.bfloat16)
+    res = torch.randn(20, 512).to(torch.bfloat16)
+    out["rpb_x"], out["rpb_w"], out["rpb_res"] = _np(xr), _np(wr), _np(res)
+    for gs in (64, 128):
+        for tag, r in (("", None), ("_res", res.clone())):
+            q = torch.zeros(20, 512, dtype=torch.float8_e4m3fn)
+            sc = torch.zeros(20, 512 // gs)
+            rpb._rms_norm_per_block_quant_torch(q, xr, wr, sc, 1e-6, None, r, gs, False)
+            out[f"rpb_q_{gs}{tag}"], out[f"rpb_s_{gs}{tag}"] = _np(q), _np(sc)
+            if r is not None:
+                out[f"rpb_newres_{gs}"] = _np(r)
+    np.savez_compressed(HERE / "quant_siblings.npz", **out)
+
     # ---- MoE / grouped GEMM references ------------------------------------------------------------
     out = {}
     torch.manual_seed(8)

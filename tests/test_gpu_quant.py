@@ -200,3 +200,84 @@ def test_nvfp4_quantiser_tie_cases():
     codes, scales, _ = hb.nvfp4_quantize(x.to(DEV), g.to(DEV))
     co, so, _ = O.nvfp4_quantize(x, g)
     assert count_diff(codes, co) == 0 and count_diff(scales, so) == 0
+
+
+# ------------------------------------------------------------------ sibling producers
+def run_dyn(x, ub=None):
+    t, h = x.shape
+    q = torch.zeros((t, h), device=DEV, dtype=FP8)
+    s = torch.full((t, 1), float("nan"), device=DEV)
+    hb.dynamic_per_token_scaled_fp8_quant(q, x.to(DEV), s, None if ub is None else ub.to(DEV))
+    return q, s
+
+
+def test_dynamic_per_token_golden(golden):
+    g = golden("quant_siblings.npz")
+    x = g.bf16("dyn_x")
+    q, s = run_dyn(x)
+    assert count_diff(q, g.e4m3("dyn_q")) == 0 and count_diff(s, g.raw("dyn_s")) == 0
+    q, s = run_dyn(x, torch.tensor(0.01))
+    assert count_diff(q, g.e4m3("dyn_q_ub")) == 0 and count_diff(s, g.raw("dyn_s_ub")) == 0
+
+
+@pytest.mark.parametrize("t,h", [(1, 8), (7, 520), (64, 7168), (33, 4096), (5, 32768), (300, 1024)])
+def test_dynamic_per_token_bit_exact(t, h):
+    g = torch.Generator().manual_seed(t + h)
+    x = (torch.randn(t, h, generator=g) * torch.logspace(-2, 2, t)[:, None]).to(torch.bfloat16)
+    q, s = run_dyn(x)
+    qo, so = O.dynamic_per_token_scaled_fp8_quant(x)
+    assert count_diff(q, qo) == 0 and count_diff(s, so) == 0
+    q, s = run_dyn(x.to(torch.float16))
+    qo, so = O.dynamic_per_token_scaled_fp8_quant(x.to(torch.float16))
+    assert count_diff(q, qo) == 0 and count_diff(s, so) == 0
+
+
+def run_rms_block(x, w, eps, gs, ub=None, res=None, transposed=False, int8=False):
+    t, h = x.shape
+    q = torch.zeros((t, h), device=DEV, dtype=torch.int8 if int8 else FP8)
+    if transposed:
+        s = torch.full((h // gs, t), float("nan"), device=DEV).t()
+    else:
+        s = torch.full((t, h // gs), float("nan"), device=DEV)
+    res_d = None if res is None else res.to(DEV).clone()
+    hb.rms_norm_per_block_quant(q, x.to(DEV), w.to(DEV), s, eps, None if ub is None else ub.to(DEV), res_d, gs, transposed)
+    return q, s, res_d
+
+
+def test_rms_per_block_golden(golden):
+    g = golden("quant_siblings.npz")
+    x, w, res = g.bf16("rpb_x"), g.bf16("rpb_w"), g.bf16("rpb_res")
+    for gs in (64, 128):
+        q, s, _ = run_rms_block(x, w, 1e-6, gs)
+        assert count_diff(q, g.e4m3(f"rpb_q_{gs}")) <= 2 and count_diff(s, g.raw(f"rpb_s_{gs}")) <= 1
+        q, s, r = run_rms_block(x, w, 1e-6, gs, None, res, transposed=True)
+        assert count_diff(q, g.e4m3(f"rpb_q_{gs}_res")) <= 2 and count_diff(s.contiguous(), g.raw(f"rpb_s_{gs}_res")) <= 1
+        assert count_diff(r, g.bf16(f"rpb_newres_{gs}")) == 0
+
+
+@pytest.mark.parametrize("t,h,gs", [(3, 64, 64), (17, 1024, 128), (64, 7168, 128), (9, 4096, 64), (4, 32768, 128)])
+def test_rms_per_block_against_oracle(t, h, gs):
+    """Rows equal the oracle bit for bit, or the oracle with that row's fp32 rms moved by <= 2 ulp."""
+    g = torch.Generator().manual_seed(h + gs)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    w = (torch.rand(h, generator=g) + 0.5).to(torch.bfloat16)
+    q, s, _ = run_rms_block(x, w, 1e-6, gs)
+    qo, so, _ = O.rms_norm_per_block_quant(x, w, 1e-6, gs)
+    bad = (bits(q) != bits(qo)).any(dim=1) | (bits(s) != bits(so)).any(dim=1)
+    for nudge in (-1, 1, -2, 2):
+        if not bad.any():
+            break
+        qn, sn, _ = O.rms_norm_per_block_quant(x, w, 1e-6, gs, None, None, torch.full((t,), nudge, dtype=torch.int32))
+        bad &= (bits(q) != bits(qn)).any(dim=1) | (bits(s) != bits(sn)).any(dim=1)
+    assert not bad.any(), f"{int(bad.sum())} rows differ beyond a 2-ulp change of rms"
+    # int8 output (the Helion kernel's rule, rms_norm_per_block_quant.py:84-90,125-128): scale = amax * (1/127)
+    # floored at fp32 eps, codes = round(x_norm * (1 / scale)).  A row whose rms moved by an ulp may differ.
+    qi, si, _ = run_rms_block(x, w, 1e-6, gs, int8=True)
+    xf = x.float()
+    rms = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + 1e-6)
+    normed = ((xf * rms).to(torch.bfloat16) * w[None, :]).float().reshape(t, h // gs, gs)
+    se = (normed.abs().amax(dim=-1) * (1.0 / 127)).clamp(min=1.1920928955078125e-07)
+    qe = (normed * (1.0 / se[:, :, None])).round().clamp(-128, 127).to(torch.int8).reshape(t, h)
+    assert qi.dtype is torch.int8
+    assert float((qi.cpu() != qe).float().mean()) <= 2e-3
+    assert torch.allclose(si.cpu(), se, rtol=1e-5, atol=0)

@@ -96,6 +96,22 @@ def test_quant_producer_references(golden):
         assert _eq_bits(q, g.e4m3(f"grp_q_{ue}")) and _eq_bits(s, g.raw(f"grp_s_{ue}"))
 
 
+def test_sibling_quant_producer_references(golden):
+    g = golden("quant_siblings.npz")
+    x = g.bf16("dyn_x")
+    q, s = O.dynamic_per_token_scaled_fp8_quant(x)
+    assert _eq_bits(q, g.e4m3("dyn_q")) and _eq_bits(s, g.raw("dyn_s"))
+    q, s = O.dynamic_per_token_scaled_fp8_quant(x, torch.tensor(0.01))
+    assert _eq_bits(q, g.e4m3("dyn_q_ub")) and _eq_bits(s, g.raw("dyn_s_ub"))
+    xr, wr, res = g.bf16("rpb_x"), g.bf16("rpb_w"), g.bf16("rpb_res")
+    for gs in (64, 128):
+        q, s, _ = O.rms_norm_per_block_quant(xr, wr, 1e-6, gs)
+        assert _eq_bits(q, g.e4m3(f"rpb_q_{gs}")) and _eq_bits(s, g.raw(f"rpb_s_{gs}"))
+        q, s, new_res = O.rms_norm_per_block_quant(xr, wr, 1e-6, gs, None, res)
+        assert _eq_bits(q, g.e4m3(f"rpb_q_{gs}_res")) and _eq_bits(s, g.raw(f"rpb_s_{gs}_res"))
+        assert _eq_bits(new_res, g.bf16(f"rpb_newres_{gs}"))
+
+
 def test_moe_references(golden):
     g = golden("moe.npz")
     a, w, top1 = g.bf16("moe_a"), g.bf16("moe_w"), g.raw("moe_top1")
