@@ -285,8 +285,8 @@ extern "C" int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const 
 extern "C" int hb200_moe_sort_pairs(const void* expert_of_pair, int idx_is_i64, int64_t pairs, int64_t experts,
                                     int32_t* sorted_pairs, int32_t* counts, int32_t* scratch, void* stream) {
   using namespace hb200;
-  if (!expert_of_pair || !sorted_pairs || !counts || !scratch) return HB200_ERR_INVALID_ARGUMENT;
-  if (pairs < 0 || experts <= 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (pairs < 0 || experts <= 0 || !counts) return HB200_ERR_INVALID_ARGUMENT;
+  if (pairs > 0 && (!expert_of_pair || !sorted_pairs || !scratch)) return HB200_ERR_INVALID_ARGUMENT;
   if (experts > 1024 || pairs > 0x7fffffff) return HB200_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int blocks = int(ceil_div64(pairs, kSortThreads));
