@@ -513,6 +513,16 @@ def wl_quant(args, dev, rank, world, timer):
     b = 2 * t * h + t * h + 4 * t * (h // 128)
     ops["per_token_group_fp8_quant_16384x7168"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
 
+    sb = torch.empty(t, h // 128, dtype=torch.float32, device=dev)
+    r = graphed(lambda: hb.rms_norm_per_block_quant(q, x, w, sb, 1e-6, None, None, 128, False))[0]
+    tm = timer.run(r, max(10, args.steps // 4), 3)
+    b = 2 * t * h + 2 * h + t * h + 4 * t * (h // 128)
+    ops["rms_norm_per_block_quant_16384x7168"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
+    r = graphed(lambda: hb.dynamic_per_token_scaled_fp8_quant(q, x, s))[0]
+    tm = timer.run(r, max(10, args.steps // 4), 3)
+    b = 2 * t * h + t * h + 4 * t
+    ops["dynamic_per_token_scaled_fp8_quant_16384x7168"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
+
     host_q = torch.empty(t, h, dtype=torch.uint8).pin_memory()
 
     def e2e_step():
