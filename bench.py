@@ -284,6 +284,21 @@ def time_cpu(workload: str, budget_s: float = 10.0, steps: int | None = None, wa
     return work / dt / scale, unit, torch.get_num_threads(), f"{sample}; {reps} calls", dt
 
 
+def reference_config(args) -> dict:
+    """The configuration of the matching GPU arm (the CPU arm times a bounded sample of it, see cpu_baseline.sample)."""
+    if args.workload == "gemm":
+        cfg = {"workload": "gemm", **GEMM_CFG}
+    elif args.workload == "gemv":
+        cfg = {"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672", "batch": args.batch}
+    elif args.workload == "moe":
+        cfg = {"workload": "moe", **MOE_CFG}
+    else:
+        cfg = {"workload": "quant", "tokens": 16384, "hidden": 7168, "op": "rms_norm_dynamic_per_token_quant"}
+    cfg["parallelism"] = "host cores (rank 0 only)"
+    cfg["sampled"] = True
+    return cfg
+
+
 def run_reference(args) -> None:
     if int(os.environ.get("RANK", "0")) != 0:
         return
@@ -292,7 +307,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRICS[args.workload], "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": args.workload, "sampled": True},
+        "config": reference_config(args),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -186,7 +186,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32
   const int64_t chunks = hidden >> 3;
   const int64_t total = tokens * chunks;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int64_t t = i / chunks, c = i - t * chunks;
+    const int64_t t = total <= 0x7fffffff ? int64_t(uint32_t(i) / uint32_t(chunks)) : i / chunks, c = i - t * chunks;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < top_k; ++s) {
       const int64_t row = row_of_pair[t * top_k + s];
