@@ -89,6 +89,26 @@ __device__ __forceinline__ int owner_of(int unit, int total, int grid) {
   return c;
 }
 
+// The segments (tile, K blocks [kb0, kb1)) of a CTA's unit range [u_begin, u_end), in the order it works on them.
+// In natural order only the first and the last can be partial tiles.  With three or more segments and a partial
+// last one, that one is moved to second place: both partial tiles are then published (and, where this CTA
+// arrives last, finished) while the whole tiles still stream, and the kernel's tail is a plain tile write.
+struct Segments {
+  int first_tile, count, kb_total, u_begin, u_end;
+  bool tail_first;
+  __device__ Segments(int ub, int ue, int kb) : kb_total(kb), u_begin(ub), u_end(ue) {
+    first_tile = ub / kb;
+    count = ue > ub ? (ue - 1) / kb - first_tile + 1 : 0;
+    tail_first = count >= 3 && (ue % kb) != 0;
+  }
+  __device__ void get(int i, int& tile, int& kb0, int& kb1) const {
+    const int j = !tail_first ? i : (i == 0 ? 0 : (i == 1 ? count - 1 : i - 1));
+    tile = first_tile + j;
+    kb0 = j == 0 ? u_begin - first_tile * kb_total : 0;
+    kb1 = j == count - 1 ? u_end - tile * kb_total : kb_total;
+  }
+};
+
 template <int NCOLS, int TERMS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -113,6 +133,7 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   const int KB = g.num_kb;
   const int total = g.row_tiles * KB, grid = int(gridDim.x), cta = int(blockIdx.x);
   const int u_begin = range_start(cta, total, grid), u_end = range_start(cta + 1, total, grid);
+  const Segments segs(u_begin, u_end, KB);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -161,8 +182,18 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     uint32_t it = 0;
     bool ok = true;
     bool dependency_met = false;
-    for (int u = u_begin; u < u_end && ok;) {
-      const int tile = u / KB, kb0 = u - tile * KB, kb1 = min(KB, kb0 + (u_end - u));
+    // the activation tiles of the first `limit` iterations, whose weights were requested before the wait
+    auto issue_deferred_x = [&](uint32_t limit) {
+      uint32_t j = 0;
+      for (int i = 0; i < segs.count && j < limit; ++i) {
+        int tile, kb0, kb1;
+        segs.get(i, tile, kb0, kb1);
+        for (int kb = kb0; kb < kb1 && j < limit; ++kb, ++j) issue_x(j, kb);
+      }
+    };
+    for (int i = 0; i < segs.count && ok; ++i) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -170,11 +201,7 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           // every stage of the ring holds its weights: now wait for the activations and request them
           griddep_wait();
           dependency_met = true;
-          if (elect_one()) {
-            int uu = u_begin;
-            for (uint32_t j = 0; j < uint32_t(STAGES); ++j, ++uu)
-              issue_x(j, uu % KB);
-          }
+          if (elect_one()) issue_deferred_x(uint32_t(STAGES));
           __syncwarp();
         }
         if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag)) { ok = false; break; }
@@ -191,14 +218,10 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         }
         __syncwarp();
       }
-      u += kb1 - kb0;
     }
     if (!dependency_met && ok) {  // fewer K blocks than stages: nothing was deferred past the loop's end
       griddep_wait();
-      if (elect_one()) {
-        int uu = u_begin;
-        for (uint32_t j = 0; j < it; ++j, ++uu) issue_x(j, uu % KB);
-      }
+      if (elect_one()) issue_deferred_x(it);
       __syncwarp();
     }
   } else if (warp == 1) {
@@ -206,8 +229,9 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     constexpr uint32_t idesc = make_idesc_mxf4nvf4(kBlockM, NCOLS);
     uint32_t it = 0, sc = 0;
     bool ok = true;
-    for (int u = u_begin; u < u_end && ok; ++sc) {
-      const int tile = u / KB, kb0 = u - tile * KB, kb1 = min(KB, kb0 + (u_end - u));
+    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
       const int acc = sc & 1;
       const uint32_t acc_ph = (sc >> 1) & 1;
       if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
@@ -235,14 +259,14 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       }
       if (ok && elect_one()) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
       __syncwarp();
-      u += kb1 - kb0;
     }
   } else if (warp == 2) {
     // -------------------------------------------------------- scale copier
     uint32_t it = 0;
     bool ok = true;
-    for (int u = u_begin; u < u_end && ok;) {
-      const int tile = u / KB, kb0 = u - tile * KB, kb1 = min(KB, kb0 + (u_end - u));
+    for (int i = 0; i < segs.count && ok; ++i) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -262,7 +286,6 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         }
         __syncwarp();
       }
-      u += kb1 - kb0;
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue
@@ -289,9 +312,9 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       }
     };
 
-    for (int u = u_begin; u < u_end && ok; ++sc) {
-      const int tile = u / KB, kb0 = u - tile * KB, kb1 = min(KB, kb0 + (u_end - u));
-      u += kb1 - kb0;
+    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
       const int acc = sc & 1;
       const uint32_t acc_ph = (sc >> 1) & 1;
       if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_ph, abort_flag)) { ok = false; break; }
