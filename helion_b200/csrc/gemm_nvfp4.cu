@@ -459,8 +459,8 @@ extern "C" int hb200_nvfp4_scaled_matmul(const void* a_packed, const void* b_pac
 
 // Column-parallel form: this rank computes columns [col0, col0 + n) of the [m, n_total] result and writes them
 // into the buffer of every rank (out_ptrs[0..world), peer-mapped pointers of one symmetric allocation; entry
-// `rank` is this rank's own).  Every copy, local and remote, is a TMA store of the same staging box through
-// that rank's tensor map; nothing is loaded from peer memory.  Follow with hb200_peer_barrier before any rank reads its buffer.
+// `rank` is this rank's own).  Every copy, local and remote, is a bulk copy of a 512-byte tile row out of a
+// shared-memory staging box; nothing is loaded from peer memory.  Follow with hb200_peer_barrier before any rank reads its buffer.
 extern "C" int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, const void* scale_a,
                                             const void* scale_b, void* const* out_ptrs, int64_t world, int64_t rank,
                                             int64_t m, int64_t n, int64_t k, int64_t n_total, int64_t col0,

@@ -44,19 +44,31 @@ constexpr int kSfBase2 = kTileN;                          // after the 256 accum
 static_assert(kStageBytes2 % 1024 == 0, "stage must keep 1024-byte alignment");
 static_assert(kSfBase2 + kStages2 * kSfCols2 <= 512, "tensor memory budget exceeded");
 
+// named barrier of the four epilogue warps (128 threads) that share lane quarter q; barrier 0 is __syncthreads'
+__device__ __forceinline__ void quarter_bar(int q) { asm volatile("bar.sync %0, 128;" : : "r"(q + 1) : "memory"); }
+// the same barrier with a vote: true when `mine` holds in all 128 threads (a warp that gave up a bounded wait
+// takes the other three out of the loop with it instead of leaving them at the barrier)
+__device__ __forceinline__ bool quarter_bar_all(int q, bool mine) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, o;\n\tsetp.ne.u32 p, %2, 0;\n\tbar.red.and.pred o, %1, 128, p;\n\tselp.u32 %0, 1, 0, o;\n\t}"
+      : "=r"(r)
+      : "r"(q + 1), "r"(uint32_t(mine))
+      : "memory");
+  return r != 0;
+}
+
 struct PairArgs {
   void* out;
   int64_t ldc;
   int m, n, k;
   float alpha;
   int m_tiles, n_tiles;  // 256 x 256 tiles
-  // Tensor-parallel form: every tile is also written to the same place of each peer's buffer (TMA stores
-  // through the peers' own tensor maps; stores only, nothing is ever loaded from peer memory).
-  int n_peers;
-};
-
-struct PeerMaps {
-  CUtensorMap m[7];
+  // Tensor-parallel form: every tile row (512 contiguous bytes) is written to the same place of every rank's
+  // buffer with bulk copies from shared memory; stores only, nothing is ever loaded from peer memory.
+  int n_dst;
+  void* dst[8];  // the [m, ldc] buffers, this rank's first; the tile columns start at column col0 of them
+  int col0;
 };
 
 // TP: the tensor-parallel form (every tile also goes to the peers).  It trades one stage of the operand ring
@@ -65,14 +77,17 @@ template <typename OutT, bool TP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                       const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ PeerMaps peer_maps,
-                       const PairArgs g) {
+                       const __grid_constant__ CUtensorMap tmap_out, const PairArgs g) {
   constexpr int kS = TP ? kStages2 - 1 : kStages2;
-  constexpr int kBoxBytes = TP ? 4096 : 2048;  // one staging box per epilogue warp
+  // staging: one 32-row x 64-byte box per epilogue warp, or (TP) one 32-row x 512-byte box per lane quarter
+  // whose rows are padded to 528 bytes so that the 32 lanes of a warp spread over all banks
+  constexpr int kBoxBytes = 2048;
+  constexpr int kRowPitchTp = 528;
+  constexpr int kOutBytes = TP ? 4 * 32 * kRowPitchTp : 16 * kBoxBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_out = smem + kS * kStageBytes2;  // 1024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + 16 * kBoxBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + ((kOutBytes + 127) / 128) * 128);
   uint64_t* full_bar = bars;                 // used in the leader only
   uint64_t* empty_bar = bars + kS;     // one set per CTA
   uint64_t* sf_full_bar = bars + 2 * kS;   // scales of a stage are in tensor memory (leader only)
@@ -222,7 +237,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
       const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
-      if (!mbar_wait(smem_u32(tmem_full_bar), tc & 1, abort_flag)) { ok = false; break; }
+      const bool have = mbar_wait(smem_u32(tmem_full_bar), tc & 1, abort_flag);
+      if constexpr (!TP) {
+        if (!have) { ok = false; break; }
+      }
       tcgen05_fence_after();
       const int row0 = m_blk * 256 + int(rank) * 128 + quarter * 32;
       const int row = row0 + lane;
@@ -236,10 +254,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       if (lane == 0) mbar_arrive_cluster(free_bar);
       const int col = n_blk * kTileN + cgroup * 64;
       if constexpr (sizeof(OutT) == 2 && TP) {
-        // one box of 64 columns (128 bytes per row, 128-byte swizzle), stored to this rank and to every peer
-        if (lane == 0) bulk_wait_group_read0();
-        __syncwarp();
-        uint8_t* rowp = box + lane * 128;
+        // The four warps of a lane quarter fill one box of 32 rows x 256 columns; its first warp then sends every
+        // row, 512 contiguous bytes, to this rank and to every peer with one bulk copy per destination.
+        uint8_t* qbox = stage_out + quarter * (32 * kRowPitchTp);
+        if (cgroup == 0) bulk_wait_group_read0();  // each lane waits for the copies it issued for the last tile
+        if (!quarter_bar_all(quarter, have)) { ok = false; break; }  // the box is free (or a wait ran out)
+        uint8_t* rowp = qbox + lane * kRowPitchTp + cgroup * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -256,15 +276,19 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 p[j] = *reinterpret_cast<const uint32_t*>(&hh);
               }
             }
-            // 128-byte swizzle: 16-byte chunk index xor the row's low three bits
-            *reinterpret_cast<uint4*>(rowp + (((h * 4 + v) ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+            *reinterpret_cast<uint4*>(rowp + (h * 4 + v) * 16) = make_uint4(p[0], p[1], p[2], p[3]);
           }
         }
         fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmap_out, col, row0, smem_u32(box));
-          for (int p = 0; p < g.n_peers; ++p) tma_store_2d(&peer_maps.m[p], col, row0, smem_u32(box));
+        quarter_bar(quarter);  // the box is complete
+        if (cgroup == 0) {
+          const int tile_col = n_blk * kTileN;
+          if (row < g.m && tile_col < g.n) {
+            const uint32_t bytes = uint32_t(min(kTileN, g.n - tile_col)) * 2u;
+            const int64_t off = int64_t(row) * g.ldc + g.col0 + tile_col;
+            for (int d = 0; d < g.n_dst; ++d)
+              bulk_store(static_cast<OutT*>(g.dst[d]) + off, smem_u32(qbox + lane * kRowPitchTp), bytes);
+          }
           bulk_commit_group();
         }
       } else if constexpr (sizeof(OutT) == 2) {
@@ -306,8 +330,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       }
     }
     // peers read the result right after the barrier kernel that follows: wait for the writes themselves
-    if (lane == 0) {
-      if constexpr (TP) bulk_wait_group0(); else bulk_wait_group_read0();
+    if constexpr (TP) {
+      if (cgroup == 0) bulk_wait_group0();
+    } else {
+      if (lane == 0) bulk_wait_group_read0();
     }
   }
 
@@ -345,35 +371,33 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
   CUtensorMap tout;
   if (out_dtype != 2) {
     if ((ldc % 8) != 0 || reinterpret_cast<uintptr_t>(out) % 16) return HB200_ERR_UNSUPPORTED;
-    // tensor parallel: the map spans this rank's columns only, so partial tiles are clipped at their end
-    void* base = tp ? static_cast<void*>(static_cast<uint16_t*>(out) + peers.col0) : out;
-    if (!make_output_map16(&tout, base, m, n, ldc, out_dtype == 0, tp)) return HB200_ERR_CUDA;
+    if (tp) {
+      tout = ta;  // the tensor-parallel epilogue writes rows with bulk copies, not through a map
+    } else if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) {
+      return HB200_ERR_CUDA;
+    }
   } else {
     tout = ta;  // unused by the fp32 epilogue
   }
-  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0};
-  PeerMaps pm;
-  for (int i = 0; i < 7; ++i) pm.m[i] = tout;
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, {}, 0};
   if (tp) {
-    g.n_peers = peers.n_peers;
-    for (int i = 0; i < peers.n_peers; ++i) {
-      void* base = static_cast<void*>(static_cast<uint16_t*>(peers.ptr[i]) + peers.col0);
-      if (!make_output_map16(&pm.m[i], base, m, n, ldc, out_dtype == 0, true)) return HB200_ERR_CUDA;
-    }
+    g.col0 = int(peers.col0);
+    g.dst[g.n_dst++] = out;
+    for (int i = 0; i < peers.n_peers; ++i) g.dst[g.n_dst++] = peers.ptr[i];
   }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = g.m_tiles * g.n_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   constexpr size_t smem = size_t(kStages2) * kStageBytes2 + kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
-  constexpr size_t smem_tp = size_t(kStages2 - 1) * kStageBytes2 + 2 * kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
+  constexpr size_t smem_tp = size_t(kStages2 - 1) * kStageBytes2 + 4 * 32 * 528 + 128 + (3 * kStages2 + 2) * 8 + 16 + 1024;
   static_assert(smem <= 232448 && smem_tp <= 232448, "shared memory budget exceeded");
 #define HB200_PAIR(T, TPV, SMEM)                                                                              \
   do {                                                                                                        \
     auto kernel = nvfp4_gemm_pair_kernel<T, TPV>;                                                             \
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)) != cudaSuccess)  \
       return HB200_ERR_CUDA;                                                                                  \
-    kernel<<<2 * pairs, kThreads2, SMEM, stream>>>(ta, tb, tsa, tsb, tout, pm, g);                            \
+    kernel<<<2 * pairs, kThreads2, SMEM, stream>>>(ta, tb, tsa, tsb, tout, g);                            \
   } while (0)
   if (tp) {
     if (out_dtype == 0) HB200_PAIR(__nv_bfloat16, true, smem_tp);

@@ -112,6 +112,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All bulk groups of this thread have finished READING their shared-memory source.
+// contiguous bytes shared memory -> global (16-byte aligned addresses, size a multiple of 16), bulk-group completion
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" : : "l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+
 // all bulk stores of this thread have been written (not only read out of shared memory)
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -286,7 +286,7 @@ int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_packed, const 
  * GEMV and GEMM: rank r owns weight rows [col0, col0 + n) of n_total, computes that slice of the output and
  * stores it into the [rows, n_total] buffer of every rank.  out_ptrs[i] is rank i's buffer as mapped into
  * this process (CUDA peer mapping of one symmetric allocation).  Peer memory is only ever stored to (plain
- * stores in the GEMV, TMA stores in the GEMM); no load and no multicast touches it. */
+ * stores in the GEMV, bulk shared-to-global copies in the GEMM); no load and no multicast touches it. */
 int hb200_nvfp4_gemv_bf16in_tp(const void* weight_packed, const void* x_bf16, const void* weight_scale,
                                void* const* out_ptrs, int64_t world, int64_t n, int64_t k, int64_t batch,
                                int64_t n_total, int64_t col0, float alpha, void* stream);
