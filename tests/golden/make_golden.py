@@ -199,4 +199,6 @@ def main(ref_root: str) -> None:
 
 if __name__ == "__main__":
     os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <reference checkout>")
+    main(sys.argv[1])

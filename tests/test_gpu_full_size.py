@@ -1,4 +1,4 @@
-"""BASELINE-size runs checked through properties that do not need a full-size oracle: slices against the CPU
+"""Full-size runs (the benchmark configurations) checked through properties that do not need a full-size oracle: slices against the CPU
 oracle, invariance under permuting independent rows, symmetry, the largest code of every quantisation group,
 and run-to-run bit identity."""
 

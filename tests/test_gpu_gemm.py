@@ -72,7 +72,7 @@ def test_golden_w4a4_fixture(golden):
 
 
 def test_quantised_operands_config1_scaled_down():
-    """BASELINE config 1 at 1/8 scale: A ~ N(0,1) bf16, B ~ N(0,0.02), both NVFP4-quantised with global scales."""
+    """The dense-GEMM benchmark configuration at 1/8 scale: A ~ N(0,1) bf16, B ~ N(0,0.02), both NVFP4-quantised with global scales."""
     m = n = k = 1024
     g = torch.Generator().manual_seed(1)
     a = torch.randn(m, k, generator=g).to(torch.bfloat16)

@@ -30,7 +30,7 @@ def assert_close_rel(y: torch.Tensor, ref: torch.Tensor, tol: float = REL_TOL) -
 
 
 def make_case(n: int, k: int, seed: int, batch: int = 1):
-    """BASELINE-style inputs: W ~ N(0, 0.02) quantised to NVFP4 with a global scale, x ~ N(0, 1) bf16."""
+    """Benchmark-style inputs: W ~ N(0, 0.02) quantised to NVFP4 with a global scale, x ~ N(0, 1) bf16."""
     g = torch.Generator().manual_seed(seed)
     w = torch.randn(n, k, generator=g) * 0.02
     x = torch.randn(batch, k, generator=g).to(torch.bfloat16)
@@ -64,7 +64,7 @@ def test_bf16in_against_oracle(n, k):
     assert_close_rel(y, ref)
     y2 = hb.nvfp4_gemv_bf16in_batched(packed.to(DEV), x.to(DEV), scales.to(DEV), gs, use_mma=True)
     assert_close_rel(y2.reshape(-1), ref)
-    # the dequantise-then-fp32-matmul formulation named by the north star
+    # the dequantise-then-fp32-matmul formulation
     ref2 = O.nvfp4_gemm_bf16in(packed, x, scales, gs).reshape(-1)
     assert_close_rel(y, ref2)
 
