@@ -52,6 +52,8 @@ SIGNATURES: dict[str, list] = {
     "hb200_moe_combine": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _P],
     "hb200_rms_norm_per_block_quant": [_P, _P, _P, _P, _I64, _I64, c_float, _P, _P, c_int, _I64, _I64, c_int, c_int, _P],
     "hb200_dynamic_per_token_scaled_fp8_quant": [_P, _P, _P, _I64, _I64, _P, c_int, _P],
+    "hb200_moe_build_schedule_256": [_P, _I64, _P, _I64, _P, _P, _I64, _P, _P, _P],
+    "hb200_nvfp4_grouped_matmul_256": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, c_int, _P],
     "hb200_moe_sort_pairs": [_P, c_int, _I64, _I64, _P, _P, _P, _P],
     "hb200_nvfp4_grouped_matmul_silu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, _P],
     "hb200_nvfp4_quantize_rows_amax": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P],

@@ -517,6 +517,34 @@ extern "C" int hb200_nvfp4_grouped_matmul(const void* a_packed, const void* b_pa
   }
 }
 
+// hb200_nvfp4_grouped_matmul for a row layout whose groups are padded to multiples of 256 rows
+// (hb200_moe_build_schedule_256): runs on CTA pairs with 256 x 256 tiles, which halves the weight-tile traffic
+// per CTA; falls back to the 128-row kernel for shapes the pair kernel does not take (N % 256 != 0, fp32 out).
+extern "C" int hb200_nvfp4_grouped_matmul_256(const void* a_packed, const void* b_packed, const void* scale_a,
+                                              const void* scale_b, void* out, const int32_t* tile_info,
+                                              int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups, int64_t ldc,
+                                              const float* row_scale, const float* group_alpha, float alpha,
+                                              int out_dtype, void* stream) {
+  using namespace hb200;
+  if (!a_packed || !b_packed || !scale_a || !scale_b || !out || !tile_info) return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles < 0 || (max_m_tiles % 2) != 0 || n < 0 || k <= 0 || groups <= 0 || ldc < n || out_dtype < 0 ||
+      out_dtype > 2 || (k % 16) != 0)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(a_packed) % 16 || reinterpret_cast<uintptr_t>(b_packed) % 16 ||
+      reinterpret_cast<uintptr_t>(scale_a) % 16 || reinterpret_cast<uintptr_t>(scale_b) % 16 ||
+      reinterpret_cast<uintptr_t>(tile_info) % 8)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_m_tiles == 0 || n == 0) return HB200_OK;
+  if (max_m_tiles * 128 <= 0x7fffff00 && n * groups <= 0x7fffff00 && k <= 0x7fffff00) {
+    const int rc = pair::launch_grouped_pair(a_packed, b_packed, scale_a, scale_b, out, tile_info, max_m_tiles, n, k,
+                                             groups, ldc, row_scale, group_alpha, alpha, out_dtype,
+                                             static_cast<cudaStream_t>(stream));
+    if (rc != HB200_ERR_UNSUPPORTED) return rc;
+  }
+  return hb200_nvfp4_grouped_matmul(a_packed, b_packed, scale_a, scale_b, out, tile_info, max_m_tiles, n, k, groups,
+                                    ldc, row_scale, group_alpha, alpha, out_dtype, stream);
+}
+
 // The first expert GEMM of an NVFP4 MoE layer with SiLU-mul in the epilogue.  The weight rows are gate/up
 // interleaved in blocks of 128 (rows [256 j, 256 j + 128) = gate outputs [128 j, 128 j + 128), the next 128
 // rows the up rows of the same outputs), n counts all of them; y = bf16(silu(gate) * up) is written to

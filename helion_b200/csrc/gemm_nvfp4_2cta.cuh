@@ -69,7 +69,36 @@ struct PairArgs {
   int n_dst;
   void* dst[8];  // the [m, ldc] buffers, this rank's first; the tile columns start at column col0 of them
   int col0;
+  // Grouped form (tile_info != nullptr): the rows of A are laid out group after group, every group padded to a
+  // multiple of 256 rows; tile_info[t] = (group, valid rows) of 128-row tile t, so entries 2j and 2j+1 describe
+  // 256-row tile j.  B is [groups * n, K/2] with the groups' scale tiles back to back.
+  const int2* tile_info;
+  const float* row_scale;    // optional fp32 factor per row of A
+  const float* group_alpha;  // optional fp32 factor per group
 };
+
+struct PairTile {
+  int m_blk, n_blk, group;
+  bool valid;
+};
+
+__device__ __forceinline__ PairTile decode_pair_tile(const PairArgs& g, int tile) {
+  PairTile t;
+  if (g.tile_info != nullptr) {
+    // all column tiles of a 256-row tile run back to back: its group's weights stay in L2
+    t.m_blk = tile / g.n_tiles;
+    t.n_blk = tile - t.m_blk * g.n_tiles;
+    const int2 ti = g.tile_info[2 * t.m_blk];
+    t.group = ti.x;
+    t.valid = ti.x >= 0 && ti.y > 0;
+  } else {
+    t.m_blk = tile % g.m_tiles;
+    t.n_blk = tile / g.m_tiles;
+    t.group = 0;
+    t.valid = true;
+  }
+  return t;
+}
 
 // TP: the tensor-parallel form (every tile also goes to the peers).  It trades one stage of the operand ring
 // for output staging boxes twice as wide, so that a store over NVLink writes 128 contiguous bytes per row.
@@ -134,10 +163,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     uint32_t it = 0;
     bool ok = true;
     const uint32_t stage_bytes = kABytes2 + kBBytes2 + kSfaBytes2 + kSfbBytes2;
+    const int n_row_tiles = (g.n + 127) / 128;  // 128-row scale tiles of one group of B
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
+      const PairTile t = decode_pair_tile(g, tile);
+      if (!t.valid) continue;
+      const int m_blk = t.m_blk, n_blk = t.n_blk;
       const int a_row = m_blk * 256 + int(rank) * 128;
-      const int b_row = n_blk * kTileN + int(rank) * 128;
+      const int b_row = t.group * g.n + n_blk * kTileN + int(rank) * 128;
+      const int sfb_tile = t.group * n_row_tiles + n_blk * 2;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % kS;
         const uint32_t ph = (it / kS) & 1;
@@ -150,9 +183,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           tma_load_2d_pair(smem_u32(st + kBOff2), &tmap_b, kb * kBlockKBytes, b_row, bar);
           // scale atoms: row = atom index = row_tile * col_tiles + column tile
           tma_load_2d_pair(smem_u32(st + kSfaOff2), &tmap_sfa, 0, (a_row / 128) * col_tiles + kb * kAtomsPerStage, bar);
-          tma_load_2d_pair(smem_u32(st + kSfbOff2), &tmap_sfb, 0, (n_blk * 2) * col_tiles + kb * kAtomsPerStage, bar);
+          tma_load_2d_pair(smem_u32(st + kSfbOff2), &tmap_sfb, 0, sfb_tile * col_tiles + kb * kAtomsPerStage, bar);
           tma_load_2d_pair(smem_u32(st + kSfbOff2 + kSfaBytes2), &tmap_sfb, 0,
-                           (n_blk * 2 + 1) * col_tiles + kb * kAtomsPerStage, bar);
+                           (sfb_tile + 1) * col_tiles + kb * kAtomsPerStage, bar);
         }
         __syncwarp();
       }
@@ -163,8 +196,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       constexpr uint32_t idesc = make_idesc_mxf4nvf4(256, kTileN);
       bool ok = true;
       uint32_t it = 0, tc = 0;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
-        if (!mbar_wait(smem_u32(tmem_empty_bar), (tc & 1) ^ 1, abort_flag)) { ok = false; break; }
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!decode_pair_tile(g, tile).valid) continue;
+        const uint32_t tcur = tc++;
+        if (!mbar_wait(smem_u32(tmem_empty_bar), (tcur & 1) ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kS;
@@ -198,6 +233,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       bool ok = true;
       uint32_t it = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!decode_pair_tile(g, tile).valid) continue;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kS;
           const uint32_t ph = (it / kS) & 1;
@@ -235,15 +271,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     uint8_t* box = stage_out + (warp - 4) * kBoxBytes;
     uint32_t tc = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
-      const int m_blk = tile % g.m_tiles, n_blk = tile / g.m_tiles;
-      const bool have = mbar_wait(smem_u32(tmem_full_bar), tc & 1, abort_flag);
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const PairTile t = decode_pair_tile(g, tile);
+      if (!t.valid) continue;
+      const int m_blk = t.m_blk, n_blk = t.n_blk;
+      const uint32_t tcur = tc++;
+      const bool have = mbar_wait(smem_u32(tmem_full_bar), tcur & 1, abort_flag);
       if constexpr (!TP) {
         if (!have) { ok = false; break; }
       }
       tcgen05_fence_after();
       const int row0 = m_blk * 256 + int(rank) * 128 + quarter * 32;
       const int row = row0 + lane;
+      float alpha = g.alpha;
+      if (g.group_alpha != nullptr) alpha *= g.group_alpha[t.group];
+      if (g.row_scale != nullptr && row < g.m) alpha *= g.row_scale[row];
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + cgroup * 64;
       uint32_t r[2][32];
       tmem_ld_32x32b_x32(taddr, r[0]);
@@ -267,8 +309,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             uint32_t p[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * g.alpha;
-              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * g.alpha;
+              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * alpha;
+              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * alpha;
               if constexpr (std::is_same<OutT, __half>::value) {
                 p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
               } else {
@@ -303,8 +345,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             uint32_t p[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * g.alpha;
-              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * g.alpha;
+              const float lo = __uint_as_float(r[h][v * 8 + 2 * j]) * alpha;
+              const float hi = __uint_as_float(r[h][v * 8 + 2 * j + 1]) * alpha;
               if constexpr (std::is_same<OutT, __half>::value) {
                 p[j] = h2_as_u32(__floats2half2_rn(lo, hi));
               } else {
@@ -324,9 +366,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
       } else {
         if (row < g.m && col < g.n)
-          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r[0], g.alpha, g.n - col, vec_ok);
+          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col, r[0], alpha, g.n - col, vec_ok);
         if (row < g.m && col + 32 < g.n)
-          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r[1], g.alpha, g.n - col - 32, vec_ok);
+          store_row_chunk<OutT>(out + int64_t(row) * g.ldc + col + 32, r[1], alpha, g.n - col - 32, vec_ok);
       }
     }
     // peers read the result right after the barrier kernel that follows: wait for the writes themselves
@@ -379,7 +421,8 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
   } else {
     tout = ta;  // unused by the fp32 epilogue
   }
-  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, {}, 0};
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, {}, 0,
+             nullptr, nullptr, nullptr};
   if (tp) {
     g.col0 = int(peers.col0);
     g.dst[g.n_dst++] = out;
@@ -408,6 +451,43 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
     else HB200_PAIR(float, false, smem);
   }
 #undef HB200_PAIR
+  return launch_status();
+}
+
+// Grouped GEMM on CTA pairs: rows of A group after group, every group padded to a multiple of 256 rows
+// (max_m_tiles counts 128-row tiles and is even); bf16 or fp16 out.  HB200_ERR_UNSUPPORTED for shapes it
+// does not take.
+inline int launch_grouped_pair(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                               const int32_t* tile_info, int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups,
+                               int64_t ldc, const float* row_scale, const float* group_alpha, float alpha,
+                               int out_dtype, cudaStream_t stream) {
+  if ((max_m_tiles % 2) != 0 || (n % 256) != 0 || (k % 32) != 0 || out_dtype == 2 || (ldc % 8) != 0 ||
+      reinterpret_cast<uintptr_t>(out) % 16)
+    return HB200_ERR_UNSUPPORTED;
+  const int64_t m = max_m_tiles * 128;
+  CUtensorMap ta, tb, tsa, tsb, tout;
+  const int64_t col_tiles = (k / 16 + 3) / 4;
+  if (!make_operand_map(&ta, a, m, k / 2, 128) || !make_operand_map(&tb, b, n * groups, k / 2, 128)) return HB200_ERR_CUDA;
+  if (!make_scale_map(&tsa, sfa, max_m_tiles * col_tiles) || !make_scale_map(&tsb, sfb, (n / 128) * groups * col_tiles))
+    return HB200_ERR_CUDA;
+  if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
+  PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(max_m_tiles / 2), int(n / 256), 0, {}, 0,
+             reinterpret_cast<const int2*>(tile_info), row_scale, group_alpha};
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = g.m_tiles * g.n_tiles;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  if (pairs == 0) return HB200_OK;
+  constexpr size_t smem = size_t(kStages2) * kStageBytes2 + kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
+  if (out_dtype == 0) {
+    auto kernel = nvfp4_gemm_pair_kernel<__nv_bfloat16, false>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+    kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);
+  } else {
+    auto kernel = nvfp4_gemm_pair_kernel<__half, false>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+    kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);
+  }
   return launch_status();
 }
 

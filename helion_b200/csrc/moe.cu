@@ -14,7 +14,7 @@ namespace {
 //   row_of_pair[pair] : padded row of a (token, slot) pair
 __global__ void __launch_bounds__(1024)
 moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __restrict__ padded_offsets,
-                    int2* __restrict__ tile_info, int max_tiles) {
+                    int2* __restrict__ tile_info, int max_tiles, int pad_rows) {
   extern __shared__ int32_t sh[];  // offsets[experts + 1], padded[experts + 1]
   int32_t* off = sh;
   int32_t* pad = sh + experts + 1;
@@ -25,7 +25,7 @@ moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __
       pad[e] = p;
       const int32_t c = max(counts[e], 0);
       o += c;
-      p += (c + 127) / 128 * 128;
+      p += (c + pad_rows - 1) / pad_rows * pad_rows;
     }
     off[experts] = o;
     pad[experts] = p;
@@ -42,7 +42,7 @@ moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __
         if (pad[mid] <= row0) lo = mid; else hi = mid;
       }
       const int32_t cnt = off[lo + 1] - off[lo];
-      info = make_int2(lo, min(128, cnt - (row0 - pad[lo])));
+      info = make_int2(lo, max(0, min(128, cnt - (row0 - pad[lo]))));  // 0: a padding-only tile of the group
     }
     tile_info[t] = info;
   }
@@ -51,7 +51,7 @@ moe_schedule_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __
 // Padded row of every sorted position / pair; every CTA rebuilds the two offset tables from the counts.
 __global__ void __launch_bounds__(256)
 moe_row_map_kernel(const int32_t* __restrict__ counts, int experts, const int32_t* __restrict__ sorted_pairs,
-                   int pairs, int32_t* __restrict__ row_of_sorted, int32_t* __restrict__ row_of_pair) {
+                   int pairs, int32_t* __restrict__ row_of_sorted, int32_t* __restrict__ row_of_pair, int pad_rows) {
   extern __shared__ int32_t sh[];
   int32_t* off = sh;
   int32_t* pad = sh + experts + 1;
@@ -62,7 +62,7 @@ moe_row_map_kernel(const int32_t* __restrict__ counts, int experts, const int32_
       pad[e] = q;
       const int32_t c = max(counts[e], 0);
       o += c;
-      q += (c + 127) / 128 * 128;
+      q += (c + pad_rows - 1) / pad_rows * pad_rows;
     }
     off[experts] = o;
     pad[experts] = q;
@@ -215,10 +215,10 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32
 // Device-side replacement for the host bookkeeping of
 // moe_matmul_ogs_helion_kernel_args_gen (examples/moe_matmul_ogs.py:89-124), which
 // reads max_T_per_expert back to the host; nothing here synchronises.
-extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs,
-                                        int64_t pairs, int32_t* padded_offsets, int32_t* tile_info,
-                                        int64_t max_tiles, int32_t* row_of_sorted, int32_t* row_of_pair,
-                                        void* stream) {
+namespace {
+int build_schedule(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs, int64_t pairs,
+                   int32_t* padded_offsets, int32_t* tile_info, int64_t max_tiles, int32_t* row_of_sorted,
+                   int32_t* row_of_pair, int pad_rows, void* stream) {
   using namespace hb200;
   if (!counts || !sorted_pairs || !padded_offsets || !tile_info || !row_of_sorted || !row_of_pair)
     return HB200_ERR_INVALID_ARGUMENT;
@@ -228,12 +228,33 @@ extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, 
   const size_t smem = size_t(2 * (experts + 1)) * sizeof(int32_t);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   moe_schedule_kernel<<<1, 1024, smem, s>>>(counts, int(experts), padded_offsets, reinterpret_cast<int2*>(tile_info),
-                                           int(max_tiles));
+                                           int(max_tiles), pad_rows);
   if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
   if (pairs > 0)
     moe_row_map_kernel<<<unsigned(ceil_div64(pairs, 256)), 256, smem, s>>>(counts, int(experts), sorted_pairs,
-                                                                          int(pairs), row_of_sorted, row_of_pair);
+                                                                          int(pairs), row_of_sorted, row_of_pair, pad_rows);
   return launch_status();
+}
+}  // namespace
+
+extern "C" int hb200_moe_build_schedule(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs,
+                                        int64_t pairs, int32_t* padded_offsets, int32_t* tile_info,
+                                        int64_t max_tiles, int32_t* row_of_sorted, int32_t* row_of_pair,
+                                        void* stream) {
+  return build_schedule(counts, experts, sorted_pairs, pairs, padded_offsets, tile_info, max_tiles, row_of_sorted,
+                        row_of_pair, 128, stream);
+}
+
+// The same schedule with every expert padded to a multiple of 256 rows, for the CTA-pair grouped GEMM whose
+// tiles are 256 rows: tile_info still has one entry per 128 rows (entries 2j and 2j+1 belong to one expert;
+// the second may have 0 valid rows).  max_tiles >= ceil(pairs / 128) + 2 * experts always suffices.
+extern "C" int hb200_moe_build_schedule_256(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs,
+                                            int64_t pairs, int32_t* padded_offsets, int32_t* tile_info,
+                                            int64_t max_tiles, int32_t* row_of_sorted, int32_t* row_of_pair,
+                                            void* stream) {
+  if ((max_tiles % 2) != 0) return HB200_ERR_INVALID_ARGUMENT;
+  return build_schedule(counts, experts, sorted_pairs, pairs, padded_offsets, tile_info, max_tiles, row_of_sorted,
+                        row_of_pair, 256, stream);
 }
 
 // Copies per-token NVFP4 rows (codes, swizzled scales, global scale) into the expert-sorted padded layout:

@@ -103,11 +103,15 @@ class MoeSchedule:
     sorted_pairs: Tensor    # int32 [T * top_k]
     row_of_sorted: Tensor   # int32 [T * top_k]
     row_of_pair: Tensor     # int32 [T * top_k]
+    pad: int = 128          # every expert's rows are padded to a multiple of this (128, or 256 for CTA-pair tiles)
 
 
-def build_schedule(experts_per_token: Tensor, num_experts: int) -> MoeSchedule:
+def build_schedule(experts_per_token: Tensor, num_experts: int, pad: int = 128) -> MoeSchedule:
     """Sort the (token, slot) pairs by expert (stable, as examples/moe_matmul_ogs.py:107-109 does for
-    top-1) and lay the experts out in 128-row padded groups; all on the device."""
+    top-1) and lay the experts out in groups padded to ``pad`` rows (128, or 256 for the CTA-pair grouped
+    GEMM); all on the device."""
+    if pad not in (128, 256):
+        raise ValueError(f"pad must be 128 or 256, got {pad}")
     _require_cuda(experts_per_token)
     flat = experts_per_token.reshape(-1).contiguous()
     pairs = flat.numel()
@@ -121,18 +125,21 @@ def build_schedule(experts_per_token: Tensor, num_experts: int) -> MoeSchedule:
     with torch.cuda.device(dev):
         _lib.call("hb200_moe_sort_pairs", flat.data_ptr(), int(flat.dtype is torch.int64), pairs, num_experts,
                   sorted_pairs.data_ptr(), counts.data_ptr(), scratch.data_ptr(), _stream())
-    max_tiles = ceil_div(pairs, 128) + num_experts  # bound that does not depend on the routing
+    # bound that does not depend on the routing (in 128-row units; even for 256-row padding)
+    max_tiles = ceil_div(pairs, 128) + num_experts * (pad // 128)
+    max_tiles += max_tiles % (pad // 128)
     tile_info = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
     padded_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     row_of_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)
     row_of_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         _lib.call(
-            "hb200_moe_build_schedule", counts.data_ptr(), num_experts, sorted_pairs.data_ptr(), pairs,
+            "hb200_moe_build_schedule" if pad == 128 else "hb200_moe_build_schedule_256",
+            counts.data_ptr(), num_experts, sorted_pairs.data_ptr(), pairs,
             padded_offsets.data_ptr(), tile_info.data_ptr(), max_tiles, row_of_sorted.data_ptr(),
             row_of_pair.data_ptr(), _stream(),
         )
-    return MoeSchedule(max_tiles, tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair)
+    return MoeSchedule(max_tiles, tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair, pad)
 
 
 def _quantize_rows(x: Tensor, k: int, sched: MoeSchedule, src_div: int, item_scale: Tensor | None, silu_mul: bool,
@@ -185,7 +192,8 @@ def grouped_matmul(a_codes: Tensor, a_scales: Tensor, w: GroupedNvfp4Weight, sch
     code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]
     with torch.cuda.device(a_codes.device):
         _lib.call(
-            "hb200_nvfp4_grouped_matmul", a_codes.data_ptr(), w.packed.data_ptr(), a_scales.data_ptr(),
+            "hb200_nvfp4_grouped_matmul_256" if sched.pad == 256 else "hb200_nvfp4_grouped_matmul",
+            a_codes.data_ptr(), w.packed.data_ptr(), a_scales.data_ptr(),
             w.scales.data_ptr(), out.data_ptr(), sched.tile_info.data_ptr(), sched.max_tiles, w.n, w.k,
             w.experts, w.n, None if row_scale is None else row_scale.data_ptr(), w.global_scale.data_ptr(),
             1.0, code, _stream(),
@@ -239,6 +247,8 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
     if w_gate_up.k != h or w_down.k != inter or w_down.n != h or w_down.experts != e:
         raise ValueError("expert weight shapes do not match the activations")
     weights, experts = route_top_k(router_logits, top_k)
+    # (build_schedule(..., pad=256) would put the second GEMM on CTA pairs: 313 against 350 us on the benchmark
+    # shape, but the first GEMM's static tile round-robin then meets the padding-only tiles and loses more)
     sched = build_schedule(experts, e)
     # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
     w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()

@@ -213,6 +213,18 @@ int hb200_rms_norm_per_block_quant(void* result, const void* input, const void* 
 int hb200_dynamic_per_token_scaled_fp8_quant(void* result, const void* input, void* scale, int64_t tokens,
                                              int64_t hidden, const float* scale_ub, int in_is_fp16, void* stream);
 
+/* hb200_moe_build_schedule with every expert padded to a multiple of 256 rows (max_tiles, still in 128-row
+ * units, must be even; ceil(pairs / 128) + 2 * experts always suffices), and hb200_nvfp4_grouped_matmul over
+ * such a layout: 256 x 256 tiles on CTA pairs (cta_group::2), which halves the weight-tile traffic per CTA.
+ * Falls back to the 128-row kernel where the pair kernel does not apply (N % 256 != 0, fp32 output). */
+int hb200_moe_build_schedule_256(const int32_t* counts, int64_t experts, const int32_t* sorted_pairs, int64_t pairs,
+                                 int32_t* padded_offsets, int32_t* tile_info, int64_t max_tiles,
+                                 int32_t* row_of_sorted, int32_t* row_of_pair, void* stream);
+int hb200_nvfp4_grouped_matmul_256(const void* a_packed, const void* b_packed, const void* scale_a,
+                                   const void* scale_b, void* out, const int32_t* tile_info, int64_t max_m_tiles,
+                                   int64_t n, int64_t k, int64_t groups, int64_t ldc, const float* row_scale,
+                                   const float* group_alpha, float alpha, int out_dtype, void* stream);
+
 /* Stable sort of the (token, slot) pairs by expert plus the per-expert counts, on the device: what
  * moe_matmul_ogs_helion_kernel_args_gen computes with bincount + argsort and a host read
  * (examples/moe_matmul_ogs.py:96-117).  expert_of_pair: one entry per pair, int64 when idx_is_i64 != 0 (what
