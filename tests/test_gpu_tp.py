@@ -68,6 +68,30 @@ def test_gemv_slices_land_in_every_buffer(batch, world):
     assert torch.equal(bufs[0][:, n // world : 2 * (n // world)], y0)
 
 
+@pytest.mark.parametrize("batch,world", [(2, 2), (8, 4), (1, 2)])
+def test_tensor_core_gemv_slices_land_in_every_buffer(batch, world):
+    n, k = 2048, 4096
+    codes, scales = random_weight(n, k, 31 + batch)
+    x = torch.randn(batch, k, generator=torch.Generator().manual_seed(batch)).to(torch.bfloat16).to(DEV)
+    bufs = [torch.full((batch, n), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    ptrs = ptr_array(bufs)
+    stream = torch.cuda.current_stream().cuda_stream
+    n_local = n // world
+    need = _lib.load().hb200_nvfp4_gemv_tc_workspace_bytes(n_local, k, batch, 4)
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    for rank in range(world):
+        w_r, s_r = D.shard_weight_rows(codes, scales, world, rank)
+        _lib.call("hb200_nvfp4_gemv_bf16in_tc", w_r.data_ptr(), x.data_ptr(), s_r.data_ptr(), ptrs, world, n_local, k,
+                  batch, n, rank * n_local, 0.5, ws.data_ptr(), need, stream)
+    assert device_status_ok()
+    for b in bufs[1:]:
+        assert torch.equal(b, bufs[0])
+    want = torch.cat([hb.nvfp4_gemv_bf16in_batched(*D.shard_weight_rows(codes, scales, world, r)[:1], x,
+                                                   D.shard_weight_rows(codes, scales, world, r)[1], 0.5, path="tc")
+                      for r in range(world)], dim=1)
+    assert torch.equal(bufs[0], want)
+
+
 @pytest.mark.parametrize("m,n,k,world", [(256, 1024, 512, 2), (512, 1024, 1024, 4), (300, 1024, 256, 2), (256, 1040, 256, 2)])
 def test_matmul_slices_land_in_every_buffer(m, n, k, world):
     g = torch.Generator().manual_seed(m + n + k)
