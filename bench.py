@@ -13,6 +13,9 @@ Workloads (``--workload``):
          expert-parallel over N GPUs.
   quant  the fused FP8 quant producers at 16384 tokens (RMSNorm hidden 7168 as the headline; the others in
          ``ops``); metric TB/s.
+  scaled_mm  the row-wise scaled FP8 GEMM on the twelve (K, N) decode weight shapes the reference tunes it on,
+         --batch tokens each (default 16; the reference sweeps 16 and 64), bias and per-tensor scales as in its
+         sweep; a step is one pass over all twelve (715 MB of weights); metric TB/s; replicas only over N GPUs.
 
 Timing: every step is bracketed by its own CUDA-event pair on the launching stream and the L2 is flushed
 (a 256 MB write) between steps, outside the pairs; ms_per_step is the mean over K steps and the max over
@@ -39,11 +42,19 @@ sys.path.insert(0, str(ROOT))
 LAYER_70B = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
 MOE_CFG = dict(tokens=8192, hidden=4096, experts=128, top_k=8, inter=1536)
 GEMM_CFG = dict(m=8192, n=8192, k=8192)
+# (K, N) of the reference's scaled_mm sweep (pretuned_kernels/scaled_mm/scaled_mm.py:167-180)
+SCALED_MM_KN = [(2048, 4096), (2048, 2048), (2048, 12288), (6144, 2048), (4096, 6144), (4096, 4096), (4096, 24576),
+                (12288, 4096), (5120, 10240), (5120, 5120), (5120, 51200), (25600, 5120)]
 
 
 def gemv_bytes(n: int, k: int, m: int = 1) -> int:
     """Algorithmic HBM bytes of one NVFP4 GEMV: packed codes + block scales + activations + outputs."""
     return n * k // 2 + n * k // 16 + 2 * m * k + 2 * m * n
+
+
+def scaled_mm_bytes(m: int, k: int, n: int) -> int:
+    """Algorithmic HBM bytes of one FP8 scaled_mm with a bf16 output and bias: weight, activations, bias, output."""
+    return n * k + m * k + 2 * n + 2 * m * n
 
 
 def moe_flops(c=MOE_CFG) -> int:
@@ -259,10 +270,23 @@ def cpu_moe():
     return (lambda: O.nvfp4_moe(x, logits, k, gp, gs, gg, dp, ds, dg)), flops, f"{t} tokens, {e} experts, top-{k} (same hidden/intermediate sizes)"
 
 
+def cpu_scaled_mm():
+    from oracle import oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    m, k, n = 16, 4096, 4096
+    g = torch.Generator().manual_seed(6)
+    a = ((0.5 + torch.rand(m, k, generator=g)) / 64).to(torch.float8_e4m3fn)
+    b = ((0.5 + torch.rand(n, k, generator=g)) / 64).to(torch.float8_e4m3fn).t()
+    sa, sb = torch.rand(1, 1, generator=g) + 0.5, torch.rand(1, 1, generator=g) + 0.5
+    bias = (torch.rand(n, generator=g) - 0.5).to(torch.bfloat16)
+    return (lambda: O.scaled_mm(a, b, sa, sb, bias)), scaled_mm_bytes(m, k, n), f"the {m}x{k}x{n} shape of the twelve"
+
+
 CPU_WORKLOADS = {"gemm": (cpu_gemm, 1e12, "TFLOP/s"), "gemv": (cpu_gemv, 1e12, "TB/s"), "quant": (cpu_quant, 1e12, "TB/s"),
-                 "moe": (cpu_moe, 1e12, "TFLOP/s")}
+                 "moe": (cpu_moe, 1e12, "TFLOP/s"), "scaled_mm": (cpu_scaled_mm, 1e12, "TB/s")}
 METRICS = {"gemm": "nvfp4_gemm_tflops", "gemv": "nvfp4_gemv_hbm_throughput", "quant": "fp8_quant_producer_hbm_throughput",
-           "moe": "nvfp4_moe_tflops"}
+           "moe": "nvfp4_moe_tflops", "scaled_mm": "fp8_scaled_mm_hbm_throughput"}
 
 
 def time_cpu(workload: str, budget_s: float = 10.0, steps: int | None = None, warmup: int = 1):
@@ -292,6 +316,8 @@ def reference_config(args) -> dict:
         cfg = {"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672", "batch": args.batch}
     elif args.workload == "moe":
         cfg = {"workload": "moe", **MOE_CFG}
+    elif args.workload == "scaled_mm":
+        cfg = {"workload": "scaled_mm", "tokens": args.batch if args.batch > 1 else 16, "kn_shapes": len(SCALED_MM_KN)}
     else:
         cfg = {"workload": "quant", "tokens": 16384, "hidden": 7168, "op": "rms_norm_dynamic_per_token_quant"}
     cfg["parallelism"] = "host cores (rank 0 only)"
@@ -558,6 +584,69 @@ def wl_quant(args, dev, rank, world, timer):
                         "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
 
 
+def wl_scaled_mm(args, dev, rank, world, timer):
+    import math
+
+    import helion_b200 as hb
+    from oracle import oracle as O
+
+    m = args.batch if args.batch > 1 else 16
+    g = torch.Generator(device=dev).manual_seed(7)
+    cases = []
+    for k, n in SCALED_MM_KN:
+        sc = 1.0 / math.sqrt(k)
+        a = (sc * (0.5 + torch.rand(m, k, device=dev, generator=g))).to(torch.float8_e4m3fn)
+        b = (sc * (0.5 + torch.rand(n, k, device=dev, generator=g))).to(torch.float8_e4m3fn).t()
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        sa = torch.rand(1, 1, device=dev, generator=g) + 0.5
+        sb = torch.rand(1, 1, device=dev, generator=g) + 0.5
+        bias = (0.5 * (torch.rand(n, device=dev, generator=g) - 0.5)).to(torch.bfloat16)
+        cases.append((a, b, c, sa, sb, bias))
+    nbytes = sum(scaled_mm_bytes(m, k, n) for k, n in SCALED_MM_KN)
+
+    def step():
+        for a, b, c, sa, sb, bias in cases:
+            hb.scaled_mm(c, a, b, sa, sb, bias)
+
+    step()
+    a, b, c, sa, sb, bias = cases[1]
+    parity = rel_err(c, O.scaled_mm(a.cpu(), b.cpu(), sa.cpu(), sb.cpu(), bias.cpu()))
+    ms = timer.run(graphed(step)[0], args.steps, args.warmup)
+
+    # the largest weight (5120 x 51200, 262 MB: larger than the L2) alone, for the roofline of the kernel
+    big = cases[10]
+    one = graphed(lambda: hb.scaled_mm(big[2], big[0], big[1], big[3], big[4], big[5]))[0]
+    big_ms = timer.run(one, max(10, args.steps // 2), 3)
+    big_bytes = scaled_mm_bytes(m, *SCALED_MM_KN[10])
+    per_shape = {}
+    for (k, n), cs in zip(SCALED_MM_KN, cases):
+        r = graphed(lambda cs=cs: hb.scaled_mm(cs[2], cs[0], cs[1], cs[3], cs[4], cs[5]))[0]
+        tm = timer.run(r, max(10, args.steps // 4), 3)
+        per_shape[f"{m}x{k}x{n}"] = {"us": tm * 1e3, "GBps": scaled_mm_bytes(m, k, n) / (tm * 1e-3) / 1e9}
+
+    host_a = [cs[0].cpu().view(torch.uint8).pin_memory() for cs in cases]
+    host_c = [torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for _, n in SCALED_MM_KN]
+
+    def e2e_step():
+        for ha, hc, (a, b, c, sa, sb, bias) in zip(host_a, host_c, cases):
+            a.view(torch.uint8).copy_(ha, non_blocking=True)
+            hb.scaled_mm(c, a, b, sa, sb, bias)
+            hc.copy_(c, non_blocking=True)
+
+    e2e_ms = timer.run(e2e_step, max(3, args.steps // 5), 3)
+    peaks = measured_peaks()
+    ach = big_bytes / (big_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": "fp8_scaled_mm_kernel", "launch": f"{m}x5120x51200", "achieved": ach,
+            "peak": peaks["hbm_gbs"], "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s",
+            "frac": ach / peaks["hbm_gbs"], "traffic": ncu_traffic(f"scaled_mm_{m}x5120x51200")}
+    return dict(value=world * nbytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms,
+                e2e_value=world * nbytes / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
+                h2d=sum(h.numel() for h in host_a), d2h=sum(h.numel() * 2 for h in host_c), launches=len(cases),
+                roofline=roof, parity=parity, extra={"shapes": per_shape}, dtype="e4m3 operands, fp32 accumulate, bf16 out",
+                config={"workload": "scaled_mm", "tokens": m, "kn_shapes": len(SCALED_MM_KN),
+                        "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
+
+
 def wl_moe(args, dev, rank, world, timer):
     import helion_b200 as hb  # noqa: F401
     from helion_b200 import dist as D
@@ -617,7 +706,7 @@ def wl_moe(args, dev, rank, world, timer):
                 config={"workload": "moe", **c, "parallelism": f"ep{world}" if world > 1 else "single", "l2": "flushed between steps"})
 
 
-WORKLOADS = {"gemm": wl_gemm, "gemv": wl_gemv, "quant": wl_quant, "moe": wl_moe}
+WORKLOADS = {"gemm": wl_gemm, "gemv": wl_gemv, "quant": wl_quant, "moe": wl_moe, "scaled_mm": wl_scaled_mm}
 
 
 def run_gpu(args) -> None:
@@ -646,7 +735,7 @@ def run_gpu(args) -> None:
         line = {
             "metric": METRICS[args.workload], "value": r["value"], "unit": r["unit"], "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"], "higher_is_better": True,
-            "scaling": "strong" if args.workload != "quant" else "weak", "vs_baseline": None, "dtype": r["dtype"],
+            "scaling": "strong" if args.workload not in ("quant", "scaled_mm") else "weak", "vs_baseline": None, "dtype": r["dtype"],
             "data": "synthetic", "config": r["config"],
             "e2e": {"value": r["e2e_value"], "unit": r["unit"], "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": r["d2h"], "ms_per_step": r["e2e_ms"]},

@@ -61,11 +61,15 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_scaled_matmul_tp": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_float, c_int, _P],
     "hb200_peer_barrier": [_P, _I64, _I64, _P, _P],
     "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],
+    "hb200_fp8_scaled_mm_workspace_bytes": [_I64, _I64, _I64],
+    "hb200_fp8_scaled_mm": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_int, c_int, c_int, c_int, _P,
+                            _I64, _P],
     "hb200_nvfp4_gemv_bf16in_tc": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P, _I64, _P],
     "hb200_nvfp4_gemv_fp4in_tc": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P, _I64, _P],
     "hb200_nvfp4_gemv_bf16in_tc_builtin_scratch": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
 }
-_RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64}
+_RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64,
+             "hb200_fp8_scaled_mm_workspace_bytes": c_int64}
 
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None

@@ -1,0 +1,426 @@
+// Row-wise scaled FP8 matrix multiply for sm_100a (tcgen05 kind::f8f6f4, fp32 accumulate):
+//   c[m, n] = cast(scale_a[m] * acc[m, n] * scale_b[n]) + bias[n],   acc = a[m, :] . b[:, n]
+// a [M, K] row-major, b [K, N] with unit stride along K (the weight stored [N, K]); scales per tensor or per
+// row / column; the bias is added after the cast, in the output type.  This is the operator of
+// pretuned_kernels/scaled_mm/scaled_mm.py:18-84.
+//
+// The shapes that operator is tuned on are decode shapes (16 or 64 tokens against weights of tens of
+// megabytes), so the kernel streams the WEIGHT through the tensor core's M side: a tile is 128 weight rows
+// by up to 256 tokens, the accumulator holds c transposed (lane = n, column = m), and when the tiles alone
+// cannot fill the GPU the K range of a tile is split over several CTAs.  Each of those writes its fp32
+// partial to the workspace; the last to arrive adds them in K order (a fixed order: results do not depend on
+// timing) and finishes the tile.  Large M runs through the same kernel, 256 tokens per tile, with no split.
+//
+// Persistent CTAs of 192 threads: warp 0 TMA producer (weights 128 x 128 bytes, tokens cols x 128 bytes, 128-byte
+// swizzle, no multicast), warp 1 MMA issuer (128 x cols x 32 per instruction), warps 2-5 epilogue; two
+// accumulators in tensor memory; every wait bounded.
+#include "gemm_common.cuh"
+
+#include <type_traits>
+
+namespace hb200 {
+
+__device__ int g_device_status_fp8 = 0;
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kFp8Threads = 192;
+constexpr int kFp8WBytes = 128 * 128;   // one stage of weights: 128 rows x 128 K-bytes
+constexpr int kFp8MaxCols = 256;        // tokens per tile
+constexpr int kFp8MaxStages = 10;
+constexpr int kFp8CounterBytes = 16384; // arrival counters at the start of the workspace
+constexpr int kFp8MaxSplitTiles = kFp8CounterBytes / 4;
+
+struct Fp8Args {
+  void* out;
+  int64_t ldc;
+  const float* scale_a;  // [M] or [1]
+  const float* scale_b;  // [N] or [1]
+  const void* bias;      // [N] in the output type, or nullptr
+  float* partials;       // [tiles * splits][cols][128] fp32 (splits > 1 only)
+  unsigned int* counters;
+  int m, n, k;
+  int scale_a_per_row, scale_b_per_col;
+  int n_tiles, m_chunks, cols;       // cols = tokens per tile, a multiple of 16
+  int splits, kb_per_split, num_kb;  // K blocks of 128 elements
+  int stages, stage_bytes;
+};
+
+__device__ __forceinline__ void mma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Instruction descriptor of kind::f8f6f4: fp32 accumulator (bits 4-5 = 1), operand format at bits 7-9 and 10-12
+// (0 = e4m3, 1 = e5m2), both operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int format) {
+  return (1u << 4) | (uint32_t(format) << 7) | (uint32_t(format) << 10) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void fp8_epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+__device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float as_float(float v) { return v; }
+
+template <typename OutT>
+__global__ void __launch_bounds__(kFp8Threads, 1)
+fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                     const Fp8Args g, const int format) {
+  constexpr int ACC = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + g.stages * g.stage_bytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kFp8MaxStages;
+  uint64_t* tmem_full_bar = bars + 2 * kFp8MaxStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = g.stages;
+  const int units = g.n_tiles * g.m_chunks * g.splits;
+  const int acc_stride = g.cols < 32 ? 32 : g.cols;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < ACC; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // unit -> (weight row tile, token chunk, K split); the splits of a tile are neighbours
+  auto decode = [&](int u, int& n_blk, int& m_blk, int& kb0, int& kb1) {
+    const int split = u % g.splits, tile = u / g.splits;
+    n_blk = tile / g.m_chunks;
+    m_blk = tile % g.m_chunks;
+    kb0 = split * g.kb_per_split;
+    kb1 = min(g.num_kb, kb0 + g.kb_per_split);
+  };
+
+  if (warp == 0) {
+    uint32_t it = 0;
+    bool ok = true;
+    const uint32_t tx = kFp8WBytes + g.cols * 128;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      int n_blk, m_blk, kb0, kb1;
+      decode(u, n_blk, m_blk, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % stages;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        uint8_t* st = smem + s * g.stage_bytes;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(bar, tx);
+          tma_load_2d(smem_u32(st), &tmap_w, kb * 128, n_blk * 128, bar);
+          tma_load_2d(smem_u32(st + kFp8WBytes), &tmap_x, kb * 128, m_blk * g.cols, bar);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t idesc = make_idesc_f8(128, g.cols, format);
+    uint32_t it = 0, uc = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++uc) {
+      int n_blk, m_blk, kb0, kb1;
+      decode(u, n_blk, m_blk, kb0, kb1);
+      const int acc = uc % ACC;
+      if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((uc / ACC) & 1) ^ 1, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * acc_stride;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % stages;
+        if (!mbar_wait(smem_u32(&full_bar[s]), (it / stages) & 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        uint8_t* st = smem + s * g.stage_bytes;
+        const uint32_t w_addr = smem_u32(st), x_addr = smem_u32(st + kFp8WBytes);
+        const int k_left = g.k - kb * 128;
+        const int steps = k_left >= 128 ? 4 : (k_left + 31) / 32;  // K tail: TMA zero-fills past K
+        if (elect_one()) {
+          for (int a = 0; a < steps; ++a) {
+            // 32 K-elements = 32 bytes further along the 128-byte swizzled row
+            const uint64_t wdesc = make_smem_desc(w_addr + a * 32, 16, 1024, kSwizzle128B);
+            const uint64_t xdesc = make_smem_desc(x_addr + a * 32, 16, 1024, kSwizzle128B);
+            mma_f8(tmem_d, wdesc, xdesc, idesc, (kb != kb0 || a != 0) ? 1u : 0u);
+          }
+          tcgen05_commit(smem_u32(&empty_bar[s]));
+        }
+        __syncwarp();
+      }
+      if (ok && elect_one()) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r_in = quarter * 32 + lane;  // weight row inside the tile = accumulator lane
+    OutT* out = static_cast<OutT*>(g.out);
+    const OutT* bias = static_cast<const OutT*>(g.bias);
+    const float sa_all = g.scale_a[0], sb_all = g.scale_b[0];
+    uint32_t uc = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++uc) {
+      int n_blk, m_blk, kb0, kb1;
+      decode(u, n_blk, m_blk, kb0, kb1);
+      const int acc = uc % ACC;
+      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), (uc / ACC) & 1, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int n_idx = n_blk * 128 + r_in;
+      const bool n_ok = n_idx < g.n;
+      const int m0 = m_blk * g.cols;
+      const float sb = g.scale_b_per_col ? (n_ok ? g.scale_b[n_idx] : 0.f) : sb_all;
+      const float bias_n = (bias && n_ok) ? as_float(bias[n_idx]) : 0.f;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * acc_stride;
+
+      // 16 accumulator columns (tokens m0 + c0 ...) of this thread's weight row
+      auto finalize = [&](const float (&v)[16], int c0) {
+        if (!n_ok) return;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m_idx = m0 + c0 + j;
+          if (m_idx < g.m) {
+            const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : sa_all;
+            OutT o = from_float<OutT>(sb * (sa * v[j]));
+            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
+            out[int64_t(m_idx) * g.ldc + n_idx] = o;
+          }
+        }
+      };
+      auto load16 = [&](int c0, float (&v)[16]) {
+        uint32_t r0[8], r1[8];
+        tmem_ld_32x32b_x8(taddr + c0, r0);
+        tmem_ld_32x32b_x8(taddr + c0 + 8, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] = __uint_as_float(r0[j]);
+          v[8 + j] = __uint_as_float(r1[j]);
+        }
+      };
+
+      if (g.splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < g.cols; c0 += 16) {
+          float v[16];
+          load16(c0, v);
+          if (c0 + 16 >= g.cols) {  // everything is in registers: hand the accumulator back
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+          }
+          finalize(v, c0);
+        }
+        continue;
+      }
+
+      // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
+      const int tile = u / g.splits;
+      float* slot = g.partials + int64_t(u) * g.cols * 128;
+#pragma unroll 1
+      for (int c0 = 0; c0 < g.cols; c0 += 16) {
+        float v[16];
+        load16(c0, v);
+        if (c0 + 16 >= g.cols) {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) __stcg(slot + (c0 + j) * 128 + r_in, v[j]);
+      }
+      __threadfence();
+      fp8_epilogue_bar();
+      if (r_in == 0) {
+        *last_flag = atomicAdd(&g.counters[tile], 1u) + 1u == unsigned(g.splits);
+      }
+      fp8_epilogue_bar();
+      const bool last = *last_flag != 0;
+      fp8_epilogue_bar();  // the flag may be rewritten by the next unit
+      if (!last) continue;
+      __threadfence();
+      const float* first = g.partials + int64_t(tile) * g.splits * g.cols * 128;
+#pragma unroll 1
+      for (int c0 = 0; c0 < g.cols; c0 += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        for (int p = 0; p < g.splits; ++p) {  // ascending K: a fixed summation order
+          const float* src = first + int64_t(p) * g.cols * 128;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (c0 + j) * 128 + r_in);
+        }
+        finalize(v, c0);
+      }
+      if (r_in == 0) g.counters[tile] = 0u;
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicMin(&g_device_status_fp8, HB200_ERR_DEVICE_TIMEOUT);
+}
+
+// K-major byte matrix [rows, K] with a row pitch of `pitch` bytes; box = 128 bytes x box_rows, 128-byte swizzle.
+bool make_fp8_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t pitch, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(pitch)};
+  const cuuint32_t box[2] = {128, cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Fp8Plan {
+  int n_tiles, m_chunks, cols, num_kb, splits, kb_per_split, stages, stage_bytes, grid;
+  int64_t workspace_bytes;
+};
+
+Fp8Plan make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms) {
+  Fp8Plan p{};
+  p.n_tiles = int((n + 127) / 128);
+  p.m_chunks = int((m + kFp8MaxCols - 1) / kFp8MaxCols);
+  p.cols = m >= kFp8MaxCols ? kFp8MaxCols : int((m + 15) / 16 * 16);
+  p.num_kb = int((k + 127) / 128);
+  const int64_t tiles = int64_t(p.n_tiles) * p.m_chunks;
+  // Split K only while the tiles alone leave SMs idle, and keep at least two K blocks per piece.
+  int splits = 1;
+  if (tiles < sms && tiles <= kFp8MaxSplitTiles) {
+    splits = int((sms + tiles - 1) / tiles);
+    const int most = p.num_kb / 2 > 1 ? p.num_kb / 2 : 1;
+    if (splits > most) splits = most;
+  }
+  p.kb_per_split = (p.num_kb + splits - 1) / splits;
+  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.stage_bytes = kFp8WBytes + ((p.cols * 128 + 1023) / 1024) * 1024;
+  const int fit = (232448 - 2048) / p.stage_bytes;
+  p.stages = fit > kFp8MaxStages ? kFp8MaxStages : fit;
+  const int64_t units = tiles * p.splits;
+  p.grid = int(units < sms ? units : sms);
+  p.workspace_bytes = p.splits > 1 ? kFp8CounterBytes + units * p.cols * 128 * 4 : 0;
+  return p;
+}
+
+int device_sms() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
+
+template <typename OutT>
+int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
+               cudaStream_t s) {
+  auto kernel = fp8_scaled_mm_kernel<OutT>;
+  const size_t smem = size_t(p.stages) * p.stage_bytes + (2 * kFp8MaxStages + 4) * 8 + 32 + 1024;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+  kernel<<<p.grid, kFp8Threads, smem, s>>>(tw, tx, g, format);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace hb200
+
+extern "C" int64_t hb200_fp8_scaled_mm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  using namespace hb200;
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return make_fp8_plan(m, n, k, device_sms()).workspace_bytes;
+}
+
+extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const float* scale_a, const float* scale_b,
+                                   const void* bias, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                   int64_t ldc, int scale_a_per_row, int scale_b_per_col, int fp8_format,
+                                   int out_dtype, void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace hb200;
+  if (!a || !b || !c || !scale_a || !scale_b) return HB200_ERR_INVALID_ARGUMENT;
+  if (m <= 0 || n <= 0 || k <= 0 || lda < k || ldb < k || ldc < n) return HB200_ERR_INVALID_ARGUMENT;
+  if (fp8_format != 0 && fp8_format != 1) return HB200_ERR_INVALID_ARGUMENT;
+  if (out_dtype < 0 || out_dtype > 2) return HB200_ERR_INVALID_ARGUMENT;
+  // TMA: 16-byte aligned bases and row pitches
+  if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b) % 16 || (lda % 16) != 0 || (ldb % 16) != 0)
+    return HB200_ERR_UNSUPPORTED;
+  if (m > 0x7fffff00 || n > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  const Fp8Plan p = make_fp8_plan(m, n, k, device_sms());
+  if (int64_t(p.n_tiles) * p.m_chunks * p.splits > 0x7fffffff) return HB200_ERR_UNSUPPORTED;
+  if (p.workspace_bytes > 0) {
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 16) return HB200_ERR_WORKSPACE;
+    if (workspace_bytes < p.workspace_bytes) return HB200_ERR_WORKSPACE;
+  }
+  CUtensorMap tw, tx;
+  if (!make_fp8_map(&tw, b, n, k, ldb, 128)) return HB200_ERR_CUDA;
+  if (!make_fp8_map(&tx, a, m, k, lda, p.cols)) return HB200_ERR_CUDA;
+  Fp8Args g{};
+  g.out = c;
+  g.ldc = ldc;
+  g.scale_a = scale_a;
+  g.scale_b = scale_b;
+  g.bias = bias;
+  g.counters = static_cast<unsigned int*>(workspace);
+  g.partials = p.workspace_bytes > 0
+                   ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kFp8CounterBytes) : nullptr;
+  g.m = int(m);
+  g.n = int(n);
+  g.k = int(k);
+  g.scale_a_per_row = scale_a_per_row != 0;
+  g.scale_b_per_col = scale_b_per_col != 0;
+  g.n_tiles = p.n_tiles;
+  g.m_chunks = p.m_chunks;
+  g.cols = p.cols;
+  g.splits = p.splits;
+  g.kb_per_split = p.kb_per_split;
+  g.num_kb = p.num_kb;
+  g.stages = p.stages;
+  g.stage_bytes = p.stage_bytes;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == 0) return launch_fp8<__nv_bfloat16>(tw, tx, g, p, fp8_format, s);
+  if (out_dtype == 1) return launch_fp8<__half>(tw, tx, g, p, fp8_format, s);
+  return launch_fp8<float>(tw, tx, g, p, fp8_format, s);
+}
+
+namespace hb200 {
+// Sticky status of this translation unit's kernels, folded into hb200_device_status().
+int fp8_device_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_status_fp8, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  if (reset && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_device_status_fp8, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+  }
+  return v;
+}
+}  // namespace hb200

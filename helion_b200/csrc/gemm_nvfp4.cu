@@ -585,6 +585,7 @@ namespace hb200 {
 int f16_device_status(int reset);
 int peer_device_status(int reset);
 int gemv_tc_device_status(int reset);
+int fp8_device_status(int reset);
 }
 
 extern "C" int hb200_device_status(int reset) {
@@ -597,5 +598,6 @@ extern "C" int hb200_device_status(int reset) {
   const int w = hb200::f16_device_status(reset);
   const int p = hb200::peer_device_status(reset);
   const int t = hb200::gemv_tc_device_status(reset);
-  return v != 0 ? v : (w != 0 ? w : (p != 0 ? p : t));
+  const int f = hb200::fp8_device_status(reset);
+  return v != 0 ? v : (w != 0 ? w : (p != 0 ? p : (t != 0 ? t : f)));
 }

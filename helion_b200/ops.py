@@ -70,6 +70,7 @@ def _check_numel(name: str, t: Tensor, expected: int) -> None:
 # ------------------------------------------------------------------ custom ops
 # Workspace of the tensor-core GEMV (activation terms, split-K partials, tile counters): one zero-filled
 # buffer per (device, stream), grown on demand.  Calls on one stream are ordered, so they can share it.
+_SCALED_MM_OUT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 _TC_WORKSPACES: dict[tuple[int, int], Tensor] = {}
 _TC_MIN_WEIGHT_ELEMS = 1 << 21  # below this a launch is latency-bound and the SIMT kernels do as well
 
@@ -240,6 +241,30 @@ def _dyn_token_quant_op(result: Tensor, input: Tensor, scale: Tensor, scale_ub: 
 
 @_dyn_token_quant_op.register_fake
 def _(result, input, scale, scale_ub):  # noqa: A002
+    return None
+
+
+@torch.library.custom_op("helion_b200::scaled_mm", mutates_args=("c",))
+def _scaled_mm_op(c: Tensor, a: Tensor, b_nk: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None) -> None:
+    _require_cuda(c, a, b_nk, scale_a, scale_b, bias)
+    m, k = a.shape
+    n = b_nk.shape[0]
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        need = lib.hb200_fp8_scaled_mm_workspace_bytes(m, n, k)
+        ws = tc_workspace(a.device, need) if need else None
+        _lib.call(
+            "hb200_fp8_scaled_mm",
+            a.data_ptr(), b_nk.data_ptr(), c.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias),
+            m, n, k, a.stride(0), b_nk.stride(0), c.stride(0),
+            int(scale_a.numel() > 1), int(scale_b.numel() > 1),
+            int(a.dtype is torch.float8_e5m2), _SCALED_MM_OUT[c.dtype],
+            _ptr(ws), ws.numel() if ws is not None else 0, _stream(),
+        )
+
+
+@_scaled_mm_op.register_fake
+def _(c, a, b_nk, scale_a, scale_b, bias):
     return None
 
 
@@ -618,6 +643,50 @@ def dynamic_per_token_scaled_fp8_quant(
     if not (result.is_contiguous() and scale.is_contiguous()):
         raise ValueError("result and scale must be contiguous")
     _dyn_token_quant_op(result, input.contiguous(), scale, scale_ub)
+
+
+def scaled_mm(
+    c: Tensor, a: Tensor, b: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None = None,
+) -> None:
+    """FP8 scaled matrix multiply ``c = scale_a * (a @ b) * scale_b + bias``, in place on ``c``.
+
+    Drop-in for ``scaled_mm`` (pretuned_kernels/scaled_mm/scaled_mm.py:18-84): ``a [M, K]`` with unit stride
+    along K, ``b [K, N]`` with ``b.stride(0) == 1`` (the weight stored ``[N, K]``), scales ``[1]``, ``[1, 1]``,
+    ``[M]`` / ``[M, 1]`` (``scale_a``) or ``[N]`` / ``[N, 1]`` (``scale_b``), optional ``bias [N]`` in ``c``'s dtype,
+    added after the cast to that dtype.  The reference's assertions are kept; its int8 form is not built.
+    """
+    M, K = a.shape  # noqa: N806
+    N = b.shape[1]  # noqa: N806
+    assert N > 0 and K > 0 and M > 0
+    assert b.shape[0] == K
+    assert a.dtype == b.dtype
+    assert a.stride(1) == 1
+    assert b.stride(0) == 1
+    scale_a = scale_a.reshape(-1, 1) if scale_a.dim() <= 1 else scale_a
+    scale_b = scale_b.reshape(-1, 1) if scale_b.dim() <= 1 else scale_b
+    assert scale_a.dtype == scale_b.dtype and scale_a.is_floating_point()
+    assert scale_a.shape[1] == 1 and (scale_a.shape[0] == 1 or scale_a.shape[0] == M)
+    assert scale_b.shape[1] == 1 and (scale_b.shape[0] == 1 or scale_b.shape[0] == N)
+    out_dtype = c.dtype
+    assert out_dtype.is_floating_point
+    if bias is not None:
+        assert bias.numel() == N and bias.dtype == out_dtype
+    if a.dtype not in (_FP8, torch.float8_e5m2):
+        raise TypeError(f"a and b must be float8_e4m3fn or float8_e5m2, got {a.dtype}")
+    if out_dtype not in _SCALED_MM_OUT:
+        raise TypeError(f"c must be bfloat16, float16 or float32, got {out_dtype}")
+    if c.shape != (M, N) or c.stride(1) != 1:
+        raise ValueError("c must be [M, N] with unit stride along N")
+    b_nk = b.t()  # [N, K], unit stride along K
+    if a.stride(0) % 16 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b_nk.stride(0) % 16 or b_nk.data_ptr() % 16:
+        b_nk = b_nk.contiguous()
+    if K % 16:
+        raise ValueError(f"K must be a multiple of 16 (row pitch of the TMA loads), got {K}")
+    scale_a = scale_a.reshape(-1).to(torch.float32).contiguous()
+    scale_b = scale_b.reshape(-1).to(torch.float32).contiguous()
+    _scaled_mm_op(c, a, b_nk, scale_a, scale_b, None if bias is None else bias.reshape(-1).contiguous())
 
 
 def per_token_group_fp8_quant(

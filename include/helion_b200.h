@@ -197,6 +197,25 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* ------------------------------------------------ row-wise scaled FP8 GEMM
+ * scaled_mm (pretuned_kernels/scaled_mm/scaled_mm.py:18-84):
+ *   c[m, n] = out_dtype(scale_b[n] * (scale_a[m] * sum_k a[m, k] * b[k, n])) + bias[n]
+ * on the tensor cores (tcgen05 kind::f8f6f4, fp32 accumulate).  a [M, K] with row pitch lda, b given as its
+ * K-major storage [N, K] with row pitch ldb (the reference's b [K, N] with b.stride(0) == 1), c [M, N] with row
+ * pitch ldc, pitches in elements.  scale_a / scale_b are fp32, one value or one per row of a / column of b
+ * (scale_a_per_row / scale_b_per_col); bias is [N] in the output type or null and is added after the cast, as
+ * the reference does.  fp8_format 0 = e4m3, 1 = e5m2 (both operands); out_dtype 0 bf16, 1 fp16, 2 fp32.
+ * Needs 16-byte aligned a and b and lda % 16 == ldb % 16 == 0 (HB200_ERR_UNSUPPORTED otherwise).
+ * When few weight tiles would leave SMs idle (decode shapes) the K range is split across CTAs and summed in a
+ * fixed order through `workspace`: caller-owned device memory of hb200_fp8_scaled_mm_workspace_bytes(m, n, k)
+ * bytes (0 when no split is used) whose first 16 KB are zero before the first call and are left zero by every
+ * call; HB200_ERR_WORKSPACE if it is missing or too small.  Calls that share a workspace must not overlap. */
+int64_t hb200_fp8_scaled_mm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const float* scale_a, const float* scale_b,
+                        const void* bias, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                        int scale_a_per_row, int scale_b_per_col, int fp8_format, int out_dtype, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+
 /* rms_norm_per_block_quant (pretuned_kernels/rms_norm_per_block_quant/rms_norm_per_block_quant.py:38-140):
  * the RMSNorm of hb200_rms_norm_dynamic_per_token_quant with one scale per group of 64 or 128 elements of the
  * hidden dimension (true division for fp8, reciprocal multiply and round for int8).  Scale (t, g) is written at

@@ -287,6 +287,28 @@ def rms_norm_per_block_quant(
     return q, s, new_res
 
 
+def scaled_mm(
+    a: Tensor, b: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> Tensor:
+    """scaled_mm (pretuned_kernels/scaled_mm/scaled_mm.py:18-84): fp32 accumulation of ``a [M, K] @ b [K, N]``
+    (FP8 operands, products exact), ``scale_a * acc`` then ``scale_b.T * acc`` in fp32, the cast to the output
+    type, and only then the bias, added in the output type.  The accumulation runs in fp64 and is rounded to
+    fp32 once: the reference leaves the summation order to the tiling."""
+    m, _k = a.shape
+    n = b.shape[1]
+    acc = (a.to(torch.float64) @ b.to(torch.float64)).to(torch.float32)
+    sa = scale_a.reshape(-1, 1).to(torch.float32)
+    sb = scale_b.reshape(-1, 1).to(torch.float32)
+    assert sa.shape[0] in (1, m) and sb.shape[0] in (1, n)
+    acc = sa * acc
+    acc = sb.T * acc
+    c = acc.to(out_dtype)
+    if bias is not None:
+        c = c + bias.reshape(1, -1).to(out_dtype)
+    return c
+
+
 def rms_norm_row_rms(x: Tensor, epsilon: float, residual: Tensor | None = None) -> Tensor:
     """The fp32 ``rms`` factor of each row as the function above computes it (test helper)."""
     xf = x.to(torch.float32)

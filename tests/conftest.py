@@ -41,6 +41,13 @@ class Golden:
     def bf16(self, key: str) -> torch.Tensor:
         return self.raw(key).view(torch.bfloat16)
 
+    def f16(self, key: str) -> torch.Tensor:
+        return self.raw(key).view(torch.float16)
+
+    def typed(self, key: str, tag: str) -> torch.Tensor:
+        """``tag`` in bf16 / f16 / f32."""
+        return {"bf16": self.bf16, "f16": self.f16, "f32": self.raw}[tag](key)
+
     def e4m3(self, key: str) -> torch.Tensor:
         return self.raw(key).view(torch.float8_e4m3fn)
 

@@ -180,6 +180,30 @@ def main(ref_root: str) -> None:
                 out[f"rpb_newres_{gs}"] = _np(r)
     np.savez_compressed(HERE / "quant_siblings.npz", **out)
 
+    # ---- row-wise scaled FP8 GEMM: the reference KERNEL itself, run by its interpreter on the CPU ----
+    smm = _load(pk / "scaled_mm" / "scaled_mm.py", "ref_scaled_mm")
+    out = {}
+    torch.manual_seed(33)
+    for tag, (m, k, n) in (("a", (16, 256, 128)), ("b", (20, 208, 72)), ("c", (3, 64, 40))):
+        scale = 1.0 / k**0.5
+        a = (scale * (0.5 + torch.rand(m, k))).to(torch.float8_e4m3fn)
+        b = (scale * (torch.rand(n, k) - 0.5)).to(torch.float8_e4m3fn).t()
+        out[f"smm_{tag}_a"], out[f"smm_{tag}_b_nk"] = _np(a), _np(b.t())
+        for stag, (sa, sb) in (
+            ("tensor", (torch.rand(1, 1) + 0.5, torch.rand(1, 1) + 0.5)),
+            ("rows", (torch.rand(m, 1) + 0.5, torch.rand(n, 1) + 0.5)),
+            ("mixed", (torch.rand(1) + 0.5, torch.rand(n) + 0.5)),
+        ):
+            out[f"smm_{tag}_{stag}_sa"], out[f"smm_{tag}_{stag}_sb"] = _np(sa), _np(sb)
+            for dtag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+                bias = (torch.rand(n) - 0.5).to(dt)
+                out[f"smm_{tag}_{stag}_{dtag}_bias"] = _np(bias)
+                for btag, bb in (("bias", bias), ("nobias", None)):
+                    c = torch.zeros(m, n, dtype=dt)
+                    smm.scaled_mm(c, a, b, sa, sb, bb)
+                    out[f"smm_{tag}_{stag}_{dtag}_{btag}_c"] = _np(c)
+    np.savez_compressed(HERE / "scaled_mm.npz", **out)
+
     # ---- MoE / grouped GEMM references ------------------------------------------------------------
     out = {}
     torch.manual_seed(8)
@@ -199,6 +223,7 @@ def main(ref_root: str) -> None:
 
 if __name__ == "__main__":
     os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
+    os.environ.setdefault("HELION_INTERPRET", "1")  # kernels called below run in the reference's CPU interpreter
     if len(sys.argv) != 2:
         raise SystemExit("usage: make_golden.py <reference checkout>")
     main(sys.argv[1])

@@ -112,6 +112,28 @@ def test_sibling_quant_producer_references(golden):
         assert _eq_bits(new_res, g.bf16(f"rpb_newres_{gs}"))
 
 
+def test_scaled_mm_reference_kernel(golden):
+    """The oracle against outputs of the reference's scaled_mm kernel itself (run by its CPU interpreter)."""
+    g = golden("scaled_mm.npz")
+    ulp = {"bf16": 2.0**-8, "f16": 2.0**-11, "f32": 2.0**-20}
+    for tag in "abc":
+        a, b = g.e4m3(f"smm_{tag}_a"), g.e4m3(f"smm_{tag}_b_nk").t()
+        for stag in ("tensor", "rows", "mixed"):
+            sa, sb = g.raw(f"smm_{tag}_{stag}_sa"), g.raw(f"smm_{tag}_{stag}_sb")
+            for dtag in ("bf16", "f16", "f32"):
+                bias = g.typed(f"smm_{tag}_{stag}_{dtag}_bias", dtag)
+                for btag, bb in (("bias", bias), ("nobias", None)):
+                    ref = g.typed(f"smm_{tag}_{stag}_{dtag}_{btag}_c", dtag)
+                    got = O.scaled_mm(a, b, sa, sb, bb, ref.dtype)
+                    assert got.dtype == ref.dtype and got.shape == ref.shape
+                    # the kernel sums fp32 in tile order, the oracle rounds an exact sum once: outputs may sit
+                    # on either side of a rounding boundary, by one place of the larger of result and bias
+                    mag = ref.float().abs() if bb is None else torch.maximum(ref.float().abs(), bb.float().abs()[None, :])
+                    assert bool(((got.float() - ref.float()).abs() <= ulp[dtag] * mag + 1e-30).all())
+                    if dtag != "f32":
+                        assert float((got == ref).float().mean()) >= 0.97
+
+
 def test_moe_references(golden):
     g = golden("moe.npz")
     a, w, top1 = g.bf16("moe_a"), g.bf16("moe_w"), g.raw("moe_top1")
