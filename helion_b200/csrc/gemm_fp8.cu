@@ -6,10 +6,11 @@
 //
 // The shapes that operator is tuned on are decode shapes (16 or 64 tokens against weights of tens of
 // megabytes), so the kernel streams the WEIGHT through the tensor core's M side: a tile is 128 weight rows
-// by up to 256 tokens, the accumulator holds c transposed (lane = n, column = m), and when the tiles alone
-// cannot fill the GPU the K range of a tile is split over several CTAs.  Each of those writes its fp32
-// partial to the workspace; the last to arrive adds them in K order (a fixed order: results do not depend on
-// timing) and finishes the tile.  Large M runs through the same kernel, 256 tokens per tile, with no split.
+// by up to 256 tokens and the accumulator holds c transposed (lane = n, column = m).  The (tile, K block) units
+// are dealt to the CTAs in contiguous ranges of equal length (stream-K), so every SM streams the same number
+// of bytes whatever the tile count.  A tile whose K range is shared has each of its CTAs write an fp32 partial to
+// the workspace; the last to arrive adds them in K order (a fixed order: results do not depend on timing) and
+// finishes the tile.  Large M runs through the same kernel, 256 tokens per tile.
 //
 // Persistent CTAs of 192 threads: warp 0 TMA producer (weights 128 x 128 bytes, tokens cols x 128 bytes, 128-byte
 // swizzle, no multicast), warp 1 MMA issuer (128 x cols x 32 per instruction), warps 2-5 epilogue; two
@@ -31,7 +32,8 @@ constexpr int kFp8WBytes = 128 * 128;   // one stage of weights: 128 rows x 128 
 constexpr int kFp8MaxCols = 256;        // tokens per tile
 constexpr int kFp8MaxStages = 10;
 constexpr int kFp8CounterBytes = 16384; // arrival counters at the start of the workspace
-constexpr int kFp8MaxSplitTiles = kFp8CounterBytes / 4;
+constexpr int kFp8MaxTiles = kFp8CounterBytes / 4;
+constexpr int kFp8MinUnits = 4;         // K blocks per CTA below which more CTAs only add partial sums
 
 struct Fp8Args {
   void* out;
@@ -39,12 +41,15 @@ struct Fp8Args {
   const float* scale_a;  // [M] or [1]
   const float* scale_b;  // [N] or [1]
   const void* bias;      // [N] in the output type, or nullptr
-  float* partials;       // [tiles * splits][cols][128] fp32 (splits > 1 only)
-  unsigned int* counters;
+  float* partials;       // two slots per CTA of [cols][128] fp32
+  unsigned int* counters;  // arrivals per tile; zero whenever no call is in flight
   int m, n, k;
   int scale_a_per_row, scale_b_per_col;
-  int n_tiles, m_chunks, cols;       // cols = tokens per tile, a multiple of 16
-  int splits, kb_per_split, num_kb;  // K blocks of 128 elements
+  int n_tiles, m_chunks, cols;  // cols = tokens per tile, a multiple of 16
+  int num_kb;                   // K blocks of 128 elements per tile
+  int whole_tiles;
+  int vec_ok;  // 16-byte stores into c are possible
+  int cluster;  // CTAs per tile in the cluster form, 0 otherwise
   int stages, stage_bytes;
 };
 
@@ -67,6 +72,14 @@ __host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int format) {
 
 __device__ __forceinline__ void fp8_epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Arrival on a tile's counter: releases what the CTA's threads wrote before the barrier they passed on the way
+// here, and acquires what earlier arrivers released, for the threads that pass the next barrier.
+__device__ __forceinline__ unsigned int arrive_acq_rel(unsigned int* counter) {
+  unsigned int old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
+
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
@@ -75,7 +88,17 @@ __device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162f
 __device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
 __device__ __forceinline__ float as_float(float v) { return v; }
 
-template <typename OutT>
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+// CLUSTER: the small-problem form.  One tile per thread-block cluster, its K range split over the cluster's CTAs;
+// every CTA leaves its fp32 partial in its own shared memory, and after a cluster barrier each CTA adds up, in
+// rank order, a slice of the tile's columns from all of them through distributed shared memory.  No workspace,
+// no counters, no trip through L2.
+template <typename OutT, bool CLUSTER>
 __global__ void __launch_bounds__(kFp8Threads, 1)
 fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                      const Fp8Args g, const int format) {
@@ -89,12 +112,35 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   uint64_t* tmem_empty_bar = tmem_full_bar + ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* fix = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [0] last arriver? [1] first owner [2] last owner
+  uint8_t* turn_base = reinterpret_cast<uint8_t*>(bars) + 256;  // 2 KB per epilogue warp
+  float* stash = reinterpret_cast<float*>(turn_base + 4 * 2048);  // CLUSTER: this CTA's partial, [cols][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = g.stages;
-  const int units = g.n_tiles * g.m_chunks * g.splits;
+  const int KB = g.num_kb;
+  const int total = g.n_tiles * g.m_chunks * KB, grid = int(gridDim.x), cta = int(blockIdx.x);
+  int u_begin, u_end;
+  if constexpr (CLUSTER) {
+    const int rank = int(cluster_ctarank()), tile = cta / g.cluster;
+    u_begin = tile * KB + range_start(rank, KB, g.cluster);
+    u_end = tile * KB + range_start(rank + 1, KB, g.cluster);
+  } else {
+    // beyond the counters' reach (thousands of tiles) whole tiles are dealt instead: nothing is shared then
+    u_begin = g.whole_tiles ? range_start(cta, total / KB, grid) * KB : range_start(cta, total, grid);
+    u_end = g.whole_tiles ? range_start(cta + 1, total / KB, grid) * KB : range_start(cta + 1, total, grid);
+  }
+  const Segments segs(u_begin, u_end, KB);
   const int acc_stride = g.cols < 32 ? 32 : g.cols;
+
+  // one stage of (tile, K block): the stage's barrier is told the bytes, both boxes are requested
+  auto issue = [&](int s, int tile, int kb) {
+    const uint32_t bar = smem_u32(&full_bar[s]);
+    uint8_t* st = smem + s * g.stage_bytes;
+    mbar_arrive_expect_tx(bar, uint32_t(kFp8WBytes + g.cols * 128));
+    tma_load_2d(smem_u32(st), &tmap_w, kb * 128, (tile / g.m_chunks) * 128, bar);
+    tma_load_2d(smem_u32(st + kFp8WBytes), &tmap_x, kb * 128, (tile % g.m_chunks) * g.cols, bar);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -107,8 +153,13 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
     *abort_flag = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_x);
+    // The ring is empty: its first round of loads goes out now, while tensor memory is still being set up.
+    int it = 0;
+    for (int i = 0; i < segs.count && it < stages; ++i) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
+      for (int kb = kb0; kb < kb1 && it < stages; ++kb, ++it) issue(it, tile, kb);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), 512);
@@ -119,44 +170,29 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // unit -> (weight row tile, token chunk, K split); the splits of a tile are neighbours
-  auto decode = [&](int u, int& n_blk, int& m_blk, int& kb0, int& kb1) {
-    const int split = u % g.splits, tile = u / g.splits;
-    n_blk = tile / g.m_chunks;
-    m_blk = tile % g.m_chunks;
-    kb0 = split * g.kb_per_split;
-    kb1 = min(g.num_kb, kb0 + g.kb_per_split);
-  };
-
   if (warp == 0) {
     uint32_t it = 0;
     bool ok = true;
-    const uint32_t tx = kFp8WBytes + g.cols * 128;
-    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-      int n_blk, m_blk, kb0, kb1;
-      decode(u, n_blk, m_blk, kb0, kb1);
+    for (int i = 0; i < segs.count && ok; ++i) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (it < uint32_t(stages)) continue;  // requested during set-up
         const int s = it % stages;
         if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        uint8_t* st = smem + s * g.stage_bytes;
-        if (elect_one()) {
-          mbar_arrive_expect_tx(bar, tx);
-          tma_load_2d(smem_u32(st), &tmap_w, kb * 128, n_blk * 128, bar);
-          tma_load_2d(smem_u32(st + kFp8WBytes), &tmap_x, kb * 128, m_blk * g.cols, bar);
-        }
+        if (elect_one()) issue(s, tile, kb);
         __syncwarp();
       }
     }
   } else if (warp == 1) {
     const uint32_t idesc = make_idesc_f8(128, g.cols, format);
-    uint32_t it = 0, uc = 0;
+    uint32_t it = 0, sc = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++uc) {
-      int n_blk, m_blk, kb0, kb1;
-      decode(u, n_blk, m_blk, kb0, kb1);
-      const int acc = uc % ACC;
-      if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((uc / ACC) & 1) ^ 1, abort_flag)) { ok = false; break; }
+    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
+      const int acc = sc % ACC;
+      if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((sc / ACC) & 1) ^ 1, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + acc * acc_stride;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -187,13 +223,16 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     OutT* out = static_cast<OutT*>(g.out);
     const OutT* bias = static_cast<const OutT*>(g.bias);
     const float sa_all = g.scale_a[0], sb_all = g.scale_b[0];
-    uint32_t uc = 0;
+    const int first_tile = u_begin / KB;
+    const int64_t slot_floats = int64_t(g.cols) * 128;
+    uint32_t sc = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++uc) {
-      int n_blk, m_blk, kb0, kb1;
-      decode(u, n_blk, m_blk, kb0, kb1);
-      const int acc = uc % ACC;
-      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), (uc / ACC) & 1, abort_flag)) { ok = false; break; }
+    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+      int tile, kb0, kb1;
+      segs.get(i, tile, kb0, kb1);
+      const int n_blk = tile / g.m_chunks, m_blk = tile % g.m_chunks;
+      const int acc = sc % ACC;
+      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), (sc / ACC) & 1, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
       const int n_idx = n_blk * 128 + r_in;
       const bool n_ok = n_idx < g.n;
@@ -201,9 +240,37 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       const float sb = g.scale_b_per_col ? (n_ok ? g.scale_b[n_idx] : 0.f) : sb_all;
       const float bias_n = (bias && n_ok) ? as_float(bias[n_idx]) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * acc_stride;
+      const bool whole = kb0 == 0 && kb1 == KB;
+      float* slot = g.partials + int64_t(2 * cta + (tile == first_tile ? 0 : 1)) * slot_floats;
 
-      // 16 accumulator columns (tokens m0 + c0 ...) of this thread's weight row
+      // 16 accumulator columns (tokens m0 + c0 ...) of this thread's weight row.  Where alignment allows the
+      // warp's 32 x 16 block is turned round in shared memory and leaves as 16-byte pieces of output rows.
+      const bool vec_tile = g.vec_ok && n_blk * 128 + 128 <= g.n;
       auto finalize = [&](const float (&v)[16], int c0) {
+        if (vec_tile) {
+          constexpr int VEC = 16 / int(sizeof(OutT)), SEGS = 32 / VEC;
+          OutT* turn = reinterpret_cast<OutT*>(turn_base + (warp - 2) * 2048);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m_idx = m0 + c0 + j;
+            const float sa = g.scale_a_per_row ? (m_idx < g.m ? __ldg(g.scale_a + m_idx) : 0.f) : sa_all;
+            OutT o = from_float<OutT>(sb * (sa * v[j]));
+            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
+            turn[j * 32 + lane] = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int pass = 0; pass < SEGS / 2; ++pass) {
+            const int idx = pass * 32 + lane, row = idx / SEGS, seg = idx % SEGS;
+            const int m_idx = m0 + c0 + row;
+            if (m_idx < g.m) {
+              const uint4 val = *reinterpret_cast<const uint4*>(turn + row * 32 + seg * VEC);
+              *reinterpret_cast<uint4*>(out + int64_t(m_idx) * g.ldc + n_blk * 128 + quarter * 32 + seg * VEC) = val;
+            }
+          }
+          __syncwarp();
+          return;
+        }
         if (!n_ok) return;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -216,73 +283,129 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           }
         }
       };
-      auto load16 = [&](int c0, float (&v)[16]) {
-        uint32_t r0[8], r1[8];
-        tmem_ld_32x32b_x8(taddr + c0, r0);
-        tmem_ld_32x32b_x8(taddr + c0 + 8, r1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          v[j] = __uint_as_float(r0[j]);
-          v[8 + j] = __uint_as_float(r1[j]);
-        }
-      };
 
-      if (g.splits == 1) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < g.cols; c0 += 16) {
-          float v[16];
-          load16(c0, v);
-          if (c0 + 16 >= g.cols) {  // everything is in registers: hand the accumulator back
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
-          }
-          finalize(v, c0);
-        }
-        continue;
-      }
-
-      // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
-      const int tile = u / g.splits;
-      float* slot = g.partials + int64_t(u) * g.cols * 128;
 #pragma unroll 1
       for (int c0 = 0; c0 < g.cols; c0 += 16) {
         float v[16];
-        load16(c0, v);
-        if (c0 + 16 >= g.cols) {
+        {
+          uint32_t r0[8], r1[8];
+          tmem_ld_32x32b_x8(taddr + c0, r0);
+          tmem_ld_32x32b_x8(taddr + c0 + 8, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[j] = __uint_as_float(r0[j]);
+            v[8 + j] = __uint_as_float(r1[j]);
+          }
+        }
+        if (c0 + 16 >= g.cols) {  // everything is in registers: hand the accumulator back
           tcgen05_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
         }
+        if constexpr (CLUSTER) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) __stcg(slot + (c0 + j) * 128 + r_in, v[j]);
+          for (int j = 0; j < 16; ++j) stash[(c0 + j) * 128 + r_in] = v[j];
+        } else if (whole) {
+          finalize(v, c0);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) __stcg(slot + (c0 + j) * 128 + r_in, v[j]);
+        }
       }
-      __threadfence();
+      if (CLUSTER || whole) continue;
+
+      // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
       fp8_epilogue_bar();
       if (r_in == 0) {
-        *last_flag = atomicAdd(&g.counters[tile], 1u) + 1u == unsigned(g.splits);
+        const int c_first = owner_of(tile * KB, total, grid), c_last = owner_of(tile * KB + KB - 1, total, grid);
+        const unsigned int seen = arrive_acq_rel(&g.counters[tile]);
+        fix[0] = seen + 1u == unsigned(c_last - c_first + 1);
+        fix[1] = c_first;
+        fix[2] = c_last;
       }
       fp8_epilogue_bar();
-      const bool last = *last_flag != 0;
-      fp8_epilogue_bar();  // the flag may be rewritten by the next unit
+      const bool last = fix[0] != 0;
+      const int c_first = fix[1], c_last = fix[2];
+      fp8_epilogue_bar();  // fix[] may be rewritten by the next shared tile
       if (!last) continue;
-      __threadfence();
-      const float* first = g.partials + int64_t(tile) * g.splits * g.cols * 128;
+      // ascending K: a fixed summation order; four pieces' loads of a whole chunk of columns in flight at a time
+      auto reduce = [&](auto width) {
+        constexpr int CW = decltype(width)::value;
 #pragma unroll 1
-      for (int c0 = 0; c0 < g.cols; c0 += 16) {
-        float v[16];
+        for (int c0 = 0; c0 < g.cols; c0 += CW) {
+          float v[CW];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        for (int p = 0; p < g.splits; ++p) {  // ascending K: a fixed summation order
-          const float* src = first + int64_t(p) * g.cols * 128;
+          for (int j = 0; j < CW; ++j) v[j] = 0.f;
+          for (int c = c_first; c <= c_last; c += 4) {
+            float t[4][CW];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (c0 + j) * 128 + r_in);
+            for (int q = 0; q < 4; ++q) {
+              const int cq = c + q;
+              if (cq <= c_last) {
+                const int c_tile0 = range_start(cq, total, grid) / KB;
+                const float* src = g.partials + int64_t(2 * cq + (tile == c_tile0 ? 0 : 1)) * slot_floats;
+#pragma unroll
+                for (int j = 0; j < CW; ++j) t[q][j] = __ldcg(src + (c0 + j) * 128 + r_in);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; ++j) t[q][j] = 0.f;
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+              for (int j = 0; j < CW; ++j) v[j] += t[q][j];
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < CW / 16; ++h) finalize(reinterpret_cast<const float(&)[16]>(v[h * 16]), c0 + h * 16);
         }
-        finalize(v, c0);
-      }
+      };
+      if (g.cols % 32 == 0) reduce(std::integral_constant<int, 32>{}); else reduce(std::integral_constant<int, 16>{});
       if (r_in == 0) g.counters[tile] = 0u;
     }
+  }
+
+  if constexpr (CLUSTER) {
+    if (warp >= 2 && segs.count == 0) {  // no K blocks for this rank: its partial is zero
+      for (int c = 0; c < g.cols; ++c) stash[c * 128 + (warp & 3) * 32 + lane] = 0.f;
+    }
+    __syncwarp();
+    cluster_sync_all();  // every thread of every CTA of the cluster gets here: all waits above are bounded
+    if (warp >= 2) {
+      const int rank = int(cluster_ctarank()), tile = cta / g.cluster;
+      const int r_in = (warp & 3) * 32 + lane;
+      const int n_idx = (tile / g.m_chunks) * 128 + r_in, m0 = (tile % g.m_chunks) * g.cols;
+      if (n_idx < g.n) {
+        OutT* out = static_cast<OutT*>(g.out);
+        const OutT* bias = static_cast<const OutT*>(g.bias);
+        const float sb = g.scale_b[g.scale_b_per_col ? n_idx : 0];
+        const float bias_n = bias ? as_float(bias[n_idx]) : 0.f;
+        const int c_lo = range_start(rank, g.cols, g.cluster), c_hi = range_start(rank + 1, g.cols, g.cluster);
+        uint32_t peer[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) peer[q] = map_to_cta(smem_u32(stash + r_in), uint32_t(q < g.cluster ? q : 0));
+#pragma unroll 2
+        for (int c = c_lo; c < c_hi; ++c) {
+          float t[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) t[q] = q < g.cluster ? ld_cluster_f32(peer[q] + uint32_t(c) * 512u) : 0.f;
+          float v = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) v += t[q];  // rank order = ascending K: a fixed summation order
+          const int m_idx = m0 + c;
+          if (m_idx < g.m) {
+            const float sa = g.scale_a[g.scale_a_per_row ? m_idx : 0];
+            OutT o = from_float<OutT>(sb * (sa * v));
+            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
+            out[int64_t(m_idx) * g.ldc + n_idx] = o;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // nobody leaves while its shared memory may still be read
   }
 
   tcgen05_fence_before();
@@ -308,33 +431,51 @@ bool make_fp8_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, i
 }
 
 struct Fp8Plan {
-  int n_tiles, m_chunks, cols, num_kb, splits, kb_per_split, stages, stage_bytes, grid;
+  int n_tiles, m_chunks, cols, num_kb, stages, stage_bytes, grid, whole_tiles, cluster;
   int64_t workspace_bytes;
 };
 
-Fp8Plan make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms) {
+bool make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms, Fp8Plan* out) {
   Fp8Plan p{};
   p.n_tiles = int((n + 127) / 128);
   p.m_chunks = int((m + kFp8MaxCols - 1) / kFp8MaxCols);
   p.cols = m >= kFp8MaxCols ? kFp8MaxCols : int((m + 15) / 16 * 16);
   p.num_kb = int((k + 127) / 128);
   const int64_t tiles = int64_t(p.n_tiles) * p.m_chunks;
-  // Split K only while the tiles alone leave SMs idle, and keep at least two K blocks per piece.
-  int splits = 1;
-  if (tiles < sms && tiles <= kFp8MaxSplitTiles) {
-    splits = int((sms + tiles - 1) / tiles);
-    const int most = p.num_kb / 2 > 1 ? p.num_kb / 2 : 1;
-    if (splits > most) splits = most;
-  }
-  p.kb_per_split = (p.num_kb + splits - 1) / splits;
-  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  const int64_t total = tiles * p.num_kb;
+  if (total > 0x7fffffff) return false;
+  p.whole_tiles = tiles > kFp8MaxTiles;
+  // one CTA per SM, fewer when that would leave a CTA under a handful of K blocks (but never fewer than tiles)
+  int64_t grid = total / kFp8MinUnits;
+  if (grid < tiles) grid = tiles;
+  if (grid > sms) grid = sms;
+  if (grid < 1) grid = 1;
+  p.grid = int(grid);
   p.stage_bytes = kFp8WBytes + ((p.cols * 128 + 1023) / 1024) * 1024;
-  const int fit = (232448 - 2048) / p.stage_bytes;
+  const int fit = (232448 - 256 - 4 * 2048 - 1024) / p.stage_bytes;
   p.stages = fit > kFp8MaxStages ? kFp8MaxStages : fit;
-  const int64_t units = tiles * p.splits;
-  p.grid = int(units < sms ? units : sms);
-  p.workspace_bytes = p.splits > 1 ? kFp8CounterBytes + units * p.cols * 128 * 4 : 0;
-  return p;
+  // Small problems (a decode GEMM against a weight of a few megabytes) are latency-bound: one cluster per tile.
+  p.cluster = 0;
+  if (p.m_chunks == 1 && p.cols <= 64 && n * k <= (int64_t(32) << 20)) {
+    for (int size = 8; size >= 2; size /= 2) {
+      if (tiles * size <= sms && p.num_kb >= 2 * size) { p.cluster = size; break; }
+    }
+  }
+  if (p.cluster) {
+    const int per_cta = (p.num_kb + p.cluster - 1) / p.cluster;
+    const int fit_with_partial = (232448 - 256 - 4 * 2048 - 1024 - p.cols * 512) / p.stage_bytes;
+    if (p.stages > fit_with_partial) p.stages = fit_with_partial;
+    if (p.stages > per_cta) p.stages = per_cta;
+    p.grid = int(tiles) * p.cluster;
+    p.workspace_bytes = 0;
+    *out = p;
+    return true;
+  }
+  // tiles are shared between CTAs only when the ranges do not end on tile boundaries
+  const bool shared = !p.whole_tiles && ((total % p.grid) != 0 || ((total / p.grid) % p.num_kb) != 0);
+  p.workspace_bytes = shared ? kFp8CounterBytes + int64_t(2) * p.grid * p.cols * 128 * 4 : 0;
+  *out = p;
+  return true;
 }
 
 int device_sms() {
@@ -346,8 +487,27 @@ int device_sms() {
 template <typename OutT>
 int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
                cudaStream_t s) {
-  auto kernel = fp8_scaled_mm_kernel<OutT>;
-  const size_t smem = size_t(p.stages) * p.stage_bytes + (2 * kFp8MaxStages + 4) * 8 + 32 + 1024;
+  if (p.cluster) {
+    auto kernel = fp8_scaled_mm_kernel<OutT, true>;
+    const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + size_t(p.cols) * 512 + 1024;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(p.grid), 1, 1);
+    cfg.blockDim = dim3(kFp8Threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = unsigned(p.cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, tw, tx, g, format) != cudaSuccess) return HB200_ERR_CUDA;
+    return HB200_OK;
+  }
+  auto kernel = fp8_scaled_mm_kernel<OutT, false>;
+  const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + 1024;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
   kernel<<<p.grid, kFp8Threads, smem, s>>>(tw, tx, g, format);
   return launch_status();
@@ -359,7 +519,8 @@ int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, c
 extern "C" int64_t hb200_fp8_scaled_mm_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   using namespace hb200;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  return make_fp8_plan(m, n, k, device_sms()).workspace_bytes;
+  Fp8Plan p;
+  return make_fp8_plan(m, n, k, device_sms(), &p) ? p.workspace_bytes : 0;
 }
 
 extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const float* scale_a, const float* scale_b,
@@ -375,8 +536,8 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
   if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b) % 16 || (lda % 16) != 0 || (ldb % 16) != 0)
     return HB200_ERR_UNSUPPORTED;
   if (m > 0x7fffff00 || n > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
-  const Fp8Plan p = make_fp8_plan(m, n, k, device_sms());
-  if (int64_t(p.n_tiles) * p.m_chunks * p.splits > 0x7fffffff) return HB200_ERR_UNSUPPORTED;
+  Fp8Plan p;
+  if (!make_fp8_plan(m, n, k, device_sms(), &p)) return HB200_ERR_UNSUPPORTED;
   if (p.workspace_bytes > 0) {
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 16) return HB200_ERR_WORKSPACE;
     if (workspace_bytes < p.workspace_bytes) return HB200_ERR_WORKSPACE;
@@ -401,9 +562,10 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
   g.n_tiles = p.n_tiles;
   g.m_chunks = p.m_chunks;
   g.cols = p.cols;
-  g.splits = p.splits;
-  g.kb_per_split = p.kb_per_split;
   g.num_kb = p.num_kb;
+  g.whole_tiles = p.whole_tiles;
+  g.cluster = p.cluster;
+  g.vec_ok = reinterpret_cast<uintptr_t>(c) % 16 == 0 && (ldc * (out_dtype == 2 ? 4 : 2)) % 16 == 0;
   g.stages = p.stages;
   g.stage_bytes = p.stage_bytes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -79,36 +79,6 @@ __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("grid
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// The contiguous range of (tile, K block) units of CTA c when `total` units are dealt to `grid` CTAs.
-__device__ __forceinline__ int range_start(int c, int total, int grid) { return int((int64_t(c) * total) / grid); }
-
-__device__ __forceinline__ int owner_of(int unit, int total, int grid) {
-  int c = int((int64_t(unit) * grid) / total);
-  while (c + 1 < grid && range_start(c + 1, total, grid) <= unit) ++c;
-  while (c > 0 && range_start(c, total, grid) > unit) --c;
-  return c;
-}
-
-// The segments (tile, K blocks [kb0, kb1)) of a CTA's unit range [u_begin, u_end), in the order it works on them.
-// In natural order only the first and the last can be partial tiles.  With three or more segments and a partial
-// last one, that one is moved to second place: both partial tiles are then published (and, where this CTA
-// arrives last, finished) while the whole tiles still stream, and the kernel's tail is a plain tile write.
-struct Segments {
-  int first_tile, count, kb_total, u_begin, u_end;
-  bool tail_first;
-  __device__ Segments(int ub, int ue, int kb) : kb_total(kb), u_begin(ub), u_end(ue) {
-    first_tile = ub / kb;
-    count = ue > ub ? (ue - 1) / kb - first_tile + 1 : 0;
-    tail_first = count >= 3 && (ue % kb) != 0;
-  }
-  __device__ void get(int i, int& tile, int& kb0, int& kb1) const {
-    const int j = !tail_first ? i : (i == 0 ? 0 : (i == 1 ? count - 1 : i - 1));
-    tile = first_tile + j;
-    kb0 = j == 0 ? u_begin - first_tile * kb_total : 0;
-    kb1 = j == count - 1 ? u_end - tile * kb_total : kb_total;
-  }
-};
-
 template <int NCOLS, int TERMS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,

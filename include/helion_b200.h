@@ -206,10 +206,11 @@ int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t*
  * (scale_a_per_row / scale_b_per_col); bias is [N] in the output type or null and is added after the cast, as
  * the reference does.  fp8_format 0 = e4m3, 1 = e5m2 (both operands); out_dtype 0 bf16, 1 fp16, 2 fp32.
  * Needs 16-byte aligned a and b and lda % 16 == ldb % 16 == 0 (HB200_ERR_UNSUPPORTED otherwise).
- * When few weight tiles would leave SMs idle (decode shapes) the K range is split across CTAs and summed in a
- * fixed order through `workspace`: caller-owned device memory of hb200_fp8_scaled_mm_workspace_bytes(m, n, k)
- * bytes (0 when no split is used) whose first 16 KB are zero before the first call and are left zero by every
- * call; HB200_ERR_WORKSPACE if it is missing or too small.  Calls that share a workspace must not overlap. */
+ * The (tile, K block) units are dealt to the CTAs in equal contiguous ranges; tiles shared between CTAs are
+ * summed in a fixed order through `workspace`: caller-owned device memory of
+ * hb200_fp8_scaled_mm_workspace_bytes(m, n, k) bytes (0 when the ranges end on tile boundaries) whose first
+ * 16 KB are zero before the first call and are left zero by every call; HB200_ERR_WORKSPACE if it is missing
+ * or too small.  Calls that share a workspace must not overlap. */
 int64_t hb200_fp8_scaled_mm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const float* scale_a, const float* scale_b,
                         const void* bias, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,

@@ -102,22 +102,28 @@ def test_shapes_scales_and_output_types(m, k, n, out_dtype):
     check(c2, a, b, sa[:1], sb[:1], None)
 
 
-def test_split_k_is_deterministic_and_leaves_its_counters_clear():
-    m, k, n = 16, 8192, 1024  # 8 weight tiles: K is split over many CTAs
+@pytest.mark.parametrize("m,k,n,shared_workspace", [
+    (16, 8192, 1024, False),  # 8 weight tiles: one thread-block cluster per tile, K split across its CTAs
+    (64, 4096, 4096, False),
+    (16, 8192, 8192, True),   # 64 MB of weights: stream-K ranges, shared tiles summed through the workspace
+    (64, 2048, 12288, True),
+])
+def test_split_k_is_deterministic(m, k, n, shared_workspace):
     lib = _lib.load()
-    assert lib.hb200_fp8_scaled_mm_workspace_bytes(m, n, k) > 16384
+    assert (lib.hb200_fp8_scaled_mm_workspace_bytes(m, n, k) > 16384) == shared_workspace
     a, b, g = random_case(m, k, n, seed=5)
     sa = (torch.rand(m, 1, generator=g) + 0.5).to(DEV)
     sb = (torch.rand(n, 1, generator=g) + 0.5).to(DEV)
+    bias = (torch.rand(n, generator=g) - 0.5).to(torch.bfloat16).to(DEV)
     outs = []
     for _ in range(4):
         c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
-        hb.scaled_mm(c, a, b, sa, sb, None)
+        hb.scaled_mm(c, a, b, sa, sb, bias)
         outs.append(c)
     assert device_status_ok()
-    check(outs[0], a, b, sa, sb, None)
+    check(outs[0], a, b, sa, sb, bias)
     for c in outs[1:]:
-        assert torch.equal(c, outs[0])
+        assert torch.equal(c, outs[0])  # which also shows the arrival counters were left clear
 
 
 def test_e5m2_operands_strided_inputs_and_padded_output():
@@ -153,7 +159,7 @@ def test_the_reference_assertions_and_the_abi_errors():
     with pytest.raises(TypeError):
         hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)
     lib = _lib.load()
-    m, k, n = 16, 8192, 1024
+    m, k, n = 16, 8192, 8192
     a, b, _ = random_case(m, k, n, seed=2)
     c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     args = (a.data_ptr(), b.t().data_ptr(), c.data_ptr(), one.data_ptr(), one.data_ptr(), None, m, n, k, k, k, n,
