@@ -17,6 +17,7 @@
 // accumulators in tensor memory; every wait bounded.
 #include "gemm_common.cuh"
 
+#include <mutex>
 #include <type_traits>
 
 namespace hb200 {
@@ -88,17 +89,16 @@ __device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162f
 __device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
 __device__ __forceinline__ float as_float(float v) { return v; }
 
-__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-  return v;
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
-// CLUSTER: the small-problem form.  One tile per thread-block cluster, its K range split over the cluster's CTAs;
-// every CTA leaves its fp32 partial in its own shared memory, and after a cluster barrier each CTA adds up, in
-// rank order, a slice of the tile's columns from all of them through distributed shared memory.  No workspace,
-// no counters, no trip through L2.
-template <typename OutT, bool CLUSTER>
+// CLUSTER: the small-problem form.  One tile per thread-block cluster, its K range split over the cluster's CTAs.
+// Every CTA owns the tile's columns c with c % CLUSTER == its rank; each CTA stores its fp32 partial of a column into the owner's
+// shared memory (distributed shared memory: remote stores, nothing waits on them), and after one cluster
+// barrier every owner adds up its columns from local shared memory in rank order.  No workspace, no counters,
+// no trip through L2.
+template <typename OutT, int CLUSTER>  // CLUSTER: CTAs per tile (2, 4 or 8) in the cluster form, 0 otherwise
 __global__ void __launch_bounds__(kFp8Threads, 1)
 fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                      const Fp8Args g, const int format) {
@@ -114,17 +114,17 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* fix = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [0] last arriver? [1] first owner [2] last owner
   uint8_t* turn_base = reinterpret_cast<uint8_t*>(bars) + 256;  // 2 KB per epilogue warp
-  float* stash = reinterpret_cast<float*>(turn_base + 4 * 2048);  // CLUSTER: this CTA's partial, [cols][128]
+  float* stash = reinterpret_cast<float*>(turn_base + 4 * 2048);  // CLUSTER: [rank][column of mine][128] partials
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = g.stages;
   const int KB = g.num_kb;
   const int total = g.n_tiles * g.m_chunks * KB, grid = int(gridDim.x), cta = int(blockIdx.x);
   int u_begin, u_end;
-  if constexpr (CLUSTER) {
-    const int rank = int(cluster_ctarank()), tile = cta / g.cluster;
-    u_begin = tile * KB + range_start(rank, KB, g.cluster);
-    u_end = tile * KB + range_start(rank + 1, KB, g.cluster);
+  if constexpr (CLUSTER > 0) {
+    const int rank = int(cluster_ctarank()), tile = cta / CLUSTER;
+    u_begin = tile * KB + range_start(rank, KB, CLUSTER);
+    u_end = tile * KB + range_start(rank + 1, KB, CLUSTER);
   } else {
     // beyond the counters' reach (thousands of tiles) whole tiles are dealt instead: nothing is shared then
     u_begin = g.whole_tiles ? range_start(cta, total / KB, grid) * KB : range_start(cta, total, grid);
@@ -161,14 +161,31 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       for (int kb = kb0; kb < kb1 && it < stages; ++kb, ++it) issue(it, tile, kb);
     }
   }
+  // two accumulators of acc_stride columns; the allocation is a power of two of at least 32 columns
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < uint32_t(ACC * acc_stride)) tmem_cols *= 2;
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_alloc(smem_u32(tmem_slot), tmem_cols);
     tmem_relinquish();
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // CLUSTER: a CTA's shared memory may be written by its peers only once it runs.  Everybody arrives here;
+  // the wait for the others sits in front of the first remote store, behind the whole main loop.
+  bool peers_running = false;
+  if constexpr (CLUSTER > 0) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+
+  // CLUSTER: what the final reduction needs from global memory is fetched now, long before it is used
+  const int c_rank = CLUSTER > 0 ? int(cluster_ctarank()) : 0, c_tile = CLUSTER > 0 ? cta / CLUSTER : 0;
+  const int per = CLUSTER > 0 ? g.cols / CLUSTER : 0;
+  const int c_r_in = (warp & 3) * 32 + lane;
+  const int c_n_idx = (c_tile / g.m_chunks) * 128 + c_r_in, c_m0 = (c_tile % g.m_chunks) * g.cols + c_rank;
+  const bool c_active = CLUSTER > 0 && warp >= 2 && c_n_idx < g.n;
+  const float c_sb = c_active ? g.scale_b[g.scale_b_per_col ? c_n_idx : 0] : 0.f;
+  const float c_bias = (c_active && g.bias) ? as_float(static_cast<const OutT*>(g.bias)[c_n_idx]) : 0.f;
+  const float c_sa_all = c_active ? g.scale_a[0] : 0.f;
 
   if (warp == 0) {
     uint32_t it = 0;
@@ -232,13 +249,14 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       segs.get(i, tile, kb0, kb1);
       const int n_blk = tile / g.m_chunks, m_blk = tile % g.m_chunks;
       const int acc = sc % ACC;
-      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), (sc / ACC) & 1, abort_flag)) { ok = false; break; }
-      tcgen05_fence_after();
+      // this row's scale and bias are fetched before the wait, not after it
       const int n_idx = n_blk * 128 + r_in;
       const bool n_ok = n_idx < g.n;
       const int m0 = m_blk * g.cols;
       const float sb = g.scale_b_per_col ? (n_ok ? g.scale_b[n_idx] : 0.f) : sb_all;
       const float bias_n = (bias && n_ok) ? as_float(bias[n_idx]) : 0.f;
+      if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), (sc / ACC) & 1, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * acc_stride;
       const bool whole = kb0 == 0 && kb1 == KB;
       float* slot = g.partials + int64_t(2 * cta + (tile == first_tile ? 0 : 1)) * slot_floats;
@@ -303,9 +321,19 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
         }
-        if constexpr (CLUSTER) {
+        if constexpr (CLUSTER > 0) {
+          if (!peers_running) {
+            asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+            peers_running = true;
+          }
+          // column c belongs to rank c % CLUSTER, which keeps it as its column c / CLUSTER of this rank's block
+          const int per = g.cols / CLUSTER, rank = int(cluster_ctarank());
+          uint32_t owner_base[CLUSTER];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) stash[(c0 + j) * 128 + r_in] = v[j];
+          for (int q = 0; q < CLUSTER; ++q)
+            owner_base[q] = map_to_cta(smem_u32(stash + (rank * per + c0 / CLUSTER) * 128 + r_in), uint32_t(q));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) st_cluster_f32(owner_base[j % CLUSTER] + uint32_t(j / CLUSTER) * 512u, v[j]);
         } else if (whole) {
           finalize(v, c0);
         } else {
@@ -313,7 +341,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           for (int j = 0; j < 16; ++j) __stcg(slot + (c0 + j) * 128 + r_in, v[j]);
         }
       }
-      if (CLUSTER || whole) continue;
+      if (CLUSTER > 0 || whole) continue;
 
       // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
       fp8_epilogue_bar();
@@ -367,52 +395,45 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
   }
 
-  if constexpr (CLUSTER) {
-    if (warp >= 2 && segs.count == 0) {  // no K blocks for this rank: its partial is zero
-      for (int c = 0; c < g.cols; ++c) stash[c * 128 + (warp & 3) * 32 + lane] = 0.f;
+  if constexpr (CLUSTER > 0) {
+    if (!peers_running) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    if (warp >= 2 && segs.count == 0) {  // no K blocks for this rank: its partials are zero
+      for (int c = 0; c < g.cols; ++c)
+        st_cluster_f32(map_to_cta(smem_u32(stash + (c_rank * per + c / CLUSTER) * 128 + c_r_in), uint32_t(c % CLUSTER)), 0.f);
     }
     __syncwarp();
-    cluster_sync_all();  // every thread of every CTA of the cluster gets here: all waits above are bounded
-    if (warp >= 2) {
-      const int rank = int(cluster_ctarank()), tile = cta / g.cluster;
-      const int r_in = (warp & 3) * 32 + lane;
-      const int n_idx = (tile / g.m_chunks) * 128 + r_in, m0 = (tile % g.m_chunks) * g.cols;
-      if (n_idx < g.n) {
-        OutT* out = static_cast<OutT*>(g.out);
-        const OutT* bias = static_cast<const OutT*>(g.bias);
-        const float sb = g.scale_b[g.scale_b_per_col ? n_idx : 0];
-        const float bias_n = bias ? as_float(bias[n_idx]) : 0.f;
-        const int c_lo = range_start(rank, g.cols, g.cluster), c_hi = range_start(rank + 1, g.cols, g.cluster);
-        uint32_t peer[8];
+    // Every thread of every CTA of the cluster gets here (all waits above are bounded).  The barrier orders the
+    // remote stores before the loads below; after it nobody touches another CTA's shared memory again, so a
+    // CTA may leave as soon as it has written its columns.
+    cluster_sync_all();
+    if (c_active) {
+      OutT* out = static_cast<OutT*>(g.out) + c_n_idx;
+      const bool bias = g.bias != nullptr;
+      const float* mine = stash + c_r_in;
+#pragma unroll 4
+      for (int i = 0; i < per; ++i) {  // my i-th column is the tile's column i * CLUSTER + rank
+        float t[CLUSTER];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) peer[q] = map_to_cta(smem_u32(stash + r_in), uint32_t(q < g.cluster ? q : 0));
-#pragma unroll 2
-        for (int c = c_lo; c < c_hi; ++c) {
-          float t[8];
+        for (int q = 0; q < CLUSTER; ++q) t[q] = mine[(q * per + i) * 128];
+        float v = t[0];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) t[q] = q < g.cluster ? ld_cluster_f32(peer[q] + uint32_t(c) * 512u) : 0.f;
-          float v = 0.f;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) v += t[q];  // rank order = ascending K: a fixed summation order
-          const int m_idx = m0 + c;
-          if (m_idx < g.m) {
-            const float sa = g.scale_a[g.scale_a_per_row ? m_idx : 0];
-            OutT o = from_float<OutT>(sb * (sa * v));
-            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
-            out[int64_t(m_idx) * g.ldc + n_idx] = o;
-          }
+        for (int q = 1; q < CLUSTER; ++q) v += t[q];  // rank order = ascending K: a fixed summation order
+        const int m_idx = c_m0 + i * CLUSTER;
+        if (m_idx < g.m) {
+          const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : c_sa_all;
+          OutT o = from_float<OutT>(c_sb * (sa * v));
+          if (bias) o = from_float<OutT>(as_float(o) + c_bias);
+          out[int64_t(m_idx) * g.ldc] = o;
         }
       }
     }
-    __syncwarp();
-    cluster_sync_all();  // nobody leaves while its shared memory may still be read
   }
 
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, tmem_cols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicMin(&g_device_status_fp8, HB200_ERR_DEVICE_TIMEOUT);
 }
@@ -434,6 +455,37 @@ struct Fp8Plan {
   int n_tiles, m_chunks, cols, num_kb, stages, stage_bytes, grid, whole_tiles, cluster;
   int64_t workspace_bytes;
 };
+
+// How many clusters of `size` CTAs (one CTA per SM) the device runs at the same time; asked once per device and size.
+int max_active_clusters(int size) {
+  static std::mutex mu;
+  static int cached[64][9] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || size < 1 || size > 8) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev][size] == 0) {
+    auto kernel = size == 8 ? fp8_scaled_mm_kernel<__nv_bfloat16, 8>
+                  : size == 4 ? fp8_scaled_mm_kernel<__nv_bfloat16, 4> : fp8_scaled_mm_kernel<__nv_bfloat16, 2>;
+    const size_t smem = 200 * 1024;
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(size) * 64, 1, 1);
+    cfg.blockDim = dim3(kFp8Threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = unsigned(size);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess)
+      n = 0;
+    cached[dev][size] = n > 0 ? n : -1;
+  }
+  return cached[dev][size] > 0 ? cached[dev][size] : 0;
+}
 
 bool make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms, Fp8Plan* out) {
   Fp8Plan p{};
@@ -458,7 +510,7 @@ bool make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms, Fp8Plan* out) {
   p.cluster = 0;
   if (p.m_chunks == 1 && p.cols <= 64 && n * k <= (int64_t(32) << 20)) {
     for (int size = 8; size >= 2; size /= 2) {
-      if (tiles * size <= sms && p.num_kb >= 2 * size) { p.cluster = size; break; }
+      if (tiles * size <= sms && p.num_kb >= 2 * size && tiles <= max_active_clusters(size)) { p.cluster = size; break; }
     }
   }
   if (p.cluster) {
@@ -488,7 +540,8 @@ template <typename OutT>
 int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
                cudaStream_t s) {
   if (p.cluster) {
-    auto kernel = fp8_scaled_mm_kernel<OutT, true>;
+    auto kernel = p.cluster == 8 ? fp8_scaled_mm_kernel<OutT, 8>
+                  : p.cluster == 4 ? fp8_scaled_mm_kernel<OutT, 4> : fp8_scaled_mm_kernel<OutT, 2>;
     const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + size_t(p.cols) * 512 + 1024;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
@@ -506,7 +559,7 @@ int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, c
     if (cudaLaunchKernelEx(&cfg, kernel, tw, tx, g, format) != cudaSuccess) return HB200_ERR_CUDA;
     return HB200_OK;
   }
-  auto kernel = fp8_scaled_mm_kernel<OutT, false>;
+  auto kernel = fp8_scaled_mm_kernel<OutT, 0>;
   const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + 1024;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
   kernel<<<p.grid, kFp8Threads, smem, s>>>(tw, tx, g, format);
