@@ -508,10 +508,18 @@ bool make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms, Fp8Plan* out) {
   p.stages = fit > kFp8MaxStages ? kFp8MaxStages : fit;
   // Small problems (a decode GEMM against a weight of a few megabytes) are latency-bound: one cluster per tile.
   p.cluster = 0;
-  if (p.m_chunks == 1 && p.cols <= 64 && n * k <= (int64_t(32) << 20)) {
+  if (p.m_chunks == 1 && p.cols <= 64) {
     for (int size = 8; size >= 2; size /= 2) {
       if (tiles * size <= sms && p.num_kb >= 2 * size && tiles <= max_active_clusters(size)) { p.cluster = size; break; }
     }
+    // A large weight is worth a cluster only if the clusters cover most of the GPU: one SM streams about 1/148
+    // of the HBM bandwidth, so idle SMs cost more there than the trip through L2 that stream-K takes.
+    if (n * k > (int64_t(32) << 20) && tiles * p.cluster * 4 < int64_t(sms) * 3) p.cluster = 0;
+  }
+  // Nearly one tile per SM: whole tiles, one per CTA, beat sharing the last few through the workspace.
+  if (!p.cluster && tiles <= sms && tiles * 5 >= int64_t(sms) * 3) {
+    p.whole_tiles = 1;
+    p.grid = int(tiles);
   }
   if (p.cluster) {
     const int per_cta = (p.num_kb + p.cluster - 1) / p.cluster;

@@ -105,8 +105,10 @@ def test_shapes_scales_and_output_types(m, k, n, out_dtype):
 @pytest.mark.parametrize("m,k,n,shared_workspace", [
     (16, 8192, 1024, False),  # 8 weight tiles: one thread-block cluster per tile, K split across its CTAs
     (64, 4096, 4096, False),
-    (16, 8192, 8192, True),   # 64 MB of weights: stream-K ranges, shared tiles summed through the workspace
-    (64, 2048, 12288, True),
+    (16, 8192, 8192, False),  # 64 tiles, two CTAs each
+    (64, 2048, 12288, False), # 96 tiles: nearly one per SM, whole tiles
+    (16, 4096, 24576, True),  # 192 tiles: stream-K ranges, shared tiles summed through the workspace
+    (64, 5120, 10240, True),
 ])
 def test_split_k_is_deterministic(m, k, n, shared_workspace):
     lib = _lib.load()
@@ -159,7 +161,7 @@ def test_the_reference_assertions_and_the_abi_errors():
     with pytest.raises(TypeError):
         hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)
     lib = _lib.load()
-    m, k, n = 16, 8192, 8192
+    m, k, n = 16, 4096, 24576
     a, b, _ = random_case(m, k, n, seed=2)
     c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     args = (a.data_ptr(), b.t().data_ptr(), c.data_ptr(), one.data_ptr(), one.data_ptr(), None, m, n, k, k, k, n,
