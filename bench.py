@@ -130,6 +130,7 @@ NCU_TRAFFIC = {
     "gemv_gate_up_m1": 268.5e6,     # profiles/nvfp4_gemv_kernels_70b_decode_layer.md
     "gemv_gate_up_m8": 274.9e6,     # tensor-core kernel
     "rms_norm_16384x7168": 315.0e6,      # profiles/quant_producers_16384_tokens.md
+    "scaled_mm_16x5120x51200": 271.6e6,  # profiles/fp8_scaled_mm_kernel_decode_shapes.md
 }
 
 
@@ -621,12 +622,26 @@ def wl_scaled_mm(args, dev, rank, world, timer):
 
     big_ms = timer.run(graphed(four_big)[0], max(10, args.steps // 2), 3) / 4
     big_bytes = scaled_mm_bytes(m, *SCALED_MM_KN[10])
+    # The same step through the library (torch._scaled_mm: cuBLASLt), and every shape eight times back to back
+    # (weights under 126 MB stay in L2 there), ours and the library's, as context for the numbers above.
+    def library_step():
+        for a, b, c, sa, sb, bias in cases:
+            torch._scaled_mm(a, b, scale_a=sa, scale_b=sb, bias=bias, out_dtype=torch.bfloat16)
+
+    library_ms = timer.run(graphed(library_step)[0], args.steps, args.warmup)
     per_shape = {}
     for (k, n), cs in zip(SCALED_MM_KN, cases):
-        r = graphed(lambda cs=cs: hb.scaled_mm(cs[2], cs[0], cs[1], cs[3], cs[4], cs[5]))[0]
-        tm = timer.run(r, max(10, args.steps // 4), 3)
-        # one launch between two events: includes a few microseconds of launch and event latency
-        per_shape[f"{m}x{k}x{n}"] = {"us_single_launch": tm * 1e3}
+        def ours8(cs=cs):
+            for _ in range(8):
+                hb.scaled_mm(cs[2], cs[0], cs[1], cs[3], cs[4], cs[5])
+
+        def library8(cs=cs):
+            for _ in range(8):
+                torch._scaled_mm(cs[0], cs[1], scale_a=cs[3], scale_b=cs[4], bias=cs[5], out_dtype=torch.bfloat16)
+
+        t_ours = timer.run(graphed(ours8)[0], max(10, args.steps // 4), 3) / 8
+        t_lib = timer.run(graphed(library8)[0], max(10, args.steps // 4), 3) / 8
+        per_shape[f"{m}x{k}x{n}"] = {"us": t_ours * 1e3, "library_us": t_lib * 1e3}
 
     host_a = [cs[0].cpu().view(torch.uint8).pin_memory() for cs in cases]
     host_c = [torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for _, n in SCALED_MM_KN]
@@ -646,7 +661,8 @@ def wl_scaled_mm(args, dev, rank, world, timer):
     return dict(value=world * nbytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms,
                 e2e_value=world * nbytes / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
                 h2d=sum(h.numel() for h in host_a), d2h=sum(h.numel() * 2 for h in host_c), launches=len(cases),
-                roofline=roof, parity=parity, extra={"shapes": per_shape}, dtype="e4m3 operands, fp32 accumulate, bf16 out",
+                roofline=roof, parity=parity,
+                extra={"library_ms_per_step": library_ms, "shapes_back_to_back": per_shape}, dtype="e4m3 operands, fp32 accumulate, bf16 out",
                 config={"workload": "scaled_mm", "tokens": m, "kn_shapes": len(SCALED_MM_KN),
                         "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
 

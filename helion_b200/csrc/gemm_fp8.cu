@@ -4,17 +4,23 @@
 // row / column; the bias is added after the cast, in the output type.  This is the operator of
 // pretuned_kernels/scaled_mm/scaled_mm.py:18-84.
 //
-// The shapes that operator is tuned on are decode shapes (16 or 64 tokens against weights of tens of
-// megabytes), so the kernel streams the WEIGHT through the tensor core's M side: a tile is 128 weight rows
-// by up to 256 tokens and the accumulator holds c transposed (lane = n, column = m).  The (tile, K block) units
-// are dealt to the CTAs in contiguous ranges of equal length (stream-K), so every SM streams the same number
-// of bytes whatever the tile count.  A tile whose K range is shared has each of its CTAs write an fp32 partial to
-// the workspace; the last to arrive adds them in K order (a fixed order: results do not depend on timing) and
-// finishes the tile.  Large M runs through the same kernel, 256 tokens per tile.
+// The shapes that operator is tuned on are decode shapes (16 or 64 tokens against weights of 4 to 262 MB), so
+// the kernel streams the WEIGHT through the tensor core's M side: a tile is 128 weight rows by up to 256 tokens
+// and the accumulator holds c transposed (lane = n, column = m).  One SM streams about 1/148 of the HBM
+// bandwidth, so the work must cover the SMs whatever the tile count; three forms, chosen on the host:
+//  * cluster form (few tiles): one thread-block cluster of 2, 4 or 8 CTAs per tile, the K range split across
+//    them, the partial sums exchanged through distributed shared memory (see the kernel's comment);
+//  * whole tiles, one per CTA, when there is nearly one tile per SM;
+//  * stream-K otherwise: the (tile, K block) units are dealt to one CTA per SM in contiguous ranges of equal
+//    length.  A tile whose K range is shared has each of its CTAs write an fp32 partial to the workspace; the last
+//    to arrive (an acq_rel counter per tile) adds them in K order and finishes the tile.
+// In every form partial sums are added in a fixed order: results do not depend on timing.  Large M runs through the
+// same kernel, 256 tokens per tile.
 //
-// Persistent CTAs of 192 threads: warp 0 TMA producer (weights 128 x 128 bytes, tokens cols x 128 bytes, 128-byte
-// swizzle, no multicast), warp 1 MMA issuer (128 x cols x 32 per instruction), warps 2-5 epilogue; two
-// accumulators in tensor memory; every wait bounded.
+// CTAs of 192 threads: warp 0 TMA producer (weights 128 x 128 bytes, tokens cols x 128 bytes, 128-byte swizzle,
+// no multicast; the first ring of loads goes out during set-up), warp 1 MMA issuer (128 x cols x 32 per
+// instruction), warps 2-5 epilogue (scales, cast, bias; 32 x 16 blocks turned round in shared memory so that c
+// is written in 16-byte pieces); two accumulators in tensor memory; every wait bounded.
 #include "gemm_common.cuh"
 
 #include <mutex>
