@@ -701,7 +701,7 @@ def wl_moe(args, dev, rank, world, timer):
             return D.expert_parallel_moe(x, logits, c["top_k"], c["experts"], fn)
 
     y = step()
-    parity = float(torch.isfinite(y.float()).all())
+    parity = 0.0 if bool(torch.isfinite(y.float()).all()) else 1.0  # full parity is the test suite's; here: finite
     ms = timer.run(step, args.steps, args.warmup)
     host_out = torch.empty(t_local, c["hidden"], dtype=torch.bfloat16).pin_memory()
 
