@@ -79,6 +79,14 @@ __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("grid
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Arrival on a tile's counter: releases what the CTA's threads wrote before the barrier they passed on the way
+// here, and acquires what earlier arrivers released, for the threads that pass the next barrier.
+__device__ __forceinline__ unsigned int arrive_acq_rel(unsigned int* counter) {
+  unsigned int old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
+
 template <int NCOLS, int TERMS>
 __global__ void __launch_bounds__(kTcThreads, 1)
 nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -328,11 +336,10 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       if (whole) continue;
 
       // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
-      __threadfence();
       epilogue_bar();
       if (et == 0) {
         const int c_first = owner_of(tile * KB, total, grid), c_last = owner_of(tile * KB + KB - 1, total, grid);
-        const unsigned int seen = atomicAdd(&g.counters[tile], 1u);
+        const unsigned int seen = arrive_acq_rel(&g.counters[tile]);
         fix[0] = seen + 1u == unsigned(c_last - c_first + 1);
         fix[1] = c_first;
         fix[2] = c_last;
@@ -342,17 +349,32 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       const int c_first = fix[1], c_last = fix[2];
       epilogue_bar();  // fix[] may be rewritten by the next shared tile
       if (!last) continue;
-      __threadfence();
 #pragma unroll 1
       for (int c0 = 0; c0 < NCOLS; c0 += CH) {
         float v[CH];
 #pragma unroll
         for (int j = 0; j < CH; ++j) v[j] = 0.f;
-        for (int c = c_first; c <= c_last; ++c) {  // ascending K: a fixed summation order
-          const int c_tile0 = range_start(c, total, grid) / KB;
-          const float* src = g.partials + (int64_t(2 * c + (tile == c_tile0 ? 0 : 1)) * NCOLS) * kBlockM;
+        // ascending K: a fixed summation order; two pieces' loads in flight at a time
+        for (int c = c_first; c <= c_last; c += 2) {
+          float t[2][CH];
 #pragma unroll
-          for (int j = 0; j < CH; ++j) v[j] += __ldcg(src + (c0 + j) * kBlockM + et);
+          for (int q = 0; q < 2; ++q) {
+            const int cq = c + q;
+            if (cq <= c_last) {
+              const int c_tile0 = range_start(cq, total, grid) / KB;
+              const float* src = g.partials + (int64_t(2 * cq + (tile == c_tile0 ? 0 : 1)) * NCOLS) * kBlockM;
+#pragma unroll
+              for (int j = 0; j < CH; ++j) t[q][j] = __ldcg(src + (c0 + j) * kBlockM + et);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CH; ++j) t[q][j] = 0.f;
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) v[j] += t[q][j];
+          }
         }
         finalize(v, c0, row);
       }
