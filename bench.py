@@ -548,6 +548,11 @@ def wl_quant(args, dev, rank, world, timer):
     tm = timer.run(r, max(10, args.steps // 4), 3)
     b = 2 * t * 2 * i + t * i + 4 * t * (i // 128)
     ops["silu_and_mul_per_block_quant_16384x18432"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
+    one = torch.tensor([0.5], device=dev)
+    r = graphed(lambda: hb.silu_mul_fp8(xs, one))[0]
+    tm = timer.run(r, max(10, args.steps // 4), 3)
+    b = 2 * t * 2 * i + t * i
+    ops["silu_mul_fp8_16384x18432"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
     del xs, qs, ss
     sg = torch.empty(t, h // 128, dtype=torch.float32, device=dev)
     r = graphed(lambda: hb.per_token_group_fp8_quant(x, q, sg, 128, 1e-10, -448.0, 448.0, False))[0]

@@ -27,6 +27,7 @@ from .ops import nvfp4_w4a16_matmul
 from .ops import per_token_group_fp8_quant
 from .ops import dynamic_per_token_scaled_fp8_quant
 from .ops import scaled_mm
+from .ops import silu_mul_fp8
 from .ops import rms_norm_dynamic_per_token_quant
 from .ops import rms_norm_per_block_quant
 from .ops import silu_and_mul_per_block_quant
@@ -48,6 +49,7 @@ __all__ = [
     "per_token_group_fp8_quant",
     "dynamic_per_token_scaled_fp8_quant",
     "scaled_mm",
+    "silu_mul_fp8",
     "rms_norm_dynamic_per_token_quant",
     "rms_norm_per_block_quant",
     "silu_and_mul_per_block_quant",

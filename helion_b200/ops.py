@@ -244,6 +244,26 @@ def _(result, input, scale, scale_ub):  # noqa: A002
     return None
 
 
+@torch.library.custom_op("helion_b200::silu_mul_fp8", mutates_args=())
+def _silu_mul_fp8_op(input: Tensor, scale: Tensor) -> Tensor:  # noqa: A002
+    _require_cuda(input, scale)
+    tokens, two_d = input.shape
+    d = two_d // 2
+    out = torch.empty((tokens, d), dtype=_FP8, device=input.device)
+    if tokens and d:
+        with torch.cuda.device(input.device):
+            _lib.call(
+                "hb200_silu_mul_fp8", out.data_ptr(), input.data_ptr(), scale.data_ptr(), tokens, d, input.stride(0),
+                int(input.dtype == torch.float16), _stream(),
+            )
+    return out
+
+
+@_silu_mul_fp8_op.register_fake
+def _(input, scale):  # noqa: A002
+    return torch.empty((input.shape[0], input.shape[1] // 2), dtype=_FP8, device=input.device)
+
+
 @torch.library.custom_op("helion_b200::scaled_mm", mutates_args=("c",))
 def _scaled_mm_op(c: Tensor, a: Tensor, b_nk: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None) -> None:
     _require_cuda(c, a, b_nk, scale_a, scale_b, bias)
@@ -643,6 +663,30 @@ def dynamic_per_token_scaled_fp8_quant(
     if not (result.is_contiguous() and scale.is_contiguous()):
         raise ValueError("result and scale must be contiguous")
     _dyn_token_quant_op(result, input.contiguous(), scale, scale_ub)
+
+
+def silu_mul_fp8(input: Tensor, scale: Tensor) -> Tensor:  # noqa: A002
+    """``fp8_e4m3((silu(x[..., :d]) * x[..., d:]) / scale)`` for an input whose last dimension is ``2 * d``.
+
+    Drop-in for ``silu_mul_fp8`` (pretuned_kernels/silu_mul_fp8/silu_mul_fp8.py:29-59): SiLU and the product are
+    rounded to the input type as the reference's tile arithmetic does, the fp32 result is multiplied by the
+    reciprocal of the one-element ``scale``; returns a new tensor of shape ``(*input.shape[:-1], d)``.
+    """
+    original_shape = input.shape
+    two_d = original_shape[-1]
+    d = two_d // 2
+    assert scale.numel() == 1, "Scale must be a scalar Tensor"
+    if two_d % 2:
+        raise ValueError(f"the last dimension must be even, got {two_d}")
+    if input.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"input must be bfloat16 or float16, got {input.dtype}")
+    if d % 8:
+        raise ValueError(f"d must be a multiple of 8 (16-byte loads of both halves), got {d}")
+    input_2d = input.reshape(-1, two_d)
+    if input_2d.stride(1) != 1 or input_2d.stride(0) % 8 or input_2d.data_ptr() % 16:
+        input_2d = input_2d.contiguous()
+    out = _silu_mul_fp8_op(input_2d, scale.reshape(1).to(torch.float32))
+    return out.view(*original_shape[:-1], d)
 
 
 def scaled_mm(

@@ -197,6 +197,14 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* silu_mul_fp8 (pretuned_kernels/silu_mul_fp8/silu_mul_fp8.py:29-59): out[t, j] = fp8_e4m3(p * (1 / scale)) with
+ * p = input_dtype(input_dtype(silu(x[t, j])) * x[t, d + j]), one static fp32 scale (device pointer), input
+ * [tokens, 2 d] bf16 (in_is_fp16 = 0) or fp16 with row pitch in_stride elements, out [tokens, d] contiguous.
+ * Values beyond the e4m3 range saturate to +-448.  d % 8 == 0 and in_stride % 8 == 0 (HB200_ERR_UNSUPPORTED
+ * otherwise). */
+int hb200_silu_mul_fp8(void* out, const void* input, const float* scale, int64_t tokens, int64_t d,
+                       int64_t in_stride, int in_is_fp16, void* stream);
+
 /* ------------------------------------------------ row-wise scaled FP8 GEMM
  * scaled_mm (pretuned_kernels/scaled_mm/scaled_mm.py:18-84):
  *   c[m, n] = out_dtype(scale_b[n] * (scale_a[m] * sum_k a[m, k] * b[k, n])) + bias[n]

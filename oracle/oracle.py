@@ -287,6 +287,17 @@ def rms_norm_per_block_quant(
     return q, s, new_res
 
 
+def silu_mul_fp8(x: Tensor, scale: Tensor) -> Tensor:
+    """silu_mul_fp8 (pretuned_kernels/silu_mul_fp8/silu_mul_fp8.py:29-59): SiLU and the product in the input
+    type (torch rounds each to it), the result in fp32 times ``1 / scale``, cast to e4m3.  Values beyond the
+    e4m3 range are clamped to +-448 first (the kernel's conversion saturates; torch's cast would give NaN)."""
+    d = x.shape[-1] // 2
+    a, b = x[..., :d], x[..., d:]
+    result = (torch.nn.functional.silu(a) * b).to(torch.float32)
+    inv = 1.0 / scale.reshape(()).to(torch.float32)
+    return (result * inv).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
 def scaled_mm(
     a: Tensor, b: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None = None,
     out_dtype: torch.dtype = torch.bfloat16,

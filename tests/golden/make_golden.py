@@ -204,6 +204,19 @@ def main(ref_root: str) -> None:
                     out[f"smm_{tag}_{stag}_{dtag}_{btag}_c"] = _np(c)
     np.savez_compressed(HERE / "scaled_mm.npz", **out)
 
+    # ---- silu_mul_fp8: the reference kernel in the CPU interpreter, and the module's torch reference ----------
+    smf = _load(pk / "silu_mul_fp8" / "silu_mul_fp8.py", "ref_silu_mul_fp8")
+    out = {}
+    torch.manual_seed(44)
+    for tag, (t, d, dt, sc) in (("a", (8, 256, torch.bfloat16, 1.0)), ("b", (5, 64, torch.bfloat16, 0.037)),
+                                ("c", (3, 128, torch.float16, 2.5))):
+        x = (torch.randn(t, 2 * d) * 3).to(dt)
+        scale = torch.tensor([sc], dtype=torch.float32)
+        out[f"smf_{tag}_x"], out[f"smf_{tag}_scale"] = _np(x), _np(scale)
+        out[f"smf_{tag}_kernel"] = _np(smf.silu_mul_fp8(x, scale))
+        out[f"smf_{tag}_torch"] = _np(smf._silu_mul_fp8_torch(x, scale))
+    np.savez_compressed(HERE / "silu_mul_fp8.npz", **out)
+
     # ---- MoE / grouped GEMM references ------------------------------------------------------------
     out = {}
     torch.manual_seed(8)

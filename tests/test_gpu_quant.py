@@ -281,3 +281,55 @@ def test_rms_per_block_against_oracle(t, h, gs):
     assert qi.dtype is torch.int8
     assert float((qi.cpu() != qe).float().mean()) <= 2e-3
     assert torch.allclose(si.cpu(), se, rtol=1e-5, atol=0)
+
+
+def _silu_mul_fp8_on_device(x, scale):
+    """The reference function evaluated by torch on the GPU, with the saturating conversion of the compiled kernel."""
+    d = x.shape[-1] // 2
+    r = (torch.nn.functional.silu(x[..., :d]) * x[..., d:]).to(torch.float32)
+    return (r * (1.0 / scale.reshape(()))).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+
+
+def test_silu_mul_fp8_golden(golden):
+    g = golden("silu_mul_fp8.npz")
+    for tag, dt in (("a", torch.bfloat16), ("b", torch.bfloat16), ("c", torch.float16)):
+        x = g.raw(f"smf_{tag}_x").view(dt).to(DEV)
+        scale = g.raw(f"smf_{tag}_scale").to(DEV)
+        ref = g.e4m3(f"smf_{tag}_kernel")
+        got = hb.silu_mul_fp8(x, scale).cpu()
+        overflow = torch.isnan(ref.float())
+        same = got.view(torch.uint8)[~overflow] == ref.view(torch.uint8)[~overflow]
+        # exp() on the device may differ from the CPU's in the last place: at most a code or two may move
+        assert float(same.float().mean()) >= 0.995
+        assert bool((got.float()[overflow].abs() == 448.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens,d", [(1, 2048), (8, 2880), (33, 4096), (256, 14336), (3, 8), (0, 64)])
+def test_silu_mul_fp8_matches_torch_on_device(tokens, d, dtype):
+    g = torch.Generator(device=DEV).manual_seed(tokens + d)
+    x = (torch.randn(tokens, 2 * d, device=DEV, generator=g) * 2).to(dtype)
+    for sc in (1.0, 0.05, 3.0):
+        scale = torch.tensor([sc], device=DEV)
+        got = hb.silu_mul_fp8(x, scale)
+        assert got.shape == (tokens, d) and got.dtype is torch.float8_e4m3fn
+        want = _silu_mul_fp8_on_device(x, scale)
+        assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    torch.cuda.synchronize()
+
+
+def test_silu_mul_fp8_shapes_and_errors():
+    x = torch.randn(2, 3, 64, device=DEV).to(torch.bfloat16)
+    scale = torch.tensor(0.5, device=DEV)
+    y = hb.silu_mul_fp8(x, scale)
+    assert y.shape == (2, 3, 32)
+    assert torch.equal(y.view(torch.uint8).reshape(6, 32), _silu_mul_fp8_on_device(x.reshape(6, 64), scale).view(torch.uint8))
+    wide = torch.randn(4, 160, device=DEV).to(torch.bfloat16)
+    assert torch.equal(hb.silu_mul_fp8(wide[:, :128], scale).view(torch.uint8),
+                       _silu_mul_fp8_on_device(wide[:, :128], scale).view(torch.uint8))
+    with pytest.raises(AssertionError):
+        hb.silu_mul_fp8(x, torch.ones(2, device=DEV))
+    with pytest.raises(ValueError):
+        hb.silu_mul_fp8(torch.zeros(2, 24, device=DEV, dtype=torch.bfloat16), scale)
+    with pytest.raises(TypeError):
+        hb.silu_mul_fp8(torch.zeros(2, 32, device=DEV), scale)

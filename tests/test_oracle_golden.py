@@ -134,6 +134,24 @@ def test_scaled_mm_reference_kernel(golden):
                         assert float((got == ref).float().mean()) >= 0.97
 
 
+def test_silu_mul_fp8_reference_kernel(golden):
+    """The oracle against outputs of the reference's silu_mul_fp8 kernel (run by its CPU interpreter).
+
+    Where the scaled value leaves the e4m3 range the interpreter's torch cast gives NaN; the compiled kernel's
+    conversion saturates, and so do the oracle and the CUDA kernel: those positions must hold +-448."""
+    g = golden("silu_mul_fp8.npz")
+    for tag, dt in (("a", torch.bfloat16), ("b", torch.bfloat16), ("c", torch.float16)):
+        x = g.raw(f"smf_{tag}_x").view(dt)
+        scale = g.raw(f"smf_{tag}_scale")
+        ref = g.e4m3(f"smf_{tag}_kernel")
+        assert _eq_bits(ref, g.e4m3(f"smf_{tag}_torch"))  # the module's torch reference agrees with its kernel
+        got = O.silu_mul_fp8(x, scale)
+        overflow = torch.isnan(ref.float())
+        assert torch.equal(got.view(torch.uint8)[~overflow], ref.view(torch.uint8)[~overflow])
+        assert bool((got.float()[overflow].abs() == 448.0).all())
+    assert bool(torch.isnan(g.e4m3("smf_b_kernel").float()).any())  # the fixture does exercise the overflow case
+
+
 def test_moe_references(golden):
     g = golden("moe.npz")
     a, w, top1 = g.bf16("moe_a"), g.bf16("moe_w"), g.raw("moe_top1")
