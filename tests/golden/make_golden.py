@@ -217,6 +217,39 @@ def main(ref_root: str) -> None:
         out[f"smf_{tag}_torch"] = _np(smf._silu_mul_fp8_torch(x, scale))
     np.savez_compressed(HERE / "silu_mul_fp8.npz", **out)
 
+    # ---- the quant producers' KERNELS themselves (CPU interpreter), beside their torch references above --------
+    # rms_norm_per_block_quant's kernel does not run in the interpreter (a shape error inside its reference-mode
+    # broadcasting); the NVFP4 GEMV / GEMM kernels use loads or a backend the interpreter does not have.
+    out = {}
+    torch.manual_seed(55)
+    x = torch.randn(12, 2 * 256, dtype=torch.bfloat16)
+    out["k_silu_x"] = _np(x)
+    for gs in (64, 128):
+        q = torch.zeros(12, 256, dtype=torch.float8_e4m3fn)
+        sc = torch.zeros(12, 256 // gs)
+        silu.silu_and_mul_per_block_quant(q, x, sc, gs)
+        out[f"k_silu_q_{gs}"], out[f"k_silu_s_{gs}"] = _np(q), _np(sc)
+    xr = (torch.randn(12, 384) * torch.logspace(-2, 1, 12)[:, None]).to(torch.bfloat16)
+    wr = (torch.rand(384) + 0.5).to(torch.bfloat16)
+    res = torch.randn(12, 384).to(torch.bfloat16)
+    out["k_rms_x"], out["k_rms_w"], out["k_rms_res"] = _np(xr), _np(wr), _np(res)
+    for tag, r in (("", None), ("_res", res.clone())):
+        q = torch.zeros(12, 384, dtype=torch.float8_e4m3fn)
+        sc = torch.zeros(12, 1)
+        rms.rms_norm_dynamic_per_token_quant(q, xr, wr, sc, 1e-6, None, r)
+        out[f"k_rms_q{tag}"], out[f"k_rms_s{tag}"] = _np(q), _np(sc)
+        if r is not None:
+            out["k_rms_newres"] = _np(r)
+    q = torch.zeros(12, 384, dtype=torch.float8_e4m3fn)
+    sc = torch.zeros(12, 1)
+    dyn.dynamic_per_token_scaled_fp8_quant(q, xr, sc, None)
+    out["k_dyn_q"], out["k_dyn_s"] = _np(q), _np(sc)
+    q = torch.zeros(12, 384, dtype=torch.float8_e4m3fn)
+    sc = torch.zeros(12, 3)
+    grp.per_token_group_fp8_quant(xr, q, sc, 128, 1e-10, -448.0, 448.0, False)
+    out["k_grp_q"], out["k_grp_s"] = _np(q), _np(sc)
+    np.savez_compressed(HERE / "reference_kernels.npz", **out)
+
     # ---- MoE / grouped GEMM references ------------------------------------------------------------
     out = {}
     torch.manual_seed(8)

@@ -333,3 +333,25 @@ def test_silu_mul_fp8_shapes_and_errors():
         hb.silu_mul_fp8(torch.zeros(2, 24, device=DEV, dtype=torch.bfloat16), scale)
     with pytest.raises(TypeError):
         hb.silu_mul_fp8(torch.zeros(2, 32, device=DEV), scale)
+
+
+def test_against_outputs_of_the_reference_kernels(golden):
+    """CUDA kernels against what the reference's own kernels wrote (reference CPU interpreter, tests/golden)."""
+    g = golden("reference_kernels.npz")
+    x = g.bf16("k_silu_x").to(DEV)
+    for gs in (64, 128):
+        q = torch.empty(12, 256, dtype=torch.float8_e4m3fn, device=DEV)
+        s = torch.empty(12, 256 // gs, device=DEV)
+        hb.silu_and_mul_per_block_quant(q, x, s, gs)
+        # exp() differs from the CPU's in the last place: scales within a few ulp, nearly all codes identical
+        torch.testing.assert_close(s.cpu(), g.raw(f"k_silu_s_{gs}"), rtol=1e-6, atol=0)
+        assert float((q.cpu().view(torch.uint8) == g.raw(f"k_silu_q_{gs}")).float().mean()) >= 0.995
+    xr = g.bf16("k_rms_x").to(DEV)
+    q = torch.empty(12, 384, dtype=torch.float8_e4m3fn, device=DEV)
+    s = torch.empty(12, 1, device=DEV)
+    hb.dynamic_per_token_scaled_fp8_quant(q, xr, s)
+    assert torch.equal(q.cpu().view(torch.uint8), g.raw("k_dyn_q")) and torch.equal(s.cpu(), g.raw("k_dyn_s"))
+    w = g.bf16("k_rms_w").to(DEV)
+    hb.rms_norm_dynamic_per_token_quant(q, xr, w, s, 1e-6)
+    torch.testing.assert_close(s.cpu(), g.raw("k_rms_s"), rtol=1e-6, atol=0)
+    assert float((q.cpu().view(torch.uint8) == g.raw("k_rms_q")).float().mean()) >= 0.995

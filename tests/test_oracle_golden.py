@@ -152,6 +152,31 @@ def test_silu_mul_fp8_reference_kernel(golden):
     assert bool(torch.isnan(g.e4m3("smf_b_kernel").float()).any())  # the fixture does exercise the overflow case
 
 
+def test_quant_producer_reference_kernels(golden):
+    """The oracle against outputs of the reference's quant KERNELS (run by the reference's CPU interpreter), in
+    addition to the modules' torch references above."""
+    g = golden("reference_kernels.npz")
+    x = g.bf16("k_silu_x")
+    for gs in (64, 128):
+        q, s = O.silu_and_mul_per_block_quant(x, gs)
+        assert _eq_bits(q, g.e4m3(f"k_silu_q_{gs}")) and _eq_bits(s, g.raw(f"k_silu_s_{gs}"))
+    xr, wr, res = g.bf16("k_rms_x"), g.bf16("k_rms_w"), g.bf16("k_rms_res")
+    q, s, _ = O.rms_norm_dynamic_per_token_quant(xr, wr, 1e-6)
+    assert _eq_bits(q, g.e4m3("k_rms_q")) and _eq_bits(s, g.raw("k_rms_s"))
+    q, s, new_res = O.rms_norm_dynamic_per_token_quant(xr, wr, 1e-6, None, res)
+    assert _eq_bits(q, g.e4m3("k_rms_q_res")) and _eq_bits(s, g.raw("k_rms_s_res"))
+    assert _eq_bits(new_res, g.bf16("k_rms_newres"))
+    q, s = O.dynamic_per_token_scaled_fp8_quant(xr)
+    assert _eq_bits(q, g.e4m3("k_dyn_q")) and _eq_bits(s, g.raw("k_dyn_s"))
+    # per_token_group_fp8_quant: the kernel takes the group maximum and divides in the input type, its module's
+    # fp32 reference (which the oracle and the CUDA kernel follow) does not: scales agree to bf16 precision only
+    q, s = O.per_token_group_fp8_quant(xr, 128, 1e-10, -448.0, 448.0, False)
+    ks, kq = g.raw("k_grp_s"), g.e4m3("k_grp_q")
+    assert float(((s - ks).abs() / s).max()) <= 2.0**-7
+    assert float((q.view(torch.uint8) == kq.view(torch.uint8)).float().mean()) >= 0.9
+    assert float((q.float() - kq.float()).abs().max()) <= 32.0  # one e4m3 step at the top of the range
+
+
 def test_moe_references(golden):
     g = golden("moe.npz")
     a, w, top1 = g.bf16("moe_a"), g.bf16("moe_w"), g.raw("moe_top1")
