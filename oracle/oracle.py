@@ -8,8 +8,9 @@ under ``helion_b200/`` imports it and no product path falls back to it.
 
 Parity pin: every function below is checked in ``tests/test_oracle_golden.py``
 against fixtures in ``tests/golden/*.npz`` that were produced by running the
-reference's functions (imported from the reference checkout) on seeded inputs;
-``tests/golden/make_golden.py`` is the generating script.  Pieces the reference
+reference's functions (imported from the reference checkout) on seeded inputs and,
+for the FP8 operators, by running the reference's KERNELS themselves in the
+reference's CPU interpreter; ``tests/golden/make_golden.py`` is the generating script.  Pieces the reference
 does not contain (the NVFP4 quantiser with a global scale, the NVFP4 MoE
 pipeline) are compositions of pinned pieces and say so in their docstring.
 
