@@ -726,7 +726,7 @@ def wl_moe(args, dev, rank, world, timer):
             "achieved": ach, "peak": 4 * peaks["bf16_tflops"], "peak_kind": f"4 x {peaks['kind']} dense bf16 burst",
             "unit": "TFLOP/s", "frac": ach / (4 * peaks["bf16_tflops"]), "traffic": None}
     return dict(value=flops / (ms * 1e-3) / 1e12, unit="TFLOP/s", ms=ms, e2e_value=flops / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
-                h2d=host_x.numel() * 2 + host_l.numel() * 4, d2h=host_out.numel() * 2, launches=8, roofline=roof,
+                h2d=host_x.numel() * 2 + host_l.numel() * 4, d2h=host_out.numel() * 2, launches=9, roofline=roof,
                 parity=parity, extra={}, dtype="e2m1 x e2m1 with e4m3 block scales, fp32 accumulate, bf16 activations",
                 config={"workload": "moe", **c, "parallelism": f"ep{world}" if world > 1 else "single", "l2": "flushed between steps"})
 

@@ -209,6 +209,95 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32
   }
 }
 
+// ------------------------------------------------------------------ routing
+// softmax over the experts (fp32: exp(x - max) / sum) followed by top-k, one warp per token; lane l holds experts
+// l, l + 32, ...  The k winners come out in descending order, equal values by ascending expert index.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(256) moe_route_top_k_kernel(const T* __restrict__ logits, int64_t tokens, int experts,
+                                                              int top_k, float* __restrict__ weights,
+                                                              int64_t* __restrict__ chosen) {
+  const int lane = threadIdx.x & 31;
+  const int64_t token = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (token >= tokens) return;
+  const T* row = logits + token * experts;
+  float v[VPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < experts ? float(row[e]) : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    v[j] = lane + 32 * j < experts ? expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) v[j] = lane + 32 * j < experts ? __fdiv_rn(v[j], sum) : -1.f;  // -1: never chosen
+
+  float my_w = 0.f;
+  int my_e = 0;
+  for (int r = 0; r < top_k; ++r) {
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      if (v[j] > best) {  // ascending j = ascending expert index: the first maximum stays
+        best = v[j];
+        best_e = lane + 32 * j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j)
+        if (lane + 32 * j == best_e) v[j] = -1.f;
+    }
+    if (lane == (r & 31)) {
+      my_w = best;
+      my_e = best_e;
+    }
+    if ((r & 31) == 31 || r == top_k - 1) {  // lanes 0..(r % 32) hold results r - r % 32 ... r
+      if (lane <= (r & 31)) {
+        const int64_t o = token * top_k + (r - (r & 31)) + lane;
+        weights[o] = my_w;
+        chosen[o] = my_e;
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_route(const void* logits, int64_t tokens, int experts, int top_k, float* weights, int64_t* chosen,
+                 cudaStream_t s) {
+  const int64_t threads = tokens * 32;
+  const int grid = int((threads + 255) / 256);
+  const T* in = static_cast<const T*>(logits);
+#define HB200_ROUTE(V) moe_route_top_k_kernel<T, V><<<grid, 256, 0, s>>>(in, tokens, experts, top_k, weights, chosen)
+  if (experts <= 32) HB200_ROUTE(1);
+  else if (experts <= 64) HB200_ROUTE(2);
+  else if (experts <= 128) HB200_ROUTE(4);
+  else if (experts <= 256) HB200_ROUTE(8);
+  else if (experts <= 512) HB200_ROUTE(16);
+  else HB200_ROUTE(32);
+#undef HB200_ROUTE
+  return launch_status();
+}
+
 }  // namespace
 }  // namespace hb200
 
@@ -338,4 +427,18 @@ extern "C" int hb200_moe_sort_pairs(const void* expert_of_pair, int idx_is_i64, 
                                                        sorted_pairs);
   }
   return launch_status();
+}
+
+extern "C" int hb200_moe_route_top_k(const void* logits, int logits_dtype, int64_t tokens, int64_t experts,
+                                     int64_t top_k, float* weights, int64_t* chosen, void* stream) {
+  using namespace hb200;
+  if (tokens < 0 || experts <= 0 || experts > 1024 || top_k <= 0 || top_k > experts) return HB200_ERR_INVALID_ARGUMENT;
+  if (logits_dtype < 0 || logits_dtype > 2) return HB200_ERR_INVALID_ARGUMENT;
+  if (tokens == 0) return HB200_OK;
+  if (!logits || !weights || !chosen) return HB200_ERR_INVALID_ARGUMENT;
+  if (tokens > (int64_t(1) << 31)) return HB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (logits_dtype == 0) return launch_route<__nv_bfloat16>(logits, tokens, int(experts), int(top_k), weights, chosen, s);
+  if (logits_dtype == 1) return launch_route<__half>(logits, tokens, int(experts), int(top_k), weights, chosen, s);
+  return launch_route<float>(logits, tokens, int(experts), int(top_k), weights, chosen, s);
 }

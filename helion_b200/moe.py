@@ -89,10 +89,35 @@ def interleave_gate_up(w: GroupedNvfp4Weight) -> GroupedNvfp4Weight:
     return GroupedNvfp4Weight(packed, scales, w.global_scale, True)
 
 
+_ROUTE_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
 def route_top_k(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
-    """softmax over experts in fp32, then top-k; weights are used as produced (not renormalised)."""
-    probs = torch.softmax(router_logits.to(torch.float32), dim=-1)
-    return torch.topk(probs, top_k, dim=-1)
+    """softmax over experts in fp32, then top-k, in one kernel; weights are used as produced (not renormalised).
+
+    Returns ``(weights [T, top_k] fp32, experts [T, top_k] int64)`` in descending order of weight, as
+    ``torch.topk(torch.softmax(logits.float(), -1), top_k)`` does.
+    """
+    if router_logits.dim() != 2:
+        raise ValueError("router_logits must be [tokens, experts]")
+    tokens, experts = router_logits.shape
+    if not 0 < top_k <= experts:
+        raise ValueError(f"top_k must be in 1..{experts}, got {top_k}")
+    if router_logits.dtype not in _ROUTE_DTYPES:
+        router_logits = router_logits.to(torch.float32)
+    if experts > 1024:
+        raise ValueError(f"at most 1024 experts are supported, got {experts}")
+    if not router_logits.is_cuda:
+        # CPU tensors only occur in the multi-rank host-logic tests (gloo): plain tensor code there
+        probs = torch.softmax(router_logits.to(torch.float32), dim=-1)
+        return torch.topk(probs, top_k, dim=-1)
+    logits = router_logits.contiguous()
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((tokens, top_k), dtype=torch.int64, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.call("hb200_moe_route_top_k", logits.data_ptr(), _ROUTE_DTYPES[logits.dtype], tokens, experts, top_k,
+                  weights.data_ptr(), chosen.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return weights, chosen
 
 
 @dataclass

@@ -253,6 +253,14 @@ int hb200_nvfp4_grouped_matmul_256(const void* a_packed, const void* b_packed, c
                                    int64_t n, int64_t k, int64_t groups, int64_t ldc, const float* row_scale,
                                    const float* group_alpha, float alpha, int out_dtype, void* stream);
 
+/* Routing front-end of the MoE layer: softmax over the experts in fp32 (exp(x - max) / sum) followed by top-k,
+ * one kernel (the reference's examples route with torch.softmax + torch.topk outside their kernels,
+ * examples/moe_matmul_ogs.py:96-117 takes the result).  logits [tokens, experts] contiguous, logits_dtype
+ * 0 bf16 / 1 fp16 / 2 fp32; weights [tokens, top_k] fp32 and chosen [tokens, top_k] int64 are written in
+ * descending order of weight, equal weights by ascending expert index.  experts <= 1024, top_k <= experts. */
+int hb200_moe_route_top_k(const void* logits, int logits_dtype, int64_t tokens, int64_t experts, int64_t top_k,
+                          float* weights, int64_t* chosen, void* stream);
+
 /* Stable sort of the (token, slot) pairs by expert plus the per-expert counts, on the device: what
  * moe_matmul_ogs_helion_kernel_args_gen computes with bincount + argsort and a host read
  * (examples/moe_matmul_ogs.py:96-117).  expert_of_pair: one entry per pair, int64 when idx_is_i64 != 0 (what

@@ -170,3 +170,31 @@ def test_device_weight_quantiser_matches_oracle():
     assert torch.equal(b.packed.cpu(), wp)
     assert torch.equal(b.global_scale.cpu(), wg)
     assert torch.equal(b.scales.cpu().view(torch.uint8), torch.stack([s.view(torch.uint8) for s in ws]))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tokens,experts,k", [(1, 8, 2), (300, 128, 8), (64, 100, 5), (17, 1024, 33), (5, 32, 32), (0, 16, 2)])
+def test_fused_routing_matches_softmax_then_topk(tokens, experts, k, dtype):
+    g = torch.Generator().manual_seed(tokens + experts + k)
+    logits = (torch.randn(tokens, experts, generator=g) * 2).to(dtype)
+    w, e = M.route_top_k(logits.to(DEV), k)
+    torch.cuda.synchronize()
+    assert w.shape == (tokens, k) and e.shape == (tokens, k) and w.dtype is torch.float32 and e.dtype is torch.int64
+    ow, oe = O.moe_route(logits, k)
+    w, e = w.cpu(), e.cpu()
+    torch.testing.assert_close(w, ow, rtol=2e-6, atol=1e-9)
+    # the same experts in the same order, except where two probabilities are equal to within the last places
+    differs = e != oe
+    if bool(differs.any()):
+        probs = torch.softmax(logits.float(), dim=-1)
+        assert torch.allclose(probs.gather(1, e)[differs], probs.gather(1, oe)[differs], rtol=4e-6, atol=0)
+    assert bool((w[:, :-1] >= w[:, 1:]).all())  # descending
+    assert all(len(set(row.tolist())) == k for row in e)  # no expert twice
+
+
+def test_fused_routing_breaks_ties_by_expert_index():
+    logits = torch.zeros(3, 64, device=DEV)
+    logits[1, 40] = 1.0
+    w, e = M.route_top_k(logits, 4)
+    assert e[0].tolist() == [0, 1, 2, 3] and e[1].tolist() == [40, 0, 1, 2]
+    assert torch.allclose(w[0], torch.full((4,), 1 / 64, device=DEV))
