@@ -18,7 +18,8 @@ Workloads (``--workload``):
          sweep; a step is one pass over all twelve (715 MB of weights); metric TB/s; replicas only over N GPUs.
 
 Timing: every step is bracketed by its own CUDA-event pair on the launching stream and the L2 is flushed
-(a 256 MB write) between steps, outside the pairs; ms_per_step is the mean over K steps and the max over
+(a 256 MB write followed by a 256 MB read of another buffer, which pushes the write's dirty lines out) between
+steps, outside the pairs; ms_per_step is the mean over K steps and the max over
 ranks.  Steps whose launch sequence is fixed are replayed from a CUDA graph so that the host does not sit
 between kernels.  ``--impl reference`` times the CPU port of the reference's PyTorch reference functions on
 a bounded sample of the same workload.
@@ -147,6 +148,7 @@ class Timer:
         self.dev = dev
         self.world = world
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        self.sweep_buf = torch.zeros(256 << 18, dtype=torch.int32, device=dev)  # 256 MB, only ever read
 
     def sync(self):
         if self.world > 1:
@@ -157,6 +159,7 @@ class Timer:
 
     def run(self, step, steps: int, warmup: int) -> float:
         """Mean milliseconds per step (max over ranks): per-step event pairs, L2 flushed between steps."""
+        # (flush = write 256 MB, then read 256 MB: see the loop)
         for _ in range(warmup):
             step()
         self.sync()
@@ -166,7 +169,10 @@ class Timer:
         if profiled:
             torch.cuda.profiler.start()
         for s, e in pairs:
+            # L2 flush: a 256 MB write, then a 256 MB read of another buffer, so that the step neither finds its
+            # inputs in L2 nor pays for writing back the flush's dirty lines
             self.flush_buf.zero_()
+            self.sweep_buf.sum()
             s.record()
             step()
             e.record()
@@ -507,12 +513,16 @@ def wl_gemv(args, dev, rank, world, timer):
                     hb.ops._gemv_path(args.path, 57344, 8192, batch)] if not (batch > 1 and args.path == "simt") else "nvfp4_gemv_batched_kernel",
                 "launch": f"gate_up 57344x8192 M={batch}", "achieved": ach, "peak": peaks["hbm_gbs"],
                 "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                "traffic": ncu_traffic(f"gemv_gate_up_m{batch}")}
+                # the tensor-core kernel was captured with 8 rows; the weights are all but 0.1 % of its traffic
+                "traffic": ncu_traffic("gemv_gate_up_m8" if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc"
+                                       else f"gemv_gate_up_m{batch}")}
     return dict(value=layer_bytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=layer_bytes / (e2e_ms * 1e-3) / 1e12,
                 e2e_ms=e2e_ms, h2d=sum(2 * batch * k for _, k in LAYER_70B.values()),
                 d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * ((2 if world > 1 else 1) + (1 if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc" else 0)),
                 roofline=roof, parity=parity, extra={"per_matrix": per_matrix, **extra},
-                dtype="fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)",
+                dtype=("e2m1 x e2m1 block-scaled tensor-core products, fp32 accumulate (bf16 activations as four NVFP4 "
+                       "terms, bf16 out)" if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc"
+                       else "fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)"),
                 config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
                         "batch": batch, "path": args.path, "parallelism": f"column-tp{world}" if world > 1 else "single",
                         "l2": "flushed between steps; 481 MB of weights per step", "bytes_per_step": layer_bytes})
@@ -785,7 +795,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "mma", "tc"],
-                    help="GEMV kernel family (gemv workload): auto = SIMT for one row, tensor cores for 2..32")
+                    help="GEMV kernel family (gemv workload): auto = tensor cores for 1..32 rows of a large weight")
     ap.add_argument("--profile-region", type=int, default=0,
                     help="which timed region (0 = the headline one) cudaProfilerStart/Stop brackets, for "
                          "`ncu --profile-from-start off`")

@@ -98,18 +98,21 @@ def test_linearity_at_full_size():
     x1 = torch.randint(-2, 3, (k,), generator=g).to(torch.bfloat16).to(DEV)
     x2 = torch.randint(-2, 3, (k,), generator=g).to(torch.bfloat16).to(DEV)
     alpha = 2.0**-6
-    y1 = hb.nvfp4_gemv_bf16in(w, x1, s, alpha).float()
-    y2 = hb.nvfp4_gemv_bf16in(w, x2, s, alpha).float()
-    y12 = hb.nvfp4_gemv_bf16in(w, x1 + x2, s, alpha).float()
+    y1 = hb.nvfp4_gemv_bf16in(w, x1, s, alpha, path="simt").float()
+    y2 = hb.nvfp4_gemv_bf16in(w, x2, s, alpha, path="simt").float()
+    y12 = hb.nvfp4_gemv_bf16in(w, x1 + x2, s, alpha, path="simt").float()
     # all partial sums are small integers times 0.5: exact in fp16/fp32, so only the final bf16 rounding differs
     assert ((y1 + y2) - y12).abs().max() <= 2.0**-7 * y12.abs().max()
-    y_half = hb.nvfp4_gemv_bf16in(w, x1, s, alpha / 2).float()
+    y_half = hb.nvfp4_gemv_bf16in(w, x1, s, alpha / 2, path="simt").float()
     assert torch.equal(y_half * 2, y1)
     yb = hb.nvfp4_gemv_bf16in_batched(w, torch.stack([x1, x2]), s, alpha, path="simt").float()
     assert torch.equal(yb[0], y1) and torch.equal(yb[1], y2)
     # the tensor-core path sees the activations through four NVFP4 terms: the last bf16 place may differ
     yt = hb.nvfp4_gemv_bf16in_batched(w, torch.stack([x1, x2]), s, alpha, path="tc").float()
     assert (yt[0] - y1).abs().max() <= 2.0**-7 * y1.abs().max() and (yt[1] - y2).abs().max() <= 2.0**-7 * y2.abs().max()
+    # which is what a single row takes by default on a matrix of this size
+    ya = hb.nvfp4_gemv_bf16in(w, x1, s, alpha).float()
+    assert (ya - y1).abs().max() <= 2.0**-7 * y1.abs().max()
 
 
 def test_c_abi_direct_call_respects_output_bounds():
