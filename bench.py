@@ -18,8 +18,8 @@ Workloads (``--workload``):
          sweep; a step is one pass over all twelve (715 MB of weights); metric TB/s; replicas only over N GPUs.
 
 Timing: every step is bracketed by its own CUDA-event pair on the launching stream and the L2 is flushed
-(a 256 MB write followed by a 256 MB read of another buffer, which pushes the write's dirty lines out) between
-steps, outside the pairs; ms_per_step is the mean over K steps and the max over
+(a 256 MB write followed, on one GPU, by a 256 MB read of another buffer, which pushes the write's dirty lines
+out) between steps, outside the pairs; ms_per_step is the mean over K steps and the max over
 ranks.  Steps whose launch sequence is fixed are replayed from a CUDA graph so that the host does not sit
 between kernels.  ``--impl reference`` times the CPU port of the reference's PyTorch reference functions on
 a bounded sample of the same workload.
@@ -142,6 +142,7 @@ def ncu_traffic(key: str):
 # ------------------------------------------------------------------ timing
 class Timer:
     profile_region = 0  # index of the timed region bracketed by cudaProfilerStart/Stop (--profile-region)
+    flush_read = True   # --flush write+read (default) or write
     regions_seen = 0
 
     def __init__(self, dev, world: int):
@@ -172,7 +173,10 @@ class Timer:
             # L2 flush: a 256 MB write, then a 256 MB read of another buffer, so that the step neither finds its
             # inputs in L2 nor pays for writing back the flush's dirty lines
             self.flush_buf.zero_()
-            self.sweep_buf.sum()
+            # (one GPU only: with peers the extra eager kernels let the ranks drift apart between steps, and a
+            # step's peer barriers then time the other rank's lateness: 135-155 us against 112 us on two GPUs)
+            if Timer.flush_read and self.world == 1:
+                self.sweep_buf.sum()
             s.record()
             step()
             e.record()
@@ -445,6 +449,8 @@ def wl_gemv(args, dev, rank, world, timer):
     from oracle import oracle as O
 
     batch = args.batch
+    # the kernel family the step runs on: with peers a single row stays on the SIMT kernel (dist.TensorParallel.gemv)
+    used_path = "simt" if (world > 1 and batch == 1) else hb.ops._gemv_path(args.path, 57344 // world, 8192, batch)
     mats = {}
     for i, (name, (n, k)) in enumerate(LAYER_70B.items()):
         c, s, g = random_nvfp4(n // world, k, dev, 4000 + 16 * i + rank, 0.02)
@@ -455,9 +461,10 @@ def wl_gemv(args, dev, rank, world, timer):
 
     def one(name, x):
         c, s, g, n, k = mats[name]
+        path = used_path if world > 1 else args.path  # with peers: the family the fused kernels run on
         if batch == 1:
-            return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g, path=args.path).reshape(1, -1)
-        return hb.nvfp4_gemv_bf16in_batched(c, x, s, g, path=args.path)
+            return hb.nvfp4_gemv_bf16in(c, x.reshape(-1), s, g, path=path).reshape(1, -1)
+        return hb.nvfp4_gemv_bf16in_batched(c, x, s, g, path=path)
 
     tp = None
     rings = {}
@@ -510,18 +517,18 @@ def wl_gemv(args, dev, rank, world, timer):
     if per_matrix:
         ach = per_matrix["gate_up"]["GBps"]
         roof = {"bound": "hbm", "kernel": {"simt": "nvfp4_gemv_kernel", "mma": "nvfp4_gemv_batched_kernel", "tc": "nvfp4_gemv_tc_kernel"}[
-                    hb.ops._gemv_path(args.path, 57344, 8192, batch)] if not (batch > 1 and args.path == "simt") else "nvfp4_gemv_batched_kernel",
+                    used_path] if not (batch > 1 and args.path == "simt") else "nvfp4_gemv_batched_kernel",
                 "launch": f"gate_up 57344x8192 M={batch}", "achieved": ach, "peak": peaks["hbm_gbs"],
                 "peak_kind": f"{peaks['kind']} copy bandwidth", "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 # the tensor-core kernel was captured with 8 rows; the weights are all but 0.1 % of its traffic
-                "traffic": ncu_traffic("gemv_gate_up_m8" if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc"
+                "traffic": ncu_traffic("gemv_gate_up_m8" if used_path == "tc"
                                        else f"gemv_gate_up_m{batch}")}
     return dict(value=layer_bytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=layer_bytes / (e2e_ms * 1e-3) / 1e12,
                 e2e_ms=e2e_ms, h2d=sum(2 * batch * k for _, k in LAYER_70B.values()),
-                d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * ((2 if world > 1 else 1) + (1 if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc" else 0)),
+                d2h=sum(2 * batch * n for n, _ in LAYER_70B.values()), launches=4 * ((2 if world > 1 else 1) + (1 if used_path == "tc" else 0)),
                 roofline=roof, parity=parity, extra={"per_matrix": per_matrix, **extra},
                 dtype=("e2m1 x e2m1 block-scaled tensor-core products, fp32 accumulate (bf16 activations as four NVFP4 "
-                       "terms, bf16 out)" if hb.ops._gemv_path(args.path, 57344, 8192, batch) == "tc"
+                       "terms, bf16 out)" if used_path == "tc"
                        else "fp16 products, fp32 accumulate (e2m1 x e4m3 weights, bf16 in/out)"),
                 config={"workload": "gemv", "layer": "qkv 10240x8192, o 8192x8192, gate_up 57344x8192, down 8192x28672",
                         "batch": batch, "path": args.path, "parallelism": f"column-tp{world}" if world > 1 else "single",
@@ -799,8 +806,11 @@ def main() -> None:
     ap.add_argument("--profile-region", type=int, default=0,
                     help="which timed region (0 = the headline one) cudaProfilerStart/Stop brackets, for "
                          "`ncu --profile-from-start off`")
+    ap.add_argument("--flush", default="write+read", choices=["write+read", "write"],
+                    help="L2 flush between steps: a 256 MB write followed by a 256 MB read (no dirty lines left), or the write alone")
     args = ap.parse_args()
     Timer.profile_region = args.profile_region
+    Timer.flush_read = args.flush == "write+read"
     if args.impl == "reference":
         run_reference(args)
         return
