@@ -11,9 +11,10 @@
 //  * cluster form (few tiles): one thread-block cluster of 2, 4 or 8 CTAs per tile, the K range split across
 //    them, the partial sums exchanged through distributed shared memory (see the kernel's comment);
 //  * whole tiles, one per CTA, when there is nearly one tile per SM;
-//  * stream-K otherwise: the (tile, K block) units are dealt to one CTA per SM in contiguous ranges of equal
-//    length.  A tile whose K range is shared has each of its CTAs write an fp32 partial to the workspace; the last
-//    to arrive (an acq_rel counter per tile) adds them in K order and finishes the tile.
+//  * stream-K otherwise, one CTA per SM: every CTA takes the same number of whole tiles, and the tiles left over
+//    are dealt as (tile, K block) units in contiguous ranges of equal length, worked on first.  A tile whose K
+//    range is shared has each of its CTAs write an fp32 partial to the workspace; the last to arrive (an acq_rel
+//    counter per tile) adds them in K order and finishes the tile.
 // In every form partial sums are added in a fixed order: results do not depend on timing.  Large M runs through the
 // same kernel, 256 tokens per tile.
 //
@@ -126,6 +127,12 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   const int stages = g.stages;
   const int KB = g.num_kb;
   const int total = g.n_tiles * g.m_chunks * KB, grid = int(gridDim.x), cta = int(blockIdx.x);
+  // Stream-K form: every CTA first gets the same number of whole tiles (tile cta + i * grid); only the tiles left
+  // over are dealt as (tile, K block) ranges, and a CTA works on its share of those first, so that what it does
+  // last is a plain tile and the sums of shared tiles are finished while everybody still streams.
+  const int tiles_all = g.n_tiles * g.m_chunks;
+  const int whole_each = (CLUSTER > 0 || g.whole_tiles) ? 0 : tiles_all / int(gridDim.x);
+  const int rest_base = whole_each * int(gridDim.x);  // first tile of the shared remainder
   int u_begin, u_end;
   if constexpr (CLUSTER > 0) {
     const int rank = int(cluster_ctarank()), tile = cta / CLUSTER;
@@ -133,10 +140,24 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     u_end = tile * KB + range_start(rank + 1, KB, CLUSTER);
   } else {
     // beyond the counters' reach (thousands of tiles) whole tiles are dealt instead: nothing is shared then
-    u_begin = g.whole_tiles ? range_start(cta, total / KB, grid) * KB : range_start(cta, total, grid);
-    u_end = g.whole_tiles ? range_start(cta + 1, total / KB, grid) * KB : range_start(cta + 1, total, grid);
+    const int rest_total = (tiles_all - rest_base) * KB;
+    u_begin = g.whole_tiles ? range_start(cta, total / KB, grid) * KB : range_start(cta, rest_total, grid);
+    u_end = g.whole_tiles ? range_start(cta + 1, total / KB, grid) * KB : range_start(cta + 1, rest_total, grid);
   }
   const Segments segs(u_begin, u_end, KB);
+  const int rest_total = (tiles_all - rest_base) * KB;  // units of the remainder (ranges above are within it)
+  const int work_count = segs.count + whole_each;
+  // i-th piece of work of this CTA: the remainder's segments, then the whole tiles
+  auto work = [&](int i, int& tile, int& kb0, int& kb1) {
+    if (i < segs.count) {
+      segs.get(i, tile, kb0, kb1);
+      tile += rest_base;
+    } else {
+      tile = cta + (i - segs.count) * grid;
+      kb0 = 0;
+      kb1 = KB;
+    }
+  };
   const int acc_stride = g.cols < 32 ? 32 : g.cols;
 
   // one stage of (tile, K block): the stage's barrier is told the bytes, both boxes are requested
@@ -161,9 +182,9 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     fence_barrier_init();
     // The ring is empty: its first round of loads goes out now, while tensor memory is still being set up.
     int it = 0;
-    for (int i = 0; i < segs.count && it < stages; ++i) {
+    for (int i = 0; i < work_count && it < stages; ++i) {
       int tile, kb0, kb1;
-      segs.get(i, tile, kb0, kb1);
+      work(i, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1 && it < stages; ++kb, ++it) issue(it, tile, kb);
     }
   }
@@ -196,9 +217,9 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   if (warp == 0) {
     uint32_t it = 0;
     bool ok = true;
-    for (int i = 0; i < segs.count && ok; ++i) {
+    for (int i = 0; i < work_count && ok; ++i) {
       int tile, kb0, kb1;
-      segs.get(i, tile, kb0, kb1);
+      work(i, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         if (it < uint32_t(stages)) continue;  // requested during set-up
         const int s = it % stages;
@@ -211,9 +232,9 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const uint32_t idesc = make_idesc_f8(128, g.cols, format);
     uint32_t it = 0, sc = 0;
     bool ok = true;
-    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+    for (int i = 0; i < work_count && ok; ++i, ++sc) {
       int tile, kb0, kb1;
-      segs.get(i, tile, kb0, kb1);
+      work(i, tile, kb0, kb1);
       const int acc = sc % ACC;
       if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), ((sc / ACC) & 1) ^ 1, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
@@ -246,13 +267,13 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     OutT* out = static_cast<OutT*>(g.out);
     const OutT* bias = static_cast<const OutT*>(g.bias);
     const float sa_all = g.scale_a[0], sb_all = g.scale_b[0];
-    const int first_tile = u_begin / KB;
+    const int first_tile = rest_base + u_begin / KB;
     const int64_t slot_floats = int64_t(g.cols) * 128;
     uint32_t sc = 0;
     bool ok = true;
-    for (int i = 0; i < segs.count && ok; ++i, ++sc) {
+    for (int i = 0; i < work_count && ok; ++i, ++sc) {
       int tile, kb0, kb1;
-      segs.get(i, tile, kb0, kb1);
+      work(i, tile, kb0, kb1);
       const int n_blk = tile / g.m_chunks, m_blk = tile % g.m_chunks;
       const int acc = sc % ACC;
       // this row's scale and bias are fetched before the wait, not after it
@@ -352,8 +373,9 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       // a tile shared with other CTAs: publish the partial, the last arriver finishes the tile
       fp8_epilogue_bar();
       if (r_in == 0) {
-        const int c_first = owner_of(tile * KB, total, grid), c_last = owner_of(tile * KB + KB - 1, total, grid);
-        const unsigned int seen = arrive_acq_rel(&g.counters[tile]);
+        const int rt = tile - rest_base;  // the tile's index in the remainder
+        const int c_first = owner_of(rt * KB, rest_total, grid), c_last = owner_of(rt * KB + KB - 1, rest_total, grid);
+        const unsigned int seen = arrive_acq_rel(&g.counters[rt]);
         fix[0] = seen + 1u == unsigned(c_last - c_first + 1);
         fix[1] = c_first;
         fix[2] = c_last;
@@ -377,7 +399,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             for (int q = 0; q < 4; ++q) {
               const int cq = c + q;
               if (cq <= c_last) {
-                const int c_tile0 = range_start(cq, total, grid) / KB;
+                const int c_tile0 = rest_base + range_start(cq, rest_total, grid) / KB;
                 const float* src = g.partials + int64_t(2 * cq + (tile == c_tile0 ? 0 : 1)) * slot_floats;
 #pragma unroll
                 for (int j = 0; j < CW; ++j) t[q][j] = __ldcg(src + (c0 + j) * 128 + r_in);
@@ -397,7 +419,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         }
       };
       if (g.cols % 32 == 0) reduce(std::integral_constant<int, 32>{}); else reduce(std::integral_constant<int, 16>{});
-      if (r_in == 0) g.counters[tile] = 0u;
+      if (r_in == 0) g.counters[tile - rest_base] = 0u;
     }
   }
 
@@ -538,7 +560,10 @@ bool make_fp8_plan(int64_t m, int64_t n, int64_t k, int sms, Fp8Plan* out) {
     return true;
   }
   // tiles are shared between CTAs only when the ranges do not end on tile boundaries
-  const bool shared = !p.whole_tiles && ((total % p.grid) != 0 || ((total / p.grid) % p.num_kb) != 0);
+  // stream-K: every CTA takes tiles / grid whole tiles, the rest is dealt in (tile, K block) ranges
+  const int64_t rest_total = (tiles >= p.grid ? tiles % p.grid : tiles) * p.num_kb;
+  const bool shared = !p.whole_tiles && rest_total > 0 &&
+                      ((rest_total % p.grid) != 0 || ((rest_total / p.grid) % p.num_kb) != 0);
   p.workspace_bytes = shared ? kFp8CounterBytes + int64_t(2) * p.grid * p.cols * 128 * 4 : 0;
   *out = p;
   return true;
