@@ -90,6 +90,30 @@ def test_no_cpu_fallback():
         hb.per_token_group_fp8_quant(torch.randn(4, 128, dtype=torch.bfloat16), q, sc, 128, 1e-10, -448.0, 448.0, False)
 
 
+def test_fp8_consumers_validate_and_have_no_cpu_fallback():
+    a = torch.zeros(4, 64).to(torch.float8_e4m3fn)
+    b = torch.zeros(32, 64).to(torch.float8_e4m3fn).t()  # [K, N] with unit stride along K, as the reference wants
+    c = torch.empty(4, 32, dtype=torch.bfloat16)
+    one = torch.ones(1)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        hb.scaled_mm(c, a, b, one, one)
+    with pytest.raises(AssertionError):
+        hb.scaled_mm(c, a, b.contiguous(), one, one)  # b no longer K-major
+    with pytest.raises(AssertionError):
+        hb.scaled_mm(c, a, b, torch.ones(3), one)  # scale_a neither [1] nor [M]
+    with pytest.raises(AssertionError):
+        hb.scaled_mm(c, a, b, one, one, torch.zeros(32))  # bias not in c's dtype
+    with pytest.raises(TypeError):
+        hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)  # the int8 form is not built
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        hb.silu_mul_fp8(x, one)
+    with pytest.raises(AssertionError, match="Scale must be a scalar Tensor"):
+        hb.silu_mul_fp8(x, torch.ones(2))
+    with pytest.raises(ValueError):
+        hb.silu_mul_fp8(torch.zeros(4, 24, dtype=torch.bfloat16), one)
+
+
 def test_quant_producer_assertions():
     x = torch.randn(4, 256, dtype=torch.bfloat16)
     out = torch.empty(4, 128, dtype=torch.float8_e4m3fn)
@@ -115,6 +139,8 @@ def test_custom_ops_registered_with_fake_impls():
         assert y.shape == (2, 64) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
         y = torch.ops.helion_b200.nvfp4_gemv_fp4in(w, torch.empty(128, dtype=torch.uint8, device="cuda"), s, s, 1.0, "auto")
         assert y.shape == (64,)
+        y8 = torch.ops.helion_b200.silu_mul_fp8(x, torch.empty(1, device="cuda"))
+        assert y8.shape == (2, 128) and y8.dtype is torch.float8_e4m3fn
         c, sc, g = torch.ops.helion_b200.nvfp4_quantize(x, None)
         assert c.shape == (2, 128) and sc.numel() == 128 * 16 and g.shape == (2,)
 
