@@ -69,8 +69,15 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_bf16in_tc": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P, _I64, _P],
     "hb200_nvfp4_gemv_fp4in_tc": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P, _I64, _P],
     "hb200_nvfp4_gemv_bf16in_tc_builtin_scratch": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
+    "hb200_nvfp4_gemv_tc_builtin_scratch_reset": [_P],
+    "hb200_nvfp4_gemv_tc_counter_bytes": [],
+    "hb200_set_wait_budget_cycles": [_I64],
+    "hb200_selftest_bounded_wait": [_P],
+    "hb200_build_worklist_tiles": [_P, _I64, _I64, _P, _I64, _P],
+    "hb200_build_split_tiles": [_P, c_int, _I64, _I64, _I64, _P, _I64, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64,
+             "hb200_nvfp4_gemv_tc_counter_bytes": c_int64,
              "hb200_fp8_scaled_mm_workspace_bytes": c_int64}
 
 _lock = threading.Lock()

@@ -36,6 +36,8 @@ struct F16Args {
   int n, k;
   const int4* tiles;  // (group, first row, valid rows, rows to store); group < 0 ends the list early
   int num_row_tiles, n_tiles;
+  int rows_total;  // rows of A and of the output: tile entries come from device data and are not trusted beyond this
+  int groups;
 };
 
 __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -106,7 +108,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.w <= 0) continue;
+      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
       const int n_blk = tile % g.n_tiles;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % kF16Stages;
@@ -127,7 +129,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.w <= 0) continue;
+      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
       const int acc = tc % ACC;
       const uint32_t acc_ph = (tc / ACC) & 1;
       ++tc;
@@ -164,7 +166,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.w <= 0) continue;
+      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
       const int n_blk = tile % g.n_tiles;
       const int acc = tc % ACC;
       const uint32_t acc_ph = (tc / ACC) & 1;
@@ -173,7 +175,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       tcgen05_fence_after();
       const int r_in = quarter * 32 + lane;
       const int64_t row = int64_t(rt.y) + r_in;
-      const bool store = r_in < rt.w;
+      const bool store = r_in < rt.w && row >= 0 && row < g.rows_total;  // a tile list built from bad sizes cannot write outside
       const float keep = r_in < rt.z ? 1.0f : 0.0f;  // rows between "valid" and "store" are written as zero
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * kF16BlockN;
 #pragma unroll 1
@@ -242,8 +244,134 @@ build_row_tiles_kernel(const int32_t* __restrict__ offsets, int groups, int4* __
   }
 }
 
+// Row tiles from per-group row counts ("split sizes", device-resident, int32 or int64, element stride `stride`):
+// group g owns rows [P_g, P_g + size_g) with P the raw running sum of the sizes as given, clipped to the rows that
+// exist: a size is first clipped to [0, total_rows] (in 64 bits, before any narrowing), the interval then to
+// [0, total_rows).  Rows no group covers get no tile.  One CTA.
+template <typename SizeT>
+__global__ void __launch_bounds__(256)
+build_split_tiles_kernel(const SizeT* __restrict__ sizes, int64_t stride, int groups, int total_rows,
+                         int4* __restrict__ tiles, int max_tiles) {
+  __shared__ int32_t first_tile[1025];
+  __shared__ int32_t lo_row[1024], hi_row[1024];
+  if (threadIdx.x == 0) {
+    long long prefix = 0;
+    int32_t t = 0;
+    for (int gidx = 0; gidx < groups; ++gidx) {
+      const long long raw = static_cast<long long>(sizes[int64_t(gidx) * stride]);
+      const long long len = raw < 0 ? 0 : (raw > total_rows ? total_rows : raw);
+      long long lo = prefix, hi = prefix + len;
+      lo = lo < 0 ? 0 : (lo > total_rows ? total_rows : lo);
+      hi = hi < 0 ? 0 : (hi > total_rows ? total_rows : hi);
+      lo_row[gidx] = int32_t(lo);
+      hi_row[gidx] = int32_t(hi > lo ? hi : lo);
+      first_tile[gidx] = t;
+      t += (hi_row[gidx] - lo_row[gidx] + 127) / 128;
+      prefix += raw;  // the raw sum: a negative size moves the groups after it back
+    }
+    first_tile[groups] = t;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    int4 info = make_int4(-1, 0, 0, 0);
+    if (t < first_tile[groups]) {
+      int lo = 0, hi = groups;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (first_tile[mid] <= t) lo = mid; else hi = mid;
+      }
+      const int32_t local = (t - first_tile[lo]) * 128;
+      const int32_t rows = min(128, hi_row[lo] - lo_row[lo] - local);
+      info = make_int4(lo, lo_row[lo] + local, rows, rows);
+    }
+    tiles[t] = info;
+  }
+}
+
+// Row tiles of a DeepGEMM-style worklist: item i = (group, start row, valid rows, rows to store) becomes
+// ceil(store / 128) tiles.  Nothing in an item is trusted: a negative group or start drops the item, store is
+// clipped to the rows that exist past start, valid to store; tiles past max_tiles are dropped.  One CTA.
+__global__ void __launch_bounds__(256)
+build_worklist_tiles_kernel(const int4* __restrict__ items, int num_items, int total_rows, int4* __restrict__ tiles,
+                            int max_tiles) {
+  extern __shared__ int32_t first_tile[];  // [num_items + 1]
+  auto store_rows = [&](const int4 it) -> int32_t {
+    if (it.x < 0 || it.y < 0 || it.y >= total_rows) return 0;
+    return max(0, min(it.w, total_rows - it.y));
+  };
+  if (threadIdx.x == 0) {
+    int32_t t = 0;
+    for (int i = 0; i < num_items; ++i) {
+      first_tile[i] = t;
+      t += (store_rows(items[i]) + 127) / 128;
+    }
+    first_tile[num_items] = t;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    int4 info = make_int4(-1, 0, 0, 0);
+    if (t < first_tile[num_items]) {
+      int lo = 0, hi = num_items;  // last item with first_tile <= t (items without tiles share a value)
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (first_tile[mid] <= t) lo = mid; else hi = mid;
+      }
+      const int4 it = items[lo];
+      const int32_t local = (t - first_tile[lo]) * 128;
+      const int32_t store = store_rows(it);
+      const int32_t valid = max(0, min(it.z, store));
+      info = make_int4(it.x, it.y + local, max(0, min(128, valid - local)), min(128, store - local));
+    }
+    tiles[t] = info;
+  }
+}
+
 }  // namespace
 }  // namespace hb200
+
+// Tile list (the row_tiles argument of hb200_grouped_gemm_f16) for a worklist [items, 4] of
+// (group, start row, valid rows, rows to store) as grouped_gemm_deepgemm takes it
+// (pretuned_kernels/grouped_gemm_deepgemm/grouped_gemm_deepgemm.py:172-224), built on the device without a
+// host read: ceil(total_rows / 128) + items entries always suffice for items whose row ranges do not overlap.
+extern "C" int hb200_build_worklist_tiles(const int32_t* worklist, int64_t items, int64_t total_rows,
+                                          int32_t* row_tiles, int64_t max_tiles, void* stream) {
+  using namespace hb200;
+  if (!row_tiles || (items > 0 && !worklist)) return HB200_ERR_INVALID_ARGUMENT;
+  if (items < 0 || items > 8192 || total_rows < 0 || total_rows > 0x7fffff00 || max_tiles < 0 || max_tiles > 0xffffff)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(row_tiles) % 16 || reinterpret_cast<uintptr_t>(worklist) % 16)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_tiles == 0) return HB200_OK;
+  build_worklist_tiles_kernel<<<1, 256, size_t(items + 1) * 4, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const int4*>(worklist), int(items), int(total_rows), reinterpret_cast<int4*>(row_tiles),
+      int(max_tiles));
+  return launch_status();
+}
+
+// Tile list from device-resident per-group row counts (the "device split sizes" of the reference's grouped
+// tcgen05 kernels, test/test_cute_grouped_gemm_split_sizes.py:620-745): sizes are int64 (sizes_are_i64 != 0) or
+// int32 with an element stride; oversized, negative and beyond-int32 entries are clipped as that test pins them,
+// never trusted.  groups <= 1024; max_tiles >= ceil(total_rows / 128) + groups suffices for sizes that do not
+// make groups overlap (tiles past max_tiles are dropped).
+extern "C" int hb200_build_split_tiles(const void* split_sizes, int sizes_are_i64, int64_t stride, int64_t groups,
+                                       int64_t total_rows, int32_t* row_tiles, int64_t max_tiles, void* stream) {
+  using namespace hb200;
+  if (!split_sizes || !row_tiles) return HB200_ERR_INVALID_ARGUMENT;
+  if (groups <= 0 || groups > 1024 || stride <= 0 || total_rows < 0 || total_rows > 0x7fffff00 || max_tiles < 0 ||
+      max_tiles > 0xffffff)
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(row_tiles) % 16 || reinterpret_cast<uintptr_t>(split_sizes) % (sizes_are_i64 ? 8 : 4))
+    return HB200_ERR_INVALID_ARGUMENT;
+  if (max_tiles == 0) return HB200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (sizes_are_i64)
+    build_split_tiles_kernel<long long><<<1, 256, 0, s>>>(static_cast<const long long*>(split_sizes), stride, int(groups),
+                                                         int(total_rows), reinterpret_cast<int4*>(row_tiles), int(max_tiles));
+  else
+    build_split_tiles_kernel<int32_t><<<1, 256, 0, s>>>(static_cast<const int32_t*>(split_sizes), stride, int(groups),
+                                                       int(total_rows), reinterpret_cast<int4*>(row_tiles), int(max_tiles));
+  return launch_status();
+}
 
 extern "C" int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_t* row_tiles,
                                       int64_t num_row_tiles, int64_t a_rows, int64_t n, int64_t k, int64_t groups,
@@ -261,7 +389,7 @@ extern "C" int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, c
   if (!make_f16_map(&ta, a, a_rows, k, 128, is_bf16 != 0)) return HB200_ERR_CUDA;
   if (!make_f16_map(&tb, b, n * groups, k, kF16BlockN, is_bf16 != 0)) return HB200_ERR_CUDA;
   F16Args g{out, ldc, int(n), int(k), reinterpret_cast<const int4*>(row_tiles), int(num_row_tiles),
-            int((n + kF16BlockN - 1) / kF16BlockN)};
+            int((n + kF16BlockN - 1) / kF16BlockN), int(a_rows), int(groups)};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t tiles = num_row_tiles * g.n_tiles;
@@ -294,6 +422,9 @@ extern "C" int hb200_build_row_tiles(const int32_t* group_offsets, int64_t group
 }
 
 namespace hb200 {
+// Wait budget of this translation unit's bounded mbarrier waits (see hb200_set_wait_budget_cycles).
+int f16_set_wait_budget(long long cycles) { return sm100::set_wait_budget_cycles(cycles) ? HB200_OK : HB200_ERR_CUDA; }
+
 // Sticky status of this translation unit's kernels, folded into hb200_device_status().
 int f16_device_status(int reset) {
   int v = 0;

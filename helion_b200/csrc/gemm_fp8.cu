@@ -667,6 +667,9 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
 }
 
 namespace hb200 {
+// Wait budget of this translation unit's bounded mbarrier waits (see hb200_set_wait_budget_cycles).
+int fp8_set_wait_budget(long long cycles) { return sm100::set_wait_budget_cycles(cycles) ? HB200_OK : HB200_ERR_CUDA; }
+
 // Sticky status of this translation unit's kernels, folded into hb200_device_status().
 int fp8_device_status(int reset) {
   int v = 0;

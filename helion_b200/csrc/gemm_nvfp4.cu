@@ -586,6 +586,47 @@ int f16_device_status(int reset);
 int peer_device_status(int reset);
 int gemv_tc_device_status(int reset);
 int fp8_device_status(int reset);
+int f16_set_wait_budget(long long cycles);
+int peer_set_wait_budget(long long cycles);
+int gemv_tc_set_wait_budget(long long cycles);
+int fp8_set_wait_budget(long long cycles);
+
+namespace {
+// One CTA whose thread 0 waits, with the bounded wait every pipeline here uses, on an mbarrier that nothing
+// ever completes: the wait runs out, the kernel records the sticky timeout status and returns.
+__global__ void bounded_wait_selftest_kernel() {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    sm100::mbar_init(sm100::smem_u32(&bar), 1);
+    sm100::fence_barrier_init();
+    if (!sm100::mbar_wait(sm100::smem_u32(&bar), 0, &abort_flag)) atomicMin(&g_device_status, HB200_ERR_DEVICE_TIMEOUT);
+  }
+}
+}  // namespace
+}  // namespace hb200
+
+// Sets the budget, in SM clock cycles, of every bounded device-side wait of the library (mbarrier waits of the
+// tcgen05 pipelines, the flag wait of hb200_peer_barrier) on the current device; the default is 4e9 cycles,
+// about two seconds.  Synchronous (a copy to device variables); not for use while kernels are in flight.
+extern "C" int hb200_set_wait_budget_cycles(int64_t cycles) {
+  using namespace hb200;
+  if (cycles <= 0) return HB200_ERR_INVALID_ARGUMENT;
+  if (!sm100::set_wait_budget_cycles(cycles)) return HB200_ERR_CUDA;
+  int rc = f16_set_wait_budget(cycles);
+  if (rc == HB200_OK) rc = peer_set_wait_budget(cycles);
+  if (rc == HB200_OK) rc = gemv_tc_set_wait_budget(cycles);
+  if (rc == HB200_OK) rc = fp8_set_wait_budget(cycles);
+  return rc;
+}
+
+// Launches a one-CTA kernel whose bounded wait cannot be satisfied (an mbarrier nothing arrives on), to check
+// the expiry path: after it, hb200_device_status reads HB200_ERR_DEVICE_TIMEOUT until reset.  It runs for one wait
+// budget, so shorten the budget first.
+extern "C" int hb200_selftest_bounded_wait(void* stream) {
+  hb200::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
+  return hb200::launch_status();
 }
 
 extern "C" int hb200_device_status(int reset) {

@@ -607,12 +607,20 @@ int check_common(const void* w, const void* x, const void* ws, int64_t n, int64_
 
 }  // namespace
 
+// Wait budget of this translation unit's bounded mbarrier waits (see hb200_set_wait_budget_cycles).
+int gemv_tc_set_wait_budget(long long cycles) { return sm100::set_wait_budget_cycles(cycles) ? HB200_OK : HB200_ERR_CUDA; }
+
+int builtin_scratch_clear_counters_sync();
+
 int gemv_tc_device_status(int reset) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_device_status_gemv_tc, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
   if (reset && v != 0) {
     const int zero = 0;
     if (cudaMemcpyToSymbol(g_device_status_gemv_tc, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
+    // a kernel that gave up may have left tile arrival counters non-zero: clear the built-in scratch's here
+    // (caller-owned workspaces are the caller's to clear: their first hb200_nvfp4_gemv_tc_counter_bytes())
+    if (builtin_scratch_clear_counters_sync() != HB200_OK) return HB200_ERR_CUDA;
   }
   return v;
 }
@@ -719,7 +727,35 @@ int builtin_scratch(cudaStream_t stream, void** out) {
 }
 
 }  // namespace
+
+// Clears the arrival counters of the current device's built-in scratch, if that device has used it; device-synchronous.
+int builtin_scratch_clear_counters_sync() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return HB200_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return HB200_OK;
+  std::lock_guard<std::mutex> lock(g_builtin_mutex);
+  if (g_builtin_ptr[dev] == nullptr) return HB200_OK;
+  return cudaMemset(g_builtin_ptr[dev], 0, size_t(kMaxRowTiles) * 4) == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
+}
+
 }  // namespace hb200
+
+// Re-zeroes, on `stream`, the part of the built-in scratch that must be zero between calls (the tile arrival
+// counters).  Needed after a call that ended with HB200_ERR_DEVICE_TIMEOUT or after two calls overlapped on the
+// device: either can leave counters non-zero, and every later call would then leave tiles unwritten.  Allocates
+// nothing.  (hb200_device_status(1) does the same, synchronously, when it clears a non-zero status.)
+extern "C" int hb200_nvfp4_gemv_tc_builtin_scratch_reset(void* stream) {
+  using namespace hb200;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  void* scratch = nullptr;
+  const int rs = builtin_scratch(s, &scratch);
+  if (rs != HB200_OK) return rs;
+  return cudaMemsetAsync(scratch, 0, size_t(kMaxRowTiles) * 4, s) == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
+}
+
+// Bytes at the start of every tensor-core GEMV workspace (caller-owned or built-in) that hold the tile arrival
+// counters: the only part that must be zero when a call starts.
+extern "C" int64_t hb200_nvfp4_gemv_tc_counter_bytes(void) { return int64_t(hb200::kMaxRowTiles) * 4; }
 
 extern "C" int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_packed, const void* x_bf16,
                                                           const void* weight_scale, void* out_bf16, int64_t n,

@@ -8,7 +8,7 @@
 // pushed into its buffer.  All ranks must call it the same number of times; the kernel keeps no host state,
 // so a CUDA graph that contains it can be replayed.
 //
-// The wait is bounded (about two seconds of SM clock): on expiry the kernel records a sticky
+// The wait is bounded (about two seconds of SM clock unless hb200_set_wait_budget_cycles changed it): on expiry the kernel records a sticky
 // HB200_ERR_DEVICE_TIMEOUT, readable through hb200_device_status, and returns.
 #include "common.cuh"
 
@@ -24,7 +24,7 @@ struct BarrierArgs {
   int rank, world;
 };
 
-constexpr long long kWaitCycles = 4000000000ll;
+__device__ long long g_peer_wait_cycles = 4000000000ll;  // settable: hb200_set_wait_budget_cycles
 
 __global__ void peer_barrier_kernel(const BarrierArgs a) {
   __shared__ uint32_t epoch_s;
@@ -45,7 +45,7 @@ __global__ void peer_barrier_kernel(const BarrierArgs a) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (int32_t(v - epoch) >= 0) break;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > *const_cast<volatile long long*>(&g_peer_wait_cycles)) {
       atomicMin(&g_device_status_peer, HB200_ERR_DEVICE_TIMEOUT);
       break;
     }
@@ -63,6 +63,10 @@ int peer_device_status(int reset) {
     if (cudaMemcpyToSymbol(g_device_status_peer, &zero, sizeof(int)) != cudaSuccess) return HB200_ERR_CUDA;
   }
   return v;
+}
+
+int peer_set_wait_budget(long long cycles) {
+  return cudaMemcpyToSymbol(g_peer_wait_cycles, &cycles, sizeof(cycles)) == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
 }
 
 }  // namespace hb200

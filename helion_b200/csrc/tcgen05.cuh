@@ -63,10 +63,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait: gives up after `budget_cycles` SM clocks or as soon as another
+// Bounded wait: gives up after the wait budget (SM clocks) or as soon as another
 // role of the CTA has raised *abort_flag, so a broken pipeline ends with an
 // error status instead of a hang.  Returns false when it gave up.
-constexpr long long kWaitBudgetCycles = 4000000000LL;  // about two seconds
+// The budget is a device variable (one copy per translation unit that includes this header, each set by
+// set_wait_budget_cycles() of that unit; hb200_set_wait_budget_cycles sets them all): about two seconds by
+// default, shortened by tests that make a wait run out.
+constexpr long long kWaitBudgetCycles = 4000000000LL;
+static __device__ long long g_wait_budget_cycles = kWaitBudgetCycles;
+
+static inline bool set_wait_budget_cycles(long long cycles) {
+  return cudaMemcpyToSymbol(g_wait_budget_cycles, &cycles, sizeof(cycles)) == cudaSuccess;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -75,7 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 63u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > *const_cast<volatile long long*>(&g_wait_budget_cycles)) {
         *abort_flag = 1;
         return false;
       }

@@ -272,37 +272,48 @@ def exchange_rows(rows: Tensor, send_counts: list[int], recv_counts: list[int], 
 ExpertFn = Callable[[Tensor, Tensor], Tensor]  # (rows [R, H], local expert id [R]) -> rows [R, H]
 
 
-def expert_parallel_moe(x: Tensor, router_logits: Tensor, top_k: int, num_experts: int, expert_fn: ExpertFn,
-                        group=None) -> Tensor:
-    """MoE layer over expert-parallel ranks.  ``x [T_local, H]`` are this rank's tokens; ``expert_fn`` applies
-    this rank's experts to the rows it receives (no routing weight).  Returns bf16 ``[T_local, H]``."""
-    from .moe import route_top_k
+Router = Callable[[Tensor, int], tuple[Tensor, Tensor]]       # (logits, top_k) -> (weights [T, k], experts [T, k])
+Combine = Callable[[Tensor, Tensor, Tensor, int], Tensor]      # (rows [P, H], row_of_pair [P], weights [P], T) -> [T, H]
 
-    weights, experts = route_top_k(router_logits, top_k)
+
+def combine_rows(back: Tensor, row_of_pair: Tensor, pair_weight: Tensor, tokens: int) -> Tensor:
+    """``out[t] = bf16(sum_s w[t*k+s] * back[row_of_pair[t*k+s]])`` in fp32 and slot order (``hb200_moe_combine``)."""
+    from . import _lib
+
+    top_k = row_of_pair.numel() // tokens
+    hidden = back.shape[1]
+    if not back.is_cuda or back.dtype is not torch.bfloat16 or hidden % 8:
+        raise ValueError("combine_rows wants CUDA bfloat16 rows with hidden % 8 == 0")
+    back = back.contiguous()
+    out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=back.device)
+    with torch.cuda.device(back.device):
+        _lib.call("hb200_moe_combine", back.data_ptr(), back.stride(0), row_of_pair.to(torch.int32).data_ptr(),
+                  pair_weight.to(torch.float32).contiguous().data_ptr(), out.data_ptr(), tokens, top_k, hidden,
+                  torch.cuda.current_stream(back.device).cuda_stream)
+    return out
+
+
+def expert_parallel_moe(x: Tensor, router_logits: Tensor, top_k: int, num_experts: int, expert_fn: ExpertFn,
+                        group=None, *, router: Router | None = None, combine: Combine | None = None) -> Tensor:
+    """MoE layer over expert-parallel ranks with the process group's all-to-all as the data plane.
+    ``x [T_local, H]`` are this rank's tokens; ``expert_fn`` applies this rank's experts to the rows it receives
+    (no routing weight).  Returns bf16 ``[T_local, H]``.  ``router`` and ``combine`` default to the CUDA kernels
+    (``moe.route_top_k``, :func:`combine_rows`); host-logic tests inject tensor-code stand-ins."""
+    if router is None:
+        from .moe import route_top_k as router
+    if combine is None:
+        combine = combine_rows
+    weights, experts = router(router_logits, top_k)
     plan = plan_dispatch(experts, num_experts, group)
     token_of_pair = plan.order // top_k
     rows = exchange_rows(x[token_of_pair], plan.send_counts, plan.recv_counts, group)
     o = expert_fn(rows, plan.local_expert)
     back = exchange_rows(o, plan.recv_counts, plan.send_counts, group)
     # `back` is in sorted-pair order: row p belongs to pair order[p]
-    if x.is_cuda and back.dtype is torch.bfloat16 and x.shape[1] % 8 == 0:
-        # weighted sum of every token's top_k rows in one pass (fp32 accumulation), on the device kernel
-        from . import _lib
-
-        pairs = plan.order.numel()
-        row_of_pair = torch.empty(pairs, dtype=torch.int32, device=x.device)
-        row_of_pair[plan.order] = torch.arange(pairs, dtype=torch.int32, device=x.device)
-        w = weights.reshape(-1).to(torch.float32).contiguous()
-        back = back.contiguous()
-        out = torch.empty(x.shape[0], x.shape[1], dtype=torch.bfloat16, device=x.device)
-        with torch.cuda.device(x.device):
-            _lib.call("hb200_moe_combine", back.data_ptr(), back.stride(0), row_of_pair.data_ptr(), w.data_ptr(),
-                      out.data_ptr(), x.shape[0], top_k, x.shape[1], torch.cuda.current_stream(x.device).cuda_stream)
-        return out
-    w_sorted = weights.reshape(-1)[plan.order].to(torch.float32)
-    out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32, device=x.device)
-    out.index_add_(0, token_of_pair, back.to(torch.float32) * w_sorted[:, None])
-    return out.to(torch.bfloat16)
+    pairs = plan.order.numel()
+    row_of_pair = torch.empty(pairs, dtype=torch.int32, device=x.device)
+    row_of_pair[plan.order] = torch.arange(pairs, dtype=torch.int32, device=x.device)
+    return combine(back, row_of_pair, weights.reshape(-1), x.shape[0])
 
 
 def make_nvfp4_expert_fn(w_gate_up, w_down) -> ExpertFn:

@@ -92,6 +92,24 @@ def interleave_gate_up(w: GroupedNvfp4Weight) -> GroupedNvfp4Weight:
 _ROUTE_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
+@torch.library.custom_op("helion_b200::moe_route_top_k", mutates_args=())
+def _route_top_k_op(logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
+    _require_cuda(logits)
+    tokens, experts = logits.shape
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
+    chosen = torch.empty((tokens, top_k), dtype=torch.int64, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.call("hb200_moe_route_top_k", logits.data_ptr(), _ROUTE_DTYPES[logits.dtype], tokens, experts, top_k,
+                  weights.data_ptr(), chosen.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return weights, chosen
+
+
+@_route_top_k_op.register_fake
+def _(logits, top_k):
+    return (logits.new_empty((logits.shape[0], top_k), dtype=torch.float32),
+            logits.new_empty((logits.shape[0], top_k), dtype=torch.int64))
+
+
 def route_top_k(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
     """softmax over experts in fp32, then top-k, in one kernel; weights are used as produced (not renormalised).
 
@@ -107,17 +125,7 @@ def route_top_k(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
         router_logits = router_logits.to(torch.float32)
     if experts > 1024:
         raise ValueError(f"at most 1024 experts are supported, got {experts}")
-    if not router_logits.is_cuda:
-        # CPU tensors only occur in the multi-rank host-logic tests (gloo): plain tensor code there
-        probs = torch.softmax(router_logits.to(torch.float32), dim=-1)
-        return torch.topk(probs, top_k, dim=-1)
-    logits = router_logits.contiguous()
-    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
-    chosen = torch.empty((tokens, top_k), dtype=torch.int64, device=logits.device)
-    with torch.cuda.device(logits.device):
-        _lib.call("hb200_moe_route_top_k", logits.data_ptr(), _ROUTE_DTYPES[logits.dtype], tokens, experts, top_k,
-                  weights.data_ptr(), chosen.data_ptr(), torch.cuda.current_stream().cuda_stream)
-    return weights, chosen
+    return _route_top_k_op(router_logits.contiguous(), top_k)
 
 
 @dataclass
@@ -131,18 +139,17 @@ class MoeSchedule:
     pad: int = 128          # every expert's rows are padded to a multiple of this (128, or 256 for CTA-pair tiles)
 
 
-def build_schedule(experts_per_token: Tensor, num_experts: int, pad: int = 128) -> MoeSchedule:
-    """Sort the (token, slot) pairs by expert (stable, as examples/moe_matmul_ogs.py:107-109 does for
-    top-1) and lay the experts out in groups padded to ``pad`` rows (128, or 256 for the CTA-pair grouped
-    GEMM); all on the device."""
-    if pad not in (128, 256):
-        raise ValueError(f"pad must be 128 or 256, got {pad}")
-    _require_cuda(experts_per_token)
-    flat = experts_per_token.reshape(-1).contiguous()
+def _max_tiles(pairs: int, num_experts: int, pad: int) -> int:
+    # bound that does not depend on the routing (in 128-row units; even for 256-row padding)
+    max_tiles = ceil_div(pairs, 128) + num_experts * (pad // 128)
+    return max_tiles + max_tiles % (pad // 128)
+
+
+@torch.library.custom_op("helion_b200::moe_build_schedule", mutates_args=())
+def _build_schedule_op(flat: Tensor, num_experts: int, pad: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    _require_cuda(flat)
     pairs = flat.numel()
     dev = flat.device
-    if flat.dtype not in (torch.int64, torch.int32):
-        flat = flat.to(torch.int64)
     # stable counting sort + per-expert counts in three small launches (no radix sort, no host read)
     sorted_pairs = torch.empty(pairs, dtype=torch.int32, device=dev)
     counts = torch.empty(num_experts, dtype=torch.int32, device=dev)
@@ -150,9 +157,7 @@ def build_schedule(experts_per_token: Tensor, num_experts: int, pad: int = 128) 
     with torch.cuda.device(dev):
         _lib.call("hb200_moe_sort_pairs", flat.data_ptr(), int(flat.dtype is torch.int64), pairs, num_experts,
                   sorted_pairs.data_ptr(), counts.data_ptr(), scratch.data_ptr(), _stream())
-    # bound that does not depend on the routing (in 128-row units; even for 256-row padding)
-    max_tiles = ceil_div(pairs, 128) + num_experts * (pad // 128)
-    max_tiles += max_tiles % (pad // 128)
+    max_tiles = _max_tiles(pairs, num_experts, pad)
     tile_info = torch.empty(max_tiles, 2, dtype=torch.int32, device=dev)
     padded_offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     row_of_sorted = torch.empty(pairs, dtype=torch.int32, device=dev)
@@ -164,7 +169,28 @@ def build_schedule(experts_per_token: Tensor, num_experts: int, pad: int = 128) 
             padded_offsets.data_ptr(), tile_info.data_ptr(), max_tiles, row_of_sorted.data_ptr(),
             row_of_pair.data_ptr(), _stream(),
         )
-    return MoeSchedule(max_tiles, tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair, pad)
+    return tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair
+
+
+@_build_schedule_op.register_fake
+def _(flat, num_experts, pad):
+    pairs = flat.numel()
+    i32 = dict(dtype=torch.int32)
+    return (flat.new_empty((_max_tiles(pairs, num_experts, pad), 2), **i32), flat.new_empty((num_experts + 1,), **i32),
+            flat.new_empty((pairs,), **i32), flat.new_empty((pairs,), **i32), flat.new_empty((pairs,), **i32))
+
+
+def build_schedule(experts_per_token: Tensor, num_experts: int, pad: int = 128) -> MoeSchedule:
+    """Sort the (token, slot) pairs by expert (stable, as examples/moe_matmul_ogs.py:107-109 does for
+    top-1) and lay the experts out in groups padded to ``pad`` rows (128, or 256 for the CTA-pair grouped
+    GEMM); all on the device."""
+    if pad not in (128, 256):
+        raise ValueError(f"pad must be 128 or 256, got {pad}")
+    flat = experts_per_token.reshape(-1).contiguous()
+    if flat.dtype not in (torch.int64, torch.int32):
+        flat = flat.to(torch.int64)
+    tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair = _build_schedule_op(flat, num_experts, pad)
+    return MoeSchedule(tile_info.shape[0], tile_info, padded_offsets, sorted_pairs, row_of_sorted, row_of_pair, pad)
 
 
 def _quantize_rows(x: Tensor, k: int, sched: MoeSchedule, src_div: int, item_scale: Tensor | None, silu_mul: bool,
@@ -260,24 +286,57 @@ def _quantize_rows_amax(y: Tensor, row_amax: Tensor, k: int, sched: MoeSchedule,
     return codes, scales, gscale
 
 
+@torch.library.custom_op("helion_b200::nvfp4_moe", mutates_args=())
+def _nvfp4_moe_op(x: Tensor, router_logits: Tensor, top_k: int, gu_packed: Tensor, gu_scales: Tensor,
+                  gu_global: Tensor, gu_interleaved: bool, d_packed: Tensor, d_scales: Tensor, d_global: Tensor) -> Tensor:
+    return _nvfp4_moe_impl(x, router_logits, top_k, GroupedNvfp4Weight(gu_packed, gu_scales, gu_global, gu_interleaved),
+                           GroupedNvfp4Weight(d_packed, d_scales, d_global), None)
+
+
+@_nvfp4_moe_op.register_fake
+def _(x, router_logits, top_k, gu_packed, gu_scales, gu_global, gu_interleaved, d_packed, d_scales, d_global):
+    return x.new_empty(x.shape)
+
+
 def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNvfp4Weight,
-              w_down: GroupedNvfp4Weight) -> Tensor:
-    """NVFP4 MoE layer: ``x [T, H]`` bf16, ``router_logits [T, E]`` -> bf16 ``[T, H]``."""
+              w_down: GroupedNvfp4Weight, *, intermediates: dict | None = None) -> Tensor:
+    """NVFP4 MoE layer: ``x [T, H]`` bf16, ``router_logits [T, E]`` -> bf16 ``[T, H]``
+    (``torch.ops.helion_b200.nvfp4_moe`` on the bundles' tensors).
+
+    The top-k, NVFP4 form of ``moe_matmul_ogs`` (examples/moe_matmul_ogs.py:31-124): softmax-then-top-k routing
+    weights used without renormalisation, per-token NVFP4 activations, SiLU-mul between the two expert GEMMs
+    (gate rows first), routing-weighted sum over the top-k slots in slot order.
+
+    ``intermediates`` (a dict, filled in place) receives what the second expert GEMM consumes, for parity
+    checks: the routing (``weights``, ``experts``), the schedule (``sched``) and, over the padded row layout,
+    the re-quantised SiLU-mul output (``a2`` packed codes, ``sf2`` swizzled scales, ``g2`` row factors with the
+    routing weight folded in) and ``y`` (bf16 SiLU-mul output) when the fused epilogue produced it.
+    """
     _require_cuda(x, router_logits)
     if x.dtype is not torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
         raise ValueError("x must be a contiguous 2D bfloat16 tensor")
-    t, h = x.shape
+    h = x.shape[1]
     e = w_gate_up.experts
     inter = w_gate_up.n // 2
     if w_gate_up.k != h or w_down.k != inter or w_down.n != h or w_down.experts != e:
         raise ValueError("expert weight shapes do not match the activations")
+    if intermediates is not None:
+        return _nvfp4_moe_impl(x, router_logits, top_k, w_gate_up, w_down, intermediates)
+    return _nvfp4_moe_op(x, router_logits, top_k, w_gate_up.packed, w_gate_up.scales, w_gate_up.global_scale,
+                         w_gate_up.gate_up_interleaved, w_down.packed, w_down.scales, w_down.global_scale)
+
+
+def _nvfp4_moe_impl(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNvfp4Weight,
+                    w_down: GroupedNvfp4Weight, intermediates: dict | None) -> Tensor:
+    t, h = x.shape
+    e = w_gate_up.experts
+    inter = w_gate_up.n // 2
     weights, experts = route_top_k(router_logits, top_k)
-    # (build_schedule(..., pad=256) would put the second GEMM on CTA pairs: 313 against 350 us on the benchmark
-    # shape, but the first GEMM's static tile round-robin then meets the padding-only tiles and loses more)
     sched = build_schedule(experts, e)
     # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
     w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()
     a1, sf1, g1 = _quantize_and_gather(x, sched, top_k)
+    y = None
     if w_gate_up.gate_up_interleaved:
         # SiLU-mul in the GEMM's epilogue: the [rows, 2I] intermediate never reaches memory
         y, row_amax = grouped_matmul_silu(a1, sf1, w_gate_up, sched, g1)
@@ -290,4 +349,6 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
     with torch.cuda.device(x.device):
         _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(), None,
                   out.data_ptr(), t, top_k, h, _stream())
+    if intermediates is not None:
+        intermediates.update(weights=weights, experts=experts, sched=sched, a2=a2, sf2=sf2, g2=g2, y=y)
     return out

@@ -11,6 +11,7 @@ CUDA stream.  There is no CPU or eager fallback: non-CUDA tensors raise.
 from __future__ import annotations
 
 import ctypes
+import threading
 
 import torch
 from torch import Tensor
@@ -68,20 +69,72 @@ def _check_numel(name: str, t: Tensor, expected: int) -> None:
 
 
 # ------------------------------------------------------------------ custom ops
-# Workspace of the tensor-core GEMV (activation terms, split-K partials, tile counters): one zero-filled
-# buffer per (device, stream), grown on demand.  Calls on one stream are ordered, so they can share it.
+# Workspace of the tensor-core GEMV and of scaled_mm's stream-K form (activation terms, split-K partials, tile
+# arrival counters): one buffer per (device, stream), grown on demand, cached under a lock.  Calls on one stream
+# are ordered, so they can share it.  Only the first _COUNTER_BYTES (the arrival counters) must be zero between
+# calls; the kernels leave them zero unless a bounded wait ran out or two calls overlapped on the device
+# (see device_status).
 _SCALED_MM_OUT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
-_TC_WORKSPACES: dict[tuple[int, int], Tensor] = {}
+_COUNTER_BYTES = 16384
+_TC_WORKSPACES: dict[tuple[int, int | str], Tensor] = {}
+_TC_LOCK = threading.Lock()
+_TC_MIN_BYTES = 1 << 22
 _TC_MIN_WEIGHT_ELEMS = 1 << 21  # below this a launch is latency-bound and the SIMT kernels do as well
 
 
 def tc_workspace(device: torch.device, nbytes: int) -> Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream() or 0)
-    ws = _TC_WORKSPACES.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
-        _TC_WORKSPACES[key] = ws
-    return ws
+    """The workspace for calls on the current stream of ``device``.
+
+    While a CUDA graph is being captured the stream is the capture's own, so a look-up by stream would allocate
+    (and zero-fill) inside the capture and the fill would be replayed with every step.  Captured calls therefore
+    use one workspace per device that is set aside for graphs: it is allocated, outside any capture, together
+    with the first ordinary workspace of the device or by :func:`reserve_graph_workspace`.  Graphs replayed
+    at the same time on two streams of one device need workspaces of their own (pass them to the C ABI).
+    """
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    capturing = torch.cuda.is_current_stream_capturing()
+    key = (index, "graph") if capturing else (index, _stream() or 0)
+    with _TC_LOCK:
+        ws = _TC_WORKSPACES.get(key)
+        if ws is None or ws.numel() < nbytes:
+            if capturing and ws is not None:
+                raise RuntimeError(
+                    f"the tensor-core workspace set aside for CUDA graphs holds {ws.numel()} bytes but this call "
+                    f"needs {nbytes}: call helion_b200.ops.reserve_graph_workspace(device, nbytes) before capturing"
+                )
+            # (a first use inside a capture allocates in the graph's pool: correct, but the fill is replayed)
+            ws = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
+            _TC_WORKSPACES[key] = ws
+            if not capturing and (index, "graph") not in _TC_WORKSPACES:
+                _TC_WORKSPACES[(index, "graph")] = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
+        return ws
+
+
+def reserve_graph_workspace(device: torch.device, nbytes: int) -> None:
+    """Make the workspace that captured calls on ``device`` use at least ``nbytes`` large (call outside capture)."""
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("reserve_graph_workspace must be called outside stream capture")
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    with _TC_LOCK:
+        ws = _TC_WORKSPACES.get((index, "graph"))
+        if ws is None or ws.numel() < nbytes:
+            _TC_WORKSPACES[(index, "graph")] = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
+
+
+def device_status(reset: bool = False) -> int:
+    """Sticky status of the current device's kernels (0, or ``HB200_ERR_DEVICE_TIMEOUT`` once a bounded
+    device-side wait ran out); synchronises the device.  With ``reset`` a non-zero status is cleared and, because
+    a kernel that gave up can leave tile arrival counters non-zero (every later call on that workspace would then
+    leave tiles unwritten), the counter region of every cached workspace of the device is zeroed again."""
+    status = int(_lib.load().hb200_device_status(1 if reset else 0))
+    if reset and status != 0:
+        index = torch.cuda.current_device()
+        with _TC_LOCK:
+            for (dev, _), ws in _TC_WORKSPACES.items():
+                if dev == index:
+                    ws[:_COUNTER_BYTES].zero_()
+        torch.cuda.synchronize()
+    return status
 
 
 def _tc_eligible(n: int, k: int, batch: int) -> bool:

@@ -197,6 +197,22 @@ int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_
 int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles, int64_t max_tiles,
                           void* stream);
 
+/* Tile list from device-resident per-group row counts (the device split sizes of the reference's grouped
+ * tcgen05 kernels, test/test_cute_grouped_gemm_split_sizes.py:620-745): group g owns rows [P_g, P_g + size_g),
+ * P the raw running sum; a size is clipped to [0, total_rows] in 64 bits, the interval to [0, total_rows), so
+ * oversized, negative and beyond-int32 sizes never reach outside the matrices.  sizes int64 or int32 with an
+ * element stride; groups <= 1024. */
+int hb200_build_split_tiles(const void* split_sizes, int sizes_are_i64, int64_t stride, int64_t groups,
+                            int64_t total_rows, int32_t* row_tiles, int64_t max_tiles, void* stream);
+
+/* Tile list for a worklist [items, 4] of (group, start row, valid rows, rows to store), the metadata
+ * grouped_gemm_deepgemm takes (pretuned_kernels/grouped_gemm_deepgemm/grouped_gemm_deepgemm.py:172-224), built
+ * on the device.  Items are not trusted: negative group or start drops the item, store is clipped to the rows
+ * that exist, valid to store.  max_tiles >= ceil(total_rows / 128) + items suffices for non-overlapping items;
+ * tiles past max_tiles are dropped.  items <= 8192. */
+int hb200_build_worklist_tiles(const int32_t* worklist, int64_t items, int64_t total_rows, int32_t* row_tiles,
+                               int64_t max_tiles, void* stream);
+
 /* silu_mul_fp8 (pretuned_kernels/silu_mul_fp8/silu_mul_fp8.py:29-59): out[t, j] = fp8_e4m3(p * (1 / scale)) with
  * p = input_dtype(input_dtype(silu(x[t, j])) * x[t, d + j]), one static fp32 scale (device pointer), input
  * [tokens, 2 d] bf16 (in_is_fp16 = 0) or fp16 with row pitch in_stride elements, out [tokens, d] contiguous.
@@ -326,6 +342,15 @@ int hb200_nvfp4_gemv_bf16in_tc_builtin_scratch(const void* weight_packed, const 
                                                const void* weight_scale, void* out_bf16, int64_t n, int64_t k,
                                                int64_t batch, float alpha, void* stream);
 
+/* Re-zeroes, on `stream`, the tile arrival counters of the built-in scratch (the part that must be zero when a
+ * call starts).  A call that ended with HB200_ERR_DEVICE_TIMEOUT, or two calls that overlapped on the device,
+ * can leave counters non-zero, and every later call on that device would then leave output tiles unwritten
+ * although hb200_device_status reads OK again: call this (or hb200_device_status(1), which does the same
+ * synchronously when it clears a non-zero status) before going on.  Allocates nothing.  For a caller-owned
+ * workspace the same holds: clear its first hb200_nvfp4_gemv_tc_counter_bytes() bytes. */
+int hb200_nvfp4_gemv_tc_builtin_scratch_reset(void* stream);
+int64_t hb200_nvfp4_gemv_tc_counter_bytes(void);
+
 /* ---- tensor-parallel forms (one process per GPU, outputs in symmetric memory) ----
  *
  * The reference's distributed examples push results to peers from inside the kernel through symmetric
@@ -358,6 +383,17 @@ int hb200_peer_barrier(void* const* flag_ptrs, int64_t world, int64_t rank, void
  * clears it.  Synchronises the device; not for use on the hot path.  (No
  * counterpart in the reference, whose device waits are unbounded.) */
 int hb200_device_status(int reset);
+
+/* Budget, in SM clock cycles, of every bounded device-side wait of the library on the current device (the
+ * mbarrier waits of the tcgen05 pipelines and the flag wait of hb200_peer_barrier); default 4e9, about two
+ * seconds.  Synchronous; do not call while kernels of the library are in flight.  (The reference's waits are
+ * unbounded: helion/runtime/triton/dist_utils.py:175-193.) */
+int hb200_set_wait_budget_cycles(int64_t cycles);
+
+/* Launches one CTA that waits, with the bounded wait every pipeline uses, on an mbarrier nothing arrives on:
+ * the wait runs out after one budget, the kernel returns and hb200_device_status reads
+ * HB200_ERR_DEVICE_TIMEOUT until reset.  Exercises the expiry path without a fault; shorten the budget first. */
+int hb200_selftest_bounded_wait(void* stream);
 
 #ifdef __cplusplus
 }

@@ -398,21 +398,31 @@ def nvfp4_moe(
     x: Tensor, logits: Tensor, top_k: int,
     w_gu_packed: Tensor, w_gu_scale: list[Tensor] | Tensor, w_gu_global: Tensor,
     w_d_packed: Tensor, w_d_scale: list[Tensor] | Tensor, w_d_global: Tensor,
-) -> Tensor:
+    return_pairs: bool = False, routing: tuple[Tensor, Tensor] | None = None,
+):
     """NVFP4 MoE layer (composition; the reference has no NVFP4 MoE): route, then per expert
     quantise the gathered bf16 rows per token to NVFP4, ``h = deq(A) @ deq(W_gu)^T`` in fp32,
     ``y = silu(h[:, :I]) * h[:, I:]`` (gate first, as silu_and_mul_per_block_quant), requantise y per
     token, ``o = deq(y) @ deq(W_d)^T``, and accumulate ``out[t] += weight * o`` in fp32; bf16 result.
+    The per-expert loop is moe_matmul_ogs_reference's (examples/moe_matmul_ogs.py:128-151).
 
     Weights: ``w_gu_packed [E, 2I, H/2]``, ``w_d_packed [E, H, I/2]``; scales are per-expert swizzled
     buffers; ``*_global`` are per-expert fp32 global scales ``[E]``.  The intermediate ``h`` is rounded to
     bf16 before SiLU-mul and ``y`` to bf16 before requantisation, as a bf16 activation pipeline does.
+    Experts no token was routed to are never touched (their entries may be ``None`` in the scale lists).
+
+    ``routing = (weights [T, k], experts [T, k])`` replaces the router (to compare the expert arithmetic
+    alone when two routers disagree on a near-tie).  With ``return_pairs`` the result is
+    ``(out, pairs)`` where ``pairs`` holds, per (token, slot) pair in expert order, the intermediate the
+    second GEMM consumes: ``tok``, ``slot``, ``expert``, ``y`` (bf16 ``[P, I]``), ``codes`` (uint8 nibbles
+    ``[P, I]``), ``scales`` (e4m3 ``[P, I/16]``, logical layout) and ``g`` (fp32 ``[P]``).
     """
     t, hdim = x.shape
-    e_count = w_gu_packed.shape[0]
-    inter = w_gu_packed.shape[1] // 2
-    weights, experts = moe_route(logits, top_k)
+    e_count = len(w_gu_packed)  # a tensor [E, ...] or a list with None for experts that are not needed
+    inter = next(w for w in w_gu_packed if w is not None).shape[0] // 2
+    weights, experts = moe_route(logits, top_k) if routing is None else routing
     out = torch.zeros(t, hdim, dtype=torch.float32)
+    keep: dict[str, list[Tensor]] = {k: [] for k in ("tok", "slot", "expert", "y", "codes", "scales", "g")}
     for e in range(e_count):
         tok, slot = (experts == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
@@ -423,8 +433,43 @@ def nvfp4_moe(
         h = (a @ wgu.t()).to(torch.bfloat16).to(torch.float32)
         y = (torch.nn.functional.silu(h[:, :inter]) * h[:, inter:]).to(torch.bfloat16)
         yp, ysc, yg = nvfp4_quantize(y, per_token=True)
+        if return_pairs:
+            keep["tok"].append(tok)
+            keep["slot"].append(slot)
+            keep["expert"].append(torch.full_like(tok, e))
+            keep["y"].append(y)
+            keep["codes"].append(unpack_codes_k_major(yp))
+            keep["scales"].append(unswizzle_scales(ysc, y.shape[0], inter // 16))
+            keep["g"].append(yg)
         yq = dequant_scaled_k_major(yp, ysc) * yg.reshape(-1, 1)
         wd = dequant_scaled_k_major(w_d_packed[e], w_d_scale[e]) * w_d_global[e]
         o = yq @ wd.t()
         out.index_add_(0, tok, o * weights[tok, slot].reshape(-1, 1))
+    if return_pairs:
+        return out.to(torch.bfloat16), {k: torch.cat(v) for k, v in keep.items()}
+    return out.to(torch.bfloat16)
+
+
+def unpack_codes_k_major(packed: Tensor) -> Tensor:
+    """``[R, K/2]`` packed bytes -> ``[R, K]`` 4-bit codes (uint8), low nibble = even k."""
+    b = _bytes(packed)
+    return torch.stack((b & 0xF, b >> 4), dim=-1).reshape(b.shape[0], -1)
+
+
+def nvfp4_moe_down(
+    codes: Tensor, scales: Tensor, g: Tensor, tok: Tensor, slot: Tensor, expert: Tensor, weights: Tensor,
+    w_d_packed: Tensor, w_d_scale: list[Tensor] | Tensor, w_d_global: Tensor, tokens: int,
+) -> Tensor:
+    """Second half of :func:`nvfp4_moe` from a given quantised intermediate (``codes [P, I]`` nibbles,
+    ``scales [P, I/16]`` e4m3 logical, ``g [P]``): ``o = deq(y) @ deq(W_d)^T``, routing-weighted sum per token
+    in fp32, bf16 result.  Used to show that an output difference comes from the intermediate's codes alone."""
+    p, inter = codes.shape
+    hdim = next(w for w in w_d_packed if w is not None).shape[0]
+    yq = dequant_e2m1(codes) * scales.to(torch.float32).repeat_interleave(16, dim=1) * g.reshape(-1, 1)
+    out = torch.zeros(tokens, hdim, dtype=torch.float32)
+    for e in expert.unique().tolist():
+        sel = (expert == e).nonzero(as_tuple=True)[0]
+        wd = dequant_scaled_k_major(w_d_packed[e], w_d_scale[e]) * w_d_global[e]
+        o = yq[sel] @ wd.t()
+        out.index_add_(0, tok[sel], o * weights[tok[sel], slot[sel]].reshape(-1, 1))
     return out.to(torch.bfloat16)

@@ -36,6 +36,17 @@ def _dense_expert_fn(w1, w2):
     return fn
 
 
+def _torch_router(logits, top_k):
+    """Tensor-code stand-in for the routing kernel (softmax in fp32, then top-k)."""
+    return torch.topk(torch.softmax(logits.to(torch.float32), dim=-1), top_k, dim=-1)
+
+
+def _torch_combine(back, row_of_pair, pair_weight, tokens):
+    """Tensor-code stand-in for the combine kernel: routing-weighted fp32 sum of every token's rows."""
+    rows = back.float()[row_of_pair.long()] * pair_weight.float()[:, None]
+    return rows.reshape(tokens, -1, back.shape[1]).sum(dim=1).to(torch.bfloat16)
+
+
 def _worker(rank: int, world: int, port: int, result_dir: str):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -50,7 +61,7 @@ def _worker(rank: int, world: int, port: int, result_dir: str):
         per_t, per_e = t // world, e // world
         xs, ls = x[rank * per_t : (rank + 1) * per_t], logits[rank * per_t : (rank + 1) * per_t]
         fn = _dense_expert_fn(w1[rank * per_e : (rank + 1) * per_e], w2[rank * per_e : (rank + 1) * per_e])
-        y = D.expert_parallel_moe(xs, ls, k, e, fn)
+        y = D.expert_parallel_moe(xs, ls, k, e, fn, router=_torch_router, combine=_torch_combine)
         torch.save(y, os.path.join(result_dir, f"moe_{rank}.pt"))
 
         # column-parallel gather: rank r contributes columns [r*N/g, (r+1)*N/g)

@@ -99,3 +99,115 @@ def test_n_major_nvfp4_matmuls_golden(golden):
     with pytest.raises(ValueError, match="K must be divisible by 16"):
         hb.nvfp4_w4a16_matmul(torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV),
                               torch.zeros(4, 8, dtype=torch.uint8, device=DEV), sb.to(DEV))
+
+
+def _graph(fn, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = fn()
+    torch.cuda.synchronize()
+    return g, out
+
+
+@pytest.mark.parametrize("split_dtype,split_stride", [(torch.int64, 2), (torch.int32, 1)])
+def test_split_sizes_edges_and_graph_replay(split_dtype, split_stride):
+    """The ragged edge cases and the capture -> mutate -> replay protocol of
+    test/test_cute_grouped_gemm_split_sizes.py:628-745: zero-row and one-row groups, then, by replaying one captured
+    launch after overwriting the device-resident sizes, another partition, an oversized size, negative sizes and
+    (int64) a size beyond int32.  Sizes are clipped, never trusted; rows no group covers keep their contents."""
+    from helion_b200 import grouped as G
+
+    gen = torch.Generator().manual_seed(5)
+    sizes0 = (0, 224, 17, 0, 449, 1, 256, 1101)
+    m, n, k, groups = sum(sizes0), 224, 128, len(sizes0)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(DEV)
+    b = torch.randn(groups, n, k, generator=gen).to(torch.bfloat16).to(DEV)
+    storage = torch.zeros(groups * split_stride, dtype=split_dtype, device=DEV)
+    split = storage[::split_stride]
+    assert split.stride() == (split_stride,)
+    out = torch.full((m, n), -7.0, dtype=torch.bfloat16, device=DEV)
+
+    def set_sizes(sizes):
+        split.copy_(torch.tensor(sizes, dtype=split_dtype, device=DEV))
+
+    def expected(sizes):
+        want = torch.full((m, n), -7.0)
+        prefix = 0
+        for g, raw in enumerate(sizes):
+            length = min(max(raw, 0), m)
+            lo, hi = min(max(prefix, 0), m), min(max(prefix + length, 0), m)
+            if hi > lo:
+                want[lo:hi] = a[lo:hi].float().cpu() @ b[g].float().cpu().t()
+            prefix += raw
+        return want
+
+    set_sizes(sizes0)
+    graph, captured = _graph(lambda: G.grouped_gemm_split_sizes(a, b, split, out=out))
+    assert captured is out
+    cases = [sizes0, (113, 0, 224, 200, 0, 1, 300, 1210), (m + 1, 0, 0, 0, 0, 0, 0, 0), (-100, 50, m + 50, 0, 0, 0, 0, 0)]
+    if split_dtype is torch.int64:
+        huge = torch.iinfo(torch.int32).max + 17
+        cases.append((huge, m - huge, 0, 0, 0, 0, 0, 0))
+    for sizes in cases:
+        a.normal_(generator=None)
+        set_sizes(sizes)
+        out.fill_(-7.0)
+        graph.replay()
+        assert status_ok()
+        want = expected(sizes)
+        got = out.float().cpu()
+        untouched = want == -7.0
+        assert torch.equal(got[untouched], want[untouched]), sizes  # nothing outside the groups' visible rows
+        assert rel_err(torch.where(untouched, torch.zeros_like(got), got),
+                       torch.where(untouched, torch.zeros_like(want), want)) <= 1e-2, sizes
+        if sizes[0] == -100:
+            # the reference's reading of negative sizes: the third group starts at -50 and writes rows [0, m - 50)
+            assert bool((out[m - 50 :].float() == -7.0).all()) and bool((out[: m - 50].float() != -7.0).any())
+
+
+def test_worklist_items_are_clipped_not_trusted():
+    """Worklist entries come from device memory: negative starts or groups drop the item, store_m is clipped to the
+    rows that exist, valid_m to store_m; unsorted items are fine."""
+    gen = torch.Generator().manual_seed(9)
+    m_total, n, k = 640, 256, 64
+    a = torch.randn(m_total, k, generator=gen).to(torch.float16)
+    b = torch.randn(3, n, k, generator=gen).to(torch.float16)
+    wl = torch.tensor([[2, 384, 100, 128], [0, 0, 128, 128], [1, 512, 300, 9999], [1, -128, 5, 128], [-1, 128, 7, 128],
+                       [0, 128, 200, 100], [2, 700, 1, 1]], dtype=torch.int32)
+    y = hb.grouped_gemm_deepgemm(a.to(DEV), b.to(DEV), wl.to(DEV))
+    assert status_ok()
+    want = torch.zeros(m_total, n)
+    af, bf = a.float(), b.float()
+    want[384:484] = af[384:484] @ bf[2].t()          # rows 484..511 of the item are stored as zero
+    want[0:128] = af[0:128] @ bf[0].t()
+    want[512:640] = af[512:640] @ bf[1].t()          # store and valid clipped to the 128 rows that exist
+    want[128:228] = af[128:228] @ bf[0].t()          # valid (200) clipped to store (100)
+    assert rel_err(y, want) <= 1e-2
+    assert float(y[228:384].float().abs().max()) == 0.0 and float(y[484:512].float().abs().max()) == 0.0
+
+
+def test_grouped_gemm_graph_replay_after_mutating_inputs():
+    """Capture -> mutate inputs and metadata -> replay (test/test_cute_deepgemm_selected.py:391-405)."""
+    gen = torch.Generator().manual_seed(12)
+    m_total, n, k = 512, 384, 128
+    a = torch.randn(m_total, k, generator=gen).to(torch.bfloat16).to(DEV)
+    b = torch.randn(4, n, k, generator=gen).to(torch.bfloat16).to(DEV)
+    wl = torch.tensor([[0, 0, 128, 128], [1, 128, 60, 128], [2, 256, 128, 128], [3, 384, 1, 128]], dtype=torch.int32, device=DEV)
+    graph, y = _graph(lambda: hb.grouped_gemm_deepgemm(a, b, wl))
+    a.normal_()
+    b.normal_()
+    wl.copy_(torch.tensor([[3, 0, 100, 128], [3, 128, 128, 128], [0, 256, 0, 128], [1, 384, 128, 128]], dtype=torch.int32))
+    graph.replay()
+    assert status_ok()
+    assert rel_err(y, O.grouped_gemm_worklist(a.cpu(), b.cpu(), wl.cpu())) <= 1e-2
+    offs = torch.tensor([0, 100, 100, 357, 512], dtype=torch.int32, device=DEV)
+    bj = torch.randn(k, n, generator=gen).to(torch.bfloat16).to(DEV)
+    graph2, yj = _graph(lambda: hb.grouped_gemm_jagged(a, bj, offs))
+    a.normal_()
+    offs.copy_(torch.tensor([0, 0, 300, 301, 512], dtype=torch.int32))
+    graph2.replay()
+    assert status_ok()
+    assert rel_err(yj, O.grouped_gemm_jagged(a.cpu(), bj.cpu(), offs.cpu())) <= 1e-2

@@ -8,6 +8,7 @@ import torch
 import helion_b200 as hb
 from helion_b200 import _lib
 from helion_b200 import moe as M
+from oracle import checks as C
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -107,19 +108,25 @@ def test_moe_layer_against_oracle(t, h, inter, e, k, interleaved):
     gp, gsc, gg, gu_bundle = oracle_weights(w_gu)
     dp, dsc, dg, d_bundle = oracle_weights(w_d)
     ref = O.nvfp4_moe(x, logits, k, gp, gsc, gg, dp, dsc, dg)
-    if interleaved:  # SiLU-mul inside the first GEMM's epilogue
-        gu_bundle = M.interleave_gate_up(gu_bundle)
-    y = M.nvfp4_moe(x.to(DEV), logits.to(DEV), k, gu_bundle, d_bundle)
+    got = {}
+    y = M.nvfp4_moe(x.to(DEV), logits.to(DEV), k, M.interleave_gate_up(gu_bundle) if interleaved else gu_bundle,
+                    d_bundle, intermediates=got)
     torch.cuda.synchronize()
     assert _lib.load().hb200_device_status(1) == 0
     assert y.shape == (t, h) and y.dtype is torch.bfloat16
-    # Two quantisation steps sit between input and output: a last-place difference in exp() or in the fp32
-    # summation order can flip one bf16 rounding of the intermediate and with it one 4-bit code, which moves a
-    # single output by about one percent.  Bound the worst element at 2e-2 and the overall (rms) error at 5e-3,
-    # about three times what the bf16 roundings of the output and of the expert rows alone contribute.
-    assert rel_err(y, ref) <= 2e-2
-    yc, rc = y.float().cpu(), ref.float()
-    assert float((yc - rc).pow(2).mean().sqrt() / rc.pow(2).mean().sqrt()) <= 5e-3
+    # Bound: 1e-2 per element.  Two quantisation steps sit between input and output: a last-place difference of
+    # the first GEMM's fp32 sum can flip one bf16 rounding of the intermediate and with it one 4-bit code by one
+    # step, which moves single outputs of that token by about a percent.  Such an element is accepted only when
+    # it is explained: its token's intermediate differs from the oracle's (by one step, never more) and the
+    # oracle's second half fed with the CUDA path's own intermediate reproduces the CUDA output within 1e-2.
+    rep = C.moe_sample_report(x, logits, k, gu_bundle, d_bundle, y, got, torch.arange(t))
+    assert rep["routing_same"]
+    assert rep["max_rel_err"] == pytest.approx(rel_err(y, ref))
+    assert rep["max_rel_err_given_cuda_intermediate"] <= 1e-2
+    assert rep["intermediate_codes_differing_by_more_than_one_step"] == 0
+    assert rep["intermediate_scales_differing_by_more_than_one_step"] == 0
+    assert rep["elements_over_1e-2_in_tokens_without_intermediate_difference"] == 0
+    assert rep["max_rel_err"] <= 2e-2 and rep["rms_rel_err"] <= 5e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.int64, torch.int32])

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import helion_b200 as hb
+from oracle import checks as C
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -133,18 +134,9 @@ def check_rms(x, w, eps, ub=None, res=None):
     qo, so, reso = O.rms_norm_dynamic_per_token_quant(x, w, eps, ub, res)
     if res is not None:
         assert count_diff(res_d, reso) == 0
-    row_bad = (bits(q) != bits(qo)).any(dim=1) | (bits(s) != bits(so)).reshape(-1)
-    unexplained = row_bad.clone()
-    for nudge in (-1, 1, -2, 2):
-        if not unexplained.any():
-            break
-        qn, sn, _ = O.rms_norm_dynamic_per_token_quant(
-            x, w, eps, ub, res, rms_ulp_nudge=torch.full((x.shape[0],), nudge, dtype=torch.int32)
-        )
-        ok = ~((bits(q) != bits(qn)).any(dim=1) | (bits(s) != bits(sn)).reshape(-1))
-        unexplained &= ~ok
-    assert not unexplained.any(), f"{int(unexplained.sum())} rows differ beyond a 2-ulp change of rms"
-    return int(row_bad.sum()), int((bits(q) != bits(qo)).sum())
+    rep = C.rms_quant_report(x, w, eps, q, s, ub, res)
+    assert rep["rows_not_explained_by_2ulp_of_rms"] == 0, rep
+    return rep["rows_differing"], rep["codes_differing"]
 
 
 def test_rms_golden(golden):
@@ -336,16 +328,25 @@ def test_silu_mul_fp8_shapes_and_errors():
 
 
 def test_against_outputs_of_the_reference_kernels(golden):
-    """CUDA kernels against what the reference's own kernels wrote (reference CPU interpreter, tests/golden)."""
+    """CUDA kernels against what the reference's own kernels wrote (reference CPU interpreter, tests/golden), with
+    exact mismatch counts.  SiLU-mul: the CPU's exp() differs from the GPU's in the last place, so block scales may
+    move by a few ulp and single codes with them; what explains a mismatch is that the kernel equals, bit for bit,
+    the reference function evaluated by torch on this GPU (the reference's own correctness protocol,
+    pretuned_kernels/silu_and_mul_per_block_quant/silu_and_mul_per_block_quant.py:197-216).  RMSNorm: a row differs
+    only where its fp32 rms moved by at most two ulp (summation order)."""
     g = golden("reference_kernels.npz")
     x = g.bf16("k_silu_x").to(DEV)
     for gs in (64, 128):
         q = torch.empty(12, 256, dtype=torch.float8_e4m3fn, device=DEV)
         s = torch.empty(12, 256 // gs, device=DEV)
         hb.silu_and_mul_per_block_quant(q, x, s, gs)
-        # exp() differs from the CPU's in the last place: scales within a few ulp, nearly all codes identical
+        qd, sd = O.silu_and_mul_per_block_quant(x, gs)  # the same function, evaluated on the device
+        assert count_diff(q, qd) == 0 and count_diff(s, sd) == 0
+        codes_off = int((q.cpu().view(torch.uint8) != g.raw(f"k_silu_q_{gs}")).sum())
+        scales_off = int((bits(s) != bits(g.raw(f"k_silu_s_{gs}"))).sum())
+        print(f"silu gs={gs}: {codes_off} of {q.numel()} codes and {scales_off} of {s.numel()} scales differ from the CPU run")
         torch.testing.assert_close(s.cpu(), g.raw(f"k_silu_s_{gs}"), rtol=1e-6, atol=0)
-        assert float((q.cpu().view(torch.uint8) == g.raw(f"k_silu_q_{gs}")).float().mean()) >= 0.995
+        assert codes_off <= 16  # of 3072
     xr = g.bf16("k_rms_x").to(DEV)
     q = torch.empty(12, 384, dtype=torch.float8_e4m3fn, device=DEV)
     s = torch.empty(12, 1, device=DEV)
@@ -353,5 +354,9 @@ def test_against_outputs_of_the_reference_kernels(golden):
     assert torch.equal(q.cpu().view(torch.uint8), g.raw("k_dyn_q")) and torch.equal(s.cpu(), g.raw("k_dyn_s"))
     w = g.bf16("k_rms_w").to(DEV)
     hb.rms_norm_dynamic_per_token_quant(q, xr, w, s, 1e-6)
-    torch.testing.assert_close(s.cpu(), g.raw("k_rms_s"), rtol=1e-6, atol=0)
-    assert float((q.cpu().view(torch.uint8) == g.raw("k_rms_q")).float().mean()) >= 0.995
+    # the oracle reproduces the reference kernel's output bit for bit, so the row-wise explanation applies to it
+    qo, so, _ = O.rms_norm_dynamic_per_token_quant(xr.cpu(), w.cpu(), 1e-6)
+    assert torch.equal(qo.view(torch.uint8), g.raw("k_rms_q")) and torch.equal(so, g.raw("k_rms_s"))
+    rep = C.rms_quant_report(xr, w, 1e-6, q, s)
+    print("rms against the reference kernel's output:", rep)
+    assert rep["rows_not_explained_by_2ulp_of_rms"] == 0

@@ -145,6 +145,52 @@ def test_custom_ops_registered_with_fake_impls():
         assert c.shape == (2, 128) and sc.numel() == 128 * 16 and g.shape == (2,)
 
 
+def test_grouped_and_moe_ops_registered_with_fake_impls():
+    """Every grouped / MoE entry point is a ``torch.library`` custom op with a fake implementation, as
+    test/test_custom_op.py:23-33 does for a kernel: shapes and dtypes trace without a device."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from helion_b200 import moe as M
+
+    for name in ("moe_matmul_ogs", "grouped_gemm_jagged", "grouped_gemm_deepgemm", "grouped_matmul_f16",
+                 "grouped_matmul_f16_out", "nvfp4_moe", "moe_route_top_k", "moe_build_schedule"):
+        assert hasattr(torch.ops.helion_b200, name), name
+    with FakeTensorMode():
+        cuda = dict(device="cuda")
+        a = torch.empty(300, 64, dtype=torch.bfloat16, **cuda)
+        y = hb.grouped_gemm_jagged(a, torch.empty(64, 96, dtype=torch.bfloat16, **cuda), torch.empty(4, dtype=torch.int32, **cuda))
+        assert y.shape == (300, 96) and y.dtype is torch.bfloat16
+        y = hb.grouped_gemm_deepgemm(a, torch.empty(3, 96, 64, dtype=torch.bfloat16, **cuda), torch.empty(5, 4, dtype=torch.int32, **cuda))
+        assert y.shape == (300, 96)
+        y = hb.moe_matmul_ogs(a.half(), torch.empty(4, 64, 96, dtype=torch.float16, **cuda), torch.empty(4, dtype=torch.int32, **cuda),
+                              torch.empty(5, dtype=torch.int32, **cuda), torch.empty(300, dtype=torch.int32, **cuda), 300)
+        assert y.shape == (300, 96) and y.dtype is torch.float16
+        x = torch.empty(64, 256, dtype=torch.bfloat16, **cuda)
+        logits = torch.empty(64, 8, **cuda)
+        w, e = M.route_top_k(logits, 2)
+        assert w.shape == (64, 2) and w.dtype is torch.float32 and e.dtype is torch.int64
+        sched = M.build_schedule(e, 8)
+        assert sched.tile_info.shape == (sched.max_tiles, 2) and sched.max_tiles == 1 + 8 and sched.row_of_pair.shape == (128,)
+        gu = M.GroupedNvfp4Weight(torch.empty(8, 256, 128, dtype=torch.uint8, **cuda),
+                                  torch.empty(8, 256 * 16, dtype=torch.float8_e4m3fn, **cuda), torch.empty(8, **cuda))
+        dn = M.GroupedNvfp4Weight(torch.empty(8, 256, 64, dtype=torch.uint8, **cuda),
+                                  torch.empty(8, 256 * 8, dtype=torch.float8_e4m3fn, **cuda), torch.empty(8, **cuda))
+        y = M.nvfp4_moe(x, logits, 2, gu, dn)
+        assert y.shape == (64, 256) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
+
+
+def test_product_modules_have_no_cpu_path():
+    """CPU tensors are refused by the routing and combine entry points (the multi-rank host-logic tests inject
+    their own stand-ins instead)."""
+    from helion_b200 import dist as D
+    from helion_b200 import moe as M
+
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        M.route_top_k(torch.zeros(4, 8), 2)
+    with pytest.raises(ValueError, match="CUDA"):
+        D.combine_rows(torch.zeros(8, 16, dtype=torch.bfloat16), torch.arange(8, dtype=torch.int32), torch.ones(8), 4)
+
+
 def test_interleave_gate_up_moves_whole_128_row_tiles():
     """Host-side weight preparation for the SiLU-mul epilogue: codes and scale tiles move together."""
     from helion_b200 import moe as M
