@@ -170,7 +170,8 @@ def nvfp4_quantize_host(x: Tensor, global_scale: Tensor | None = None, per_token
     g = global_scale.to(torch.float32).reshape(-1, 1, 1) if per_token else global_scale.to(torch.float32)
     blocks = xf.reshape(rows, k // 16, 16)
     amax = blocks.abs().amax(dim=-1, keepdim=True)
-    sf = (amax / FP4_MAX) / g
+    # (tensor divisors: dividing a CUDA tensor by a Python scalar multiplies by the rounded reciprocal)
+    sf = (amax / torch.tensor(FP4_MAX, dtype=torch.float32, device=xf.device)) / g
     sf = torch.where(g > 0, sf, torch.zeros_like(sf))
     s8 = sf.to(torch.float8_e4m3fn)
     denom = s8.to(torch.float32) * g
