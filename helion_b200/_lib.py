@@ -75,9 +75,16 @@ SIGNATURES: dict[str, list] = {
     "hb200_selftest_bounded_wait": [_P],
     "hb200_build_worklist_tiles": [_P, _I64, _I64, _P, _I64, _P],
     "hb200_build_split_tiles": [_P, c_int, _I64, _I64, _I64, _P, _I64, _P],
+    "hb200_ep_buffer_bytes": [_I64, _I64, _I64, _I64, _I64],
+    "hb200_ep_slots": [_I64, _I64, _I64, _I64, _I64],
+    "hb200_ep_dispatch": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    "hb200_ep_collect": [_P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    "hb200_ep_gather": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    "hb200_ep_return": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    "hb200_ep_combine": [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
 }
 _RESTYPES = {"hb200_error_string": c_char_p, "hb200_nvfp4_gemv_tc_workspace_bytes": c_int64,
-             "hb200_nvfp4_gemv_tc_counter_bytes": c_int64,
+             "hb200_nvfp4_gemv_tc_counter_bytes": c_int64, "hb200_ep_buffer_bytes": c_int64, "hb200_ep_slots": c_int64,
              "hb200_fp8_scaled_mm_workspace_bytes": c_int64}
 
 _lock = threading.Lock()

@@ -477,10 +477,10 @@ extern "C" int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_
   pair::PeerOut peers;
   peers.n_total = n_total;
   peers.col0 = col0;
-  for (int i = 0; i < world; ++i) {
+  for (int i = 0; i < world; ++i)
     if (!out_ptrs[i] || reinterpret_cast<uintptr_t>(out_ptrs[i]) % 16) return HB200_ERR_INVALID_ARGUMENT;
-    if (i != rank) peers.ptr[peers.n_peers++] = out_ptrs[i];
-  }
+  // peers in ring order starting at the next rank: at any moment every rank then pushes to a different destination
+  for (int i = 1; i < world; ++i) peers.ptr[peers.n_peers++] = out_ptrs[(rank + i) % world];
   if (m == 0 || n == 0) return HB200_OK;
   if (k == 0 || (k % 32) != 0 || (n_total % 8) != 0) return HB200_ERR_UNSUPPORTED;
   if (m > 0x7fffff00 || n_total > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;

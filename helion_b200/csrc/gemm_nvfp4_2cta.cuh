@@ -67,7 +67,7 @@ struct PairArgs {
   // Tensor-parallel form: every tile row (512 contiguous bytes) is written to the same place of every rank's
   // buffer with bulk copies from shared memory; stores only, nothing is ever loaded from peer memory.
   int n_dst;
-  void* dst[8];  // the [m, ldc] buffers, this rank's first; the tile columns start at column col0 of them
+  void* dst[8];  // the [m, ldc] buffers, peers in ring order from the next rank, this rank's own last; the tile columns start at column col0
   int col0;
   // Grouped form (tile_info != nullptr): the rows of A are laid out group after group, every group padded to a
   // multiple of 256 rows; tile_info[t] = (group, valid rows) of 128-row tile t, so entries 2j and 2j+1 describe
@@ -425,8 +425,9 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
              nullptr, nullptr, nullptr};
   if (tp) {
     g.col0 = int(peers.col0);
-    g.dst[g.n_dst++] = out;
+    // the copies over NVLink are issued first, the local one last
     for (int i = 0; i < peers.n_peers; ++i) g.dst[g.n_dst++] = peers.ptr[i];
+    g.dst[g.n_dst++] = out;
   }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -70,6 +70,10 @@ moe_row_map_kernel(const int32_t* __restrict__ counts, int experts, const int32_
   __syncthreads();
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= pairs) return;
+  if (p >= off[experts]) {  // the sorted list is shorter than `pairs` when entries were dropped (expert id out of range)
+    row_of_sorted[p] = -1;
+    return;
+  }
   int lo = 0, hi = experts;  // last e with off[e] <= p (experts with zero tokens share an offset)
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;

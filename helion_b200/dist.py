@@ -336,3 +336,186 @@ def make_nvfp4_expert_fn(w_gate_up, w_down) -> ExpertFn:
         return o[sched.row_of_pair.long()]
 
     return fn
+
+
+# ------------------------------------------------------------------ expert parallelism over peer memory
+class ExpertParallel:
+    """NVFP4 MoE layer over expert-parallel ranks whose exchange is done by this library's own kernels over peer
+    memory (``csrc/moe_ep.cu``): tokens travel as NVFP4 rows (codes, block scales, one global scale per token: about
+    2.3 KB per (token, expert) pair at hidden 4096 instead of 8 KB in bf16), every expert rank returns ONE
+    routing-weighted, pre-reduced bf16 row per (token, rank), receive areas have a capacity that follows from the
+    shapes, and nothing is read on the host: a step is a fixed sequence of launches and two barrier kernels.
+
+    ``tokens`` is the number of tokens per rank (fixed at construction: the symmetric buffer is sized from it).
+    Rank r owns experts ``[r E / W, (r + 1) E / W)``; weights are :class:`moe.GroupedNvfp4Weight` bundles of the local
+    experts, the gate/up bundle interleaved with :func:`moe.interleave_gate_up`.
+
+    Numerics: every (token, slot) pair is computed exactly as on one GPU; the sum over a token's slots is taken per
+    expert rank first (fp32, slot order, rounded to bf16) and over ranks second, so results agree with the one-GPU
+    layer to bf16 rounding of the partial sums, not bit for bit.
+    """
+
+    def __init__(self, device: torch.device, tokens: int, hidden: int, top_k: int, num_experts: int, group=None,
+                 *, _emulate: tuple[int, int, list[Tensor]] | None = None):
+        import ctypes
+
+        from . import _lib
+
+        self.device = device
+        self.tokens, self.hidden, self.top_k, self.experts = tokens, hidden, top_k, num_experts
+        if _emulate is not None:
+            # several "ranks" on one GPU for tests: buffers are ordinary tensors, phases are run rank after rank
+            # by the caller and no barrier kernel is launched (nothing may wait for a launch that has not started)
+            self.world, self.rank, buffers = _emulate
+            self._tp = None
+        else:
+            self._tp = TensorParallel(device, group)
+            self.world, self.rank = self._tp.world, self._tp.rank
+        lib = _lib.load()
+        nbytes = int(lib.hb200_ep_buffer_bytes(self.world, tokens, hidden, top_k, num_experts))
+        if nbytes < 0:
+            _lib.check(nbytes, "hb200_ep_buffer_bytes")
+        self.slots = int(lib.hb200_ep_slots(self.world, tokens, hidden, top_k, num_experts))
+        self.e_local = num_experts // self.world
+        if _emulate is not None:
+            if any(b.numel() < nbytes for b in buffers):
+                raise ValueError(f"emulated exchange buffers must hold {nbytes} bytes")
+            self._buf = buffers[self.rank]
+            self.bases = (ctypes.c_void_p * self.world)(*[b.data_ptr() for b in buffers])
+        else:
+            self._buf, self.bases = self._tp._symmetric(nbytes, torch.uint8)
+            self._tp._sync_all()
+        self._state = None
+
+    @staticmethod
+    def buffer_bytes(world: int, tokens: int, hidden: int, top_k: int, num_experts: int) -> int:
+        from . import _lib
+
+        return int(_lib.load().hb200_ep_buffer_bytes(world, tokens, hidden, top_k, num_experts))
+
+    def _shape_args(self):
+        return (self.world, self.rank, self.tokens, self.hidden, self.top_k, self.experts)
+
+    def _barrier(self):
+        if self._tp is not None:
+            self._tp.barrier()
+
+    # -- phases (a rank's phases run in this order; ranks meet at the barriers)
+    def dispatch(self, x: Tensor, router_logits: Tensor) -> None:
+        """Route, quantise every token once, sort the (token, slot) pairs by expert and push them to their ranks."""
+        from . import _lib
+        from . import moe as M
+        from . import ops
+
+        if x.shape != (self.tokens, self.hidden) or x.dtype is not torch.bfloat16 or not x.is_contiguous():
+            raise ValueError(f"x must be a contiguous bfloat16 [{self.tokens}, {self.hidden}] tensor")
+        weights, experts = M.route_top_k(router_logits, self.top_k)
+        codes_t, scales_t, g_t = ops.nvfp4_quantize(x)
+        flat = experts.reshape(-1)
+        pairs = flat.numel()
+        dev = x.device
+        sorted_pairs = torch.empty(pairs, dtype=torch.int32, device=dev)
+        counts = torch.empty(self.experts, dtype=torch.int32, device=dev)
+        scratch = torch.empty(max(1, -(-pairs // 1024)) * self.experts, dtype=torch.int32, device=dev)
+        route_local = torch.empty(pairs, dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            _lib.call("hb200_moe_sort_pairs", flat.data_ptr(), 1, pairs, self.experts, sorted_pairs.data_ptr(),
+                      counts.data_ptr(), scratch.data_ptr(), stream)
+            _lib.call("hb200_ep_dispatch", codes_t.data_ptr(), scales_t.data_ptr(), g_t.data_ptr(),
+                      weights.data_ptr(), flat.data_ptr(), sorted_pairs.data_ptr(), counts.data_ptr(),
+                      route_local.data_ptr(), self.bases, *self._shape_args(), stream)
+        self._state = route_local
+
+    def run_experts(self, w_gate_up, w_down) -> None:
+        """Sort what arrived by expert, run the two grouped GEMMs (SiLU-mul between them) and push one pre-reduced
+        row per (source, token) back."""
+        from . import _lib
+        from . import moe as M
+        from .layouts import ceil_div
+        from .layouts import swizzled_scale_numel
+
+        if w_gate_up.experts != self.e_local or w_down.experts != self.e_local:
+            raise ValueError(f"this rank owns {self.e_local} experts")
+        if w_gate_up.k != self.hidden or w_down.n != self.hidden or w_down.k != w_gate_up.n // 2:
+            raise ValueError("expert weight shapes do not match the activations")
+        dev = self.device
+        slots, h, inter = self.slots, self.hidden, w_down.k
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        i32 = dict(dtype=torch.int32, device=dev)
+        expert_of_slot = torch.empty(slots, **i32)
+        sorted_slots = torch.empty(slots, **i32)
+        counts = torch.empty(self.e_local, **i32)
+        scratch = torch.empty(max(1, ceil_div(slots, 1024)) * self.e_local, **i32)
+        max_tiles = ceil_div(slots, 128) + self.e_local
+        rows = max_tiles * 128
+        tile_info = torch.empty(max_tiles, 2, **i32)
+        padded_offsets = torch.empty(self.e_local + 1, **i32)
+        row_of_sorted = torch.empty(slots, **i32)
+        row_of_slot = torch.full((slots,), -1, **i32)
+        a1 = torch.empty(rows, h // 2, dtype=torch.uint8, device=dev)
+        sf1 = torch.empty(swizzled_scale_numel(rows, h // 16), dtype=torch.uint8, device=dev)
+        g1 = torch.zeros(rows, dtype=torch.float32, device=dev)
+        w_row = torch.zeros(rows, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.call("hb200_ep_collect", self._buf.data_ptr(), expert_of_slot.data_ptr(), *self._shape_args(), stream)
+            _lib.call("hb200_moe_sort_pairs", expert_of_slot.data_ptr(), 0, slots, self.e_local, sorted_slots.data_ptr(),
+                      counts.data_ptr(), scratch.data_ptr(), stream)
+            _lib.call("hb200_moe_build_schedule", counts.data_ptr(), self.e_local, sorted_slots.data_ptr(), slots,
+                      padded_offsets.data_ptr(), tile_info.data_ptr(), max_tiles, row_of_sorted.data_ptr(),
+                      row_of_slot.data_ptr(), stream)
+            _lib.call("hb200_ep_gather", self._buf.data_ptr(), sorted_slots.data_ptr(), row_of_sorted.data_ptr(),
+                      a1.data_ptr(), sf1.data_ptr(), g1.data_ptr(), w_row.data_ptr(), *self._shape_args(), stream)
+        sched = M.MoeSchedule(max_tiles, tile_info, padded_offsets, sorted_slots, row_of_sorted, row_of_slot, 128)
+        if w_gate_up.gate_up_interleaved:
+            y, row_amax = M.grouped_matmul_silu(a1, sf1, w_gate_up, sched, g1)
+            a2, sf2, g2 = M._quantize_rows_amax(y, row_amax, inter, sched, None)
+        else:
+            h1 = M.grouped_matmul(a1, sf1, w_gate_up, sched, g1)
+            a2, sf2, g2 = M._quantize_rows(h1, inter, sched, 1, None, True, gather=False)
+        o = M.grouped_matmul(a2, sf2, w_down, sched, g2)
+        with torch.cuda.device(dev):
+            _lib.call("hb200_ep_return", o.data_ptr(), o.stride(0), row_of_slot.data_ptr(), w_row.data_ptr(), self.bases,
+                      *self._shape_args(), stream)
+
+    def combine(self) -> Tensor:
+        """Add, per token, the rows the expert ranks returned (rank order, fp32); bf16 ``[tokens, hidden]``."""
+        from . import _lib
+
+        if self._state is None:
+            raise RuntimeError("combine() follows dispatch() and run_experts()")
+        out = torch.empty(self.tokens, self.hidden, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.call("hb200_ep_combine", self._buf.data_ptr(), self._state.data_ptr(), out.data_ptr(),
+                      *self._shape_args(), torch.cuda.current_stream(self.device).cuda_stream)
+        self._state = None
+        return out
+
+    def moe(self, x: Tensor, router_logits: Tensor, w_gate_up, w_down) -> Tensor:
+        """One MoE layer step: ``x [tokens, hidden]`` bf16 and ``router_logits [tokens, E]`` of this rank's tokens."""
+        self.dispatch(x, router_logits)
+        self._barrier()  # every rank's rows, counts and tables have arrived
+        self.run_experts(w_gate_up, w_down)
+        self._barrier()  # every rank's returned rows have arrived
+        return self.combine()
+
+    def phase_times(self, x: Tensor, router_logits: Tensor, w_gate_up, w_down) -> dict:
+        """Microseconds of every phase of one step on this rank (CUDA events, a device synchronisation and a host
+        barrier between phases, so the figures do not add up to the pipelined step time)."""
+        def timed(fn):
+            if self._tp is not None:
+                self._tp._sync_all()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            r = fn()
+            b.record()
+            torch.cuda.synchronize(self.device)
+            return a.elapsed_time(b) * 1e3, r
+
+        out = {}
+        out["dispatch"], _ = timed(lambda: self.dispatch(x, router_logits))
+        out["barrier_1"], _ = timed(self._barrier)
+        out["experts_and_return"], _ = timed(lambda: self.run_experts(w_gate_up, w_down))
+        out["barrier_2"], _ = timed(self._barrier)
+        out["combine"], _ = timed(self.combine)
+        return out

@@ -309,8 +309,8 @@ def nvfp4_moe(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: GroupedNv
 
     ``intermediates`` (a dict, filled in place) receives what the second expert GEMM consumes, for parity
     checks: the routing (``weights``, ``experts``), the schedule (``sched``) and, over the padded row layout,
-    the re-quantised SiLU-mul output (``a2`` packed codes, ``sf2`` swizzled scales, ``g2`` row factors with the
-    routing weight folded in) and ``y`` (bf16 SiLU-mul output) when the fused epilogue produced it.
+    the re-quantised SiLU-mul output (``a2`` packed codes, ``sf2`` swizzled scales, ``g2`` per-row global scales)
+    and ``y`` (bf16 SiLU-mul output) when the fused epilogue produced it.
     """
     _require_cuda(x, router_logits)
     if x.dtype is not torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
@@ -333,22 +333,21 @@ def _nvfp4_moe_impl(x: Tensor, router_logits: Tensor, top_k: int, w_gate_up: Gro
     inter = w_gate_up.n // 2
     weights, experts = route_top_k(router_logits, top_k)
     sched = build_schedule(experts, e)
-    # sorted position p holds pair sorted_pairs[p]; its routing weight rides on the second GEMM's row scale
-    w_sorted = weights.reshape(-1)[sched.sorted_pairs.long()].contiguous()
     a1, sf1, g1 = _quantize_and_gather(x, sched, top_k)
     y = None
     if w_gate_up.gate_up_interleaved:
         # SiLU-mul in the GEMM's epilogue: the [rows, 2I] intermediate never reaches memory
         y, row_amax = grouped_matmul_silu(a1, sf1, w_gate_up, sched, g1)
-        a2, sf2, g2 = _quantize_rows_amax(y, row_amax, inter, sched, w_sorted)
+        a2, sf2, g2 = _quantize_rows_amax(y, row_amax, inter, sched, None)
     else:
         h1 = grouped_matmul(a1, sf1, w_gate_up, sched, g1)
-        a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, w_sorted, True, gather=False)
+        a2, sf2, g2 = _quantize_rows(h1, inter, sched, 1, None, True, gather=False)
+    # every expert's output rows in bf16, as moe_matmul_ogs returns them; the routing weights enter in the combine
     o = grouped_matmul(a2, sf2, w_down, sched, g2)
     out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(), None,
-                  out.data_ptr(), t, top_k, h, _stream())
+        _lib.call("hb200_moe_combine", o.data_ptr(), o.stride(0), sched.row_of_pair.data_ptr(),
+                  weights.reshape(-1).data_ptr(), out.data_ptr(), t, top_k, h, _stream())
     if intermediates is not None:
         intermediates.update(weights=weights, experts=experts, sched=sched, a2=a2, sf2=sf2, g2=g2, y=y)
     return out

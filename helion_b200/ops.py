@@ -77,6 +77,7 @@ def _check_numel(name: str, t: Tensor, expected: int) -> None:
 _SCALED_MM_OUT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 _COUNTER_BYTES = 16384
 _TC_WORKSPACES: dict[tuple[int, int | str], Tensor] = {}
+_TC_RETIRED: list[Tensor] = []  # outgrown graph workspaces, kept alive for the graphs that captured them
 _TC_LOCK = threading.Lock()
 _TC_MIN_BYTES = 1 << 22
 _TC_MIN_WEIGHT_ELEMS = 1 << 21  # below this a launch is latency-bound and the SIMT kernels do as well
@@ -100,14 +101,25 @@ def tc_workspace(device: torch.device, nbytes: int) -> Tensor:
             if capturing and ws is not None:
                 raise RuntimeError(
                     f"the tensor-core workspace set aside for CUDA graphs holds {ws.numel()} bytes but this call "
-                    f"needs {nbytes}: call helion_b200.ops.reserve_graph_workspace(device, nbytes) before capturing"
+                    f"needs {nbytes}: run the call once outside the capture (warm-up) or call "
+                    "helion_b200.ops.reserve_graph_workspace(device, nbytes) before capturing"
                 )
             # (a first use inside a capture allocates in the graph's pool: correct, but the fill is replayed)
             ws = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
             _TC_WORKSPACES[key] = ws
-            if not capturing and (index, "graph") not in _TC_WORKSPACES:
-                _TC_WORKSPACES[(index, "graph")] = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
+        if not capturing:
+            _grow_graph_workspace(index, device, nbytes)  # what ran eagerly (a warm-up) can be captured next
         return ws
+
+
+def _grow_graph_workspace(index: int, device: torch.device, nbytes: int) -> None:
+    """(lock held, not capturing)  Graphs captured earlier keep the address of the workspace they were captured
+    with, so an outgrown one is retired, not freed."""
+    gw = _TC_WORKSPACES.get((index, "graph"))
+    if gw is None or gw.numel() < nbytes:
+        if gw is not None:
+            _TC_RETIRED.append(gw)
+        _TC_WORKSPACES[(index, "graph")] = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
 
 
 def reserve_graph_workspace(device: torch.device, nbytes: int) -> None:
@@ -116,9 +128,7 @@ def reserve_graph_workspace(device: torch.device, nbytes: int) -> None:
         raise RuntimeError("reserve_graph_workspace must be called outside stream capture")
     index = device.index if device.index is not None else torch.cuda.current_device()
     with _TC_LOCK:
-        ws = _TC_WORKSPACES.get((index, "graph"))
-        if ws is None or ws.numel() < nbytes:
-            _TC_WORKSPACES[(index, "graph")] = torch.zeros(max(nbytes, _TC_MIN_BYTES), dtype=torch.uint8, device=device)
+        _grow_graph_workspace(index, device, nbytes)
 
 
 def device_status(reset: bool = False) -> int:
@@ -132,6 +142,9 @@ def device_status(reset: bool = False) -> int:
         with _TC_LOCK:
             for (dev, _), ws in _TC_WORKSPACES.items():
                 if dev == index:
+                    ws[:_COUNTER_BYTES].zero_()
+            for ws in _TC_RETIRED:
+                if ws.device.index == index:
                     ws[:_COUNTER_BYTES].zero_()
         torch.cuda.synchronize()
     return status

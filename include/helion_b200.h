@@ -371,6 +371,41 @@ int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, con
                                  int64_t m, int64_t n, int64_t k, int64_t n_total, int64_t col0, float alpha,
                                  int out_dtype, void* stream);
 
+/* ---- expert-parallel exchange of the NVFP4 MoE layer (one process per GPU) ----
+ *
+ * Rank r owns experts [r E/W, (r+1) E/W) and `tokens` tokens of its own.  Every rank allocates one symmetric,
+ * zero-filled buffer of hb200_ep_buffer_bytes(...) bytes; bases[i] is rank i's buffer as mapped into this process.
+ * A step: hb200_ep_dispatch, hb200_peer_barrier, [hb200_ep_collect, sort + schedule, hb200_ep_gather, the two grouped
+ * GEMMs], hb200_ep_return, hb200_peer_barrier, hb200_ep_combine.  Rows travel as NVFP4 (codes + block scales + one
+ * global scale per token), results as ONE routing-weighted bf16 row per (token, expert rank).  The receive areas
+ * have a capacity that follows from the shapes (tokens * min(top_k, E/W) pairs per source), so no count is ever
+ * read on the host.  Peer memory is only stored to; nothing is multicast.  hidden % 64 == 0, experts % world == 0.
+ * No counterpart in the reference (its distributed examples push to peers and signal the same way:
+ * examples/distributed/all_gather_matmul.py:36-87). */
+int64_t hb200_ep_buffer_bytes(int64_t world, int64_t tokens, int64_t hidden, int64_t top_k, int64_t experts);
+int64_t hb200_ep_slots(int64_t world, int64_t tokens, int64_t hidden, int64_t top_k, int64_t experts);
+/* codes_t [T, H/2], scales_t swizzled [T, H/16], g_t [T]: per-token NVFP4 rows (hb200_nvfp4_quantize); weights fp32
+ * and experts_of_pair int64 [T * top_k] (hb200_moe_route_top_k); sorted_pairs / counts from hb200_moe_sort_pairs over
+ * the global expert ids; route_local int32 [T * top_k] (this rank's memory) receives where every pair went. */
+int hb200_ep_dispatch(const void* codes_t, const void* scales_t, const float* g_t, const float* weights,
+                      const int64_t* experts_of_pair, const int32_t* sorted_pairs, const int32_t* counts,
+                      int32_t* route_local, void* const* bases, int64_t world, int64_t rank, int64_t tokens,
+                      int64_t hidden, int64_t top_k, int64_t experts, void* stream);
+/* expert_of_slot int32 [hb200_ep_slots]: local expert of every receive slot, -1 where nothing arrived. */
+int hb200_ep_collect(const void* base, int32_t* expert_of_slot, int64_t world, int64_t rank, int64_t tokens,
+                     int64_t hidden, int64_t top_k, int64_t experts, void* stream);
+/* Received rows -> padded expert-sorted operand of the first grouped GEMM; w_row = routing weight per padded row.
+ * sorted_slots / row_of_sorted from hb200_moe_sort_pairs / hb200_moe_build_schedule over expert_of_slot. */
+int hb200_ep_gather(const void* base, const int32_t* sorted_slots, const int32_t* row_of_sorted, void* codes_out,
+                    void* scales_out, float* g_out, float* w_row, int64_t world, int64_t rank, int64_t tokens,
+                    int64_t hidden, int64_t top_k, int64_t experts, void* stream);
+/* o [padded rows, H] bf16: the second grouped GEMM's rows; row_of_slot: padded row of every receive slot. */
+int hb200_ep_return(const void* o_bf16, int64_t ldo, const int32_t* row_of_slot, const float* w_row,
+                    void* const* bases, int64_t world, int64_t rank, int64_t tokens, int64_t hidden, int64_t top_k,
+                    int64_t experts, void* stream);
+int hb200_ep_combine(const void* base, const int32_t* route_local, void* out_bf16, int64_t world, int64_t rank,
+                     int64_t tokens, int64_t hidden, int64_t top_k, int64_t experts, void* stream);
+
 /* Barrier between the ranks as a kernel on `stream`: flag_ptrs[i] is rank i's array of >= world uint32
  * (zero-initialised symmetric memory), epoch_counter one uint32 in this rank's own memory (zero-initialised,
  * owned by the barrier).  Orders every earlier peer store on the stream before the other ranks' later reads.

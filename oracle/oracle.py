@@ -403,8 +403,9 @@ def nvfp4_moe(
     """NVFP4 MoE layer (composition; the reference has no NVFP4 MoE): route, then per expert
     quantise the gathered bf16 rows per token to NVFP4, ``h = deq(A) @ deq(W_gu)^T`` in fp32,
     ``y = silu(h[:, :I]) * h[:, I:]`` (gate first, as silu_and_mul_per_block_quant), requantise y per
-    token, ``o = deq(y) @ deq(W_d)^T``, and accumulate ``out[t] += weight * o`` in fp32; bf16 result.
-    The per-expert loop is moe_matmul_ogs_reference's (examples/moe_matmul_ogs.py:128-151).
+    token, ``o = bf16(deq(y) @ deq(W_d)^T)``, and accumulate ``out[t] += weight * o`` in fp32; bf16 result.
+    The per-expert loop is moe_matmul_ogs_reference's (examples/moe_matmul_ogs.py:128-151), which returns every
+    expert's output rows in the activation dtype: ``o`` is rounded to bf16 before the routing-weighted sum.
 
     Weights: ``w_gu_packed [E, 2I, H/2]``, ``w_d_packed [E, H, I/2]``; scales are per-expert swizzled
     buffers; ``*_global`` are per-expert fp32 global scales ``[E]``.  The intermediate ``h`` is rounded to
@@ -443,7 +444,7 @@ def nvfp4_moe(
             keep["g"].append(yg)
         yq = dequant_scaled_k_major(yp, ysc) * yg.reshape(-1, 1)
         wd = dequant_scaled_k_major(w_d_packed[e], w_d_scale[e]) * w_d_global[e]
-        o = yq @ wd.t()
+        o = (yq @ wd.t()).to(torch.bfloat16).to(torch.float32)
         out.index_add_(0, tok, o * weights[tok, slot].reshape(-1, 1))
     if return_pairs:
         return out.to(torch.bfloat16), {k: torch.cat(v) for k, v in keep.items()}
@@ -462,7 +463,8 @@ def nvfp4_moe_down(
 ) -> Tensor:
     """Second half of :func:`nvfp4_moe` from a given quantised intermediate (``codes [P, I]`` nibbles,
     ``scales [P, I/16]`` e4m3 logical, ``g [P]``): ``o = deq(y) @ deq(W_d)^T``, routing-weighted sum per token
-    in fp32, bf16 result.  Used to show that an output difference comes from the intermediate's codes alone."""
+    in fp32 over bf16 expert rows, bf16 result.  Used to show that an output difference comes from the
+    intermediate's codes alone."""
     p, inter = codes.shape
     hdim = next(w for w in w_d_packed if w is not None).shape[0]
     yq = dequant_e2m1(codes) * scales.to(torch.float32).repeat_interleave(16, dim=1) * g.reshape(-1, 1)
@@ -470,6 +472,6 @@ def nvfp4_moe_down(
     for e in expert.unique().tolist():
         sel = (expert == e).nonzero(as_tuple=True)[0]
         wd = dequant_scaled_k_major(w_d_packed[e], w_d_scale[e]) * w_d_global[e]
-        o = yq[sel] @ wd.t()
+        o = (yq[sel] @ wd.t()).to(torch.bfloat16).to(torch.float32)
         out.index_add_(0, tok[sel], o * weights[tok[sel], slot[sel]].reshape(-1, 1))
     return out.to(torch.bfloat16)
