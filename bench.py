@@ -902,7 +902,8 @@ def sub_gemv_published_shapes(args, dev, timer) -> dict:
         xq, xs, gx = hb.nvfp4_quantize(x.reshape(1, -1), hb.layouts.nvfp4_global_scale(x).reshape(1))
         ms, med = timer.run2(graphed(lambda: hb.nvfp4_gemv_bf16in(codes, x, scales, gw))[0], steps, 3)
         rec = {"w4a16": hbm_record(ms, med, gemv_bytes(n, k), reference_published_us=pub["w4a16_us"])}
-        ms, med = timer.run2(graphed(lambda: hb.nvfp4_gemv_fp4in(codes, xq.reshape(-1), scales, xs, gw * float(gx)))[0], steps, 3)
+        alpha4 = gw * float(gx)
+        ms, med = timer.run2(graphed(lambda: hb.nvfp4_gemv_fp4in(codes, xq.reshape(-1), scales, xs, alpha4))[0], steps, 3)
         rec["w4a4"] = hbm_record(ms, med, gemv_bytes(n, k) - k - k // 2 + k // 16, reference_published_us=pub["w4a4_us"])
         out[f"{n}x{k}"] = rec
         del codes, scales

@@ -6,7 +6,9 @@
 //              of where every pair went follow                                              (then a peer barrier)
 //   experts  : the owning rank sorts what arrived by expert, runs the two grouped GEMMs with SiLU-mul between them,
 //   return   : sums, per (source rank, token), the routing-weighted bf16 output rows of that token's pairs in fp32
-//              (slot order) and pushes ONE bf16 row per (token, expert rank) back to the source  (peer barrier)
+//              (slot order) and pushes ONE row per (token, expert rank) back to the source: fp16 values times a
+//              power-of-two row scale that travels with them (11 significant bits at the bytes of bf16, so the
+//              per-rank partial sums add at most 2^-12 of relative error each)            (peer barrier)
 //   combine  : the source adds the rows it got from the ranks its token used, in rank order, in fp32.
 // Everything that crosses NVLink is a plain store from the sending rank's kernel into the receiver's symmetric
 // buffer; nothing is loaded from peer memory, nothing is multicast, no count is read on the host: the receive
@@ -31,7 +33,7 @@ struct EpShape {
 
 // Byte offsets of the regions inside one rank's symmetric buffer.
 struct EpLayout {
-  int64_t codes, sf, meta, count, table, ret, bytes;
+  int64_t codes, sf, meta, count, table, ret, ret_scale, bytes;
 };
 
 __host__ __device__ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -45,6 +47,7 @@ __host__ __device__ inline EpLayout ep_layout(const EpShape& s) {
   l.count = off; off = align_up(off + int64_t(s.world) * 4, 256);
   l.table = off; off = align_up(off + int64_t(s.world) * s.tokens * s.top_k * 4, 256);
   l.ret = off;   off = align_up(off + int64_t(s.world) * s.tokens * s.hidden * 2, 256);
+  l.ret_scale = off; off = align_up(off + int64_t(s.world) * s.tokens * 4, 256);
   l.bytes = off;
   return l;
 }
@@ -160,58 +163,103 @@ ep_gather_kernel(const uint8_t* __restrict__ base, const int32_t* __restrict__ s
   }
 }
 
-// ---- return: one CTA row of work per (source rank, token): out = bf16(sum over the token's pairs that came to
-// this rank, in slot order, of weight * o[row]) in fp32, stored into the source's return area [this rank][token].
+// ---- return: one CTA per (source rank, token): row = sum over the token's pairs that came to this rank, in slot
+// order, of weight * o[row] in fp32; the row goes to the source's return area [this rank][token] as fp16 values
+// times 2^e (e from the row's largest magnitude, so that it lands just below the fp16 maximum) with the factor
+// beside it.  Rows with no pair here are not written.  hidden <= 8 * 256 * kRetChunks.
+constexpr int kRetChunks = 4;  // 8-column chunks per thread: hidden <= 8192
+
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo, const int32_t* __restrict__ row_of_slot,
                  const float* __restrict__ w_row, const EpPeers peers, const uint8_t* __restrict__ base,
                  const EpShape s, const EpLayout l) {
-  const int64_t chunks = s.hidden >> 3;
-  const int64_t total = int64_t(s.world) * s.tokens * chunks;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int64_t st = i / chunks, c = i - st * chunks;  // st = source * T + token
-    const int src = int(st / s.tokens);
-    const int64_t t = st - int64_t(src) * s.tokens;
+  __shared__ float red[8];
+  __shared__ int64_t rows_s[64];
+  __shared__ float w_s[64];
+  __shared__ int n_rows_s;
+  const int64_t st = blockIdx.x;  // source * T + token
+  const int src = int(st / s.tokens);
+  const int64_t t = st - int64_t(src) * s.tokens;
+  if (threadIdx.x == 0) {
     const int32_t* tab = reinterpret_cast<const int32_t*>(base + l.table) + st * s.top_k;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    bool any = false;
+    int n = 0;
     for (int k = 0; k < s.top_k; ++k) {
       const int32_t v = tab[k];
       if (v < 0 || v / s.cap != s.rank) continue;
-      const int64_t slot = int64_t(src) * s.cap + (v - s.rank * s.cap);
-      const int64_t row = row_of_slot[slot];
+      const int64_t row = row_of_slot[int64_t(src) * s.cap + (v - s.rank * s.cap)];
       if (row < 0) continue;
-      any = true;
-      const float pw = w_row[row];
-      const uint4 q = ldg_stream_u4(o + row * ldo + c * 8);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      rows_s[n] = row;
+      w_s[n] = w_row[row];
+      ++n;
+    }
+    n_rows_s = n;
+  }
+  __syncthreads();
+  const int n_rows = n_rows_s;
+  if (n_rows == 0) return;
+  const int chunks = s.hidden >> 3;
+  float acc[kRetChunks][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRetChunks; ++j) {
+    const int c = threadIdx.x + j * 256;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[j][e] = 0.f;
+    if (c < chunks) {
+      for (int r = 0; r < n_rows; ++r) {
+        const float pw = w_s[r];
+        const uint4 q = ldg_stream_u4(o + rows_s[r] * ldo + c * 8);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[j][2 * e] = fmaf(pw, __uint_as_float(w[e] << 16), acc[j][2 * e]);
+          acc[j][2 * e + 1] = fmaf(pw, __uint_as_float(w[e] & 0xffff0000u), acc[j][2 * e + 1]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(acc[j][e]));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  // power of two that brings the largest magnitude into [2^14, 2^15): exact to apply and to undo
+  int ex = 0;
+  if (amax > 0.f && amax < INFINITY) ex = 14 - (int((__float_as_uint(amax) >> 23) & 0xffu) - 127);
+  ex = max(-100, min(100, ex));
+  const float up = __uint_as_float(uint32_t(127 + ex) << 23), down = __uint_as_float(uint32_t(127 - ex) << 23);
+  uint8_t* dst_base = peers.base[src];
+  __half* dst = reinterpret_cast<__half*>(dst_base + l.ret) + (int64_t(s.rank) * s.tokens + t) * s.hidden;
+#pragma unroll
+  for (int j = 0; j < kRetChunks; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < chunks) {
+      uint32_t pk[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        acc[2 * e] = fmaf(pw, __uint_as_float(w[e] << 16), acc[2 * e]);
-        acc[2 * e + 1] = fmaf(pw, __uint_as_float(w[e] & 0xffff0000u), acc[2 * e + 1]);
+        const __half2 h = __floats2half2_rn(acc[j][2 * e] * up, acc[j][2 * e + 1] * up);
+        pk[e] = *reinterpret_cast<const uint32_t*>(&h);
       }
+      *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
-    if (!any) continue;
-    uint32_t pk[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-      pk[e] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peers.base[src] + l.ret) +
-                         (int64_t(s.rank) * s.tokens + t) * s.hidden + c * 8;
-    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
   }
+  if (threadIdx.x == 0)
+    reinterpret_cast<float*>(dst_base + l.ret_scale)[int64_t(s.rank) * s.tokens + t] = down;
 }
 
 // ---- combine on the source: out[t] = bf16(sum over the ranks the token's pairs went to, ascending, of the row
-// that rank returned), fp32.
+// that rank returned times its factor), fp32.
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(const uint8_t* __restrict__ base, const int32_t* __restrict__ route_local,
                   __nv_bfloat16* __restrict__ out, const EpShape s, const EpLayout l) {
   const int64_t chunks = s.hidden >> 3;
   const int64_t total = int64_t(s.tokens) * chunks;
-  const __nv_bfloat16* ret = reinterpret_cast<const __nv_bfloat16*>(base + l.ret);
+  const __half* ret = reinterpret_cast<const __half*>(base + l.ret);
+  const float* ret_scale = reinterpret_cast<const float*>(base + l.ret_scale);
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
     const int64_t t = i / chunks, c = i - t * chunks;
     uint32_t used = 0;
@@ -222,12 +270,14 @@ ep_combine_kernel(const uint8_t* __restrict__ base, const int32_t* __restrict__ 
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int d = 0; d < s.world; ++d) {
       if (!(used >> d & 1u)) continue;
+      const float f = ret_scale[int64_t(d) * s.tokens + t];
       const uint4 q = ldg_stream_u4(ret + (int64_t(d) * s.tokens + t) * s.hidden + c * 8);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        acc[2 * e] += __uint_as_float(w[e] << 16);
-        acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+        acc[2 * e] = fmaf(v2.x, f, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(v2.y, f, acc[2 * e + 1]);
       }
     }
     uint32_t pk[4];
@@ -243,6 +293,7 @@ ep_combine_kernel(const uint8_t* __restrict__ base, const int32_t* __restrict__ 
 bool make_shape(int64_t world, int64_t rank, int64_t tokens, int64_t hidden, int64_t top_k, int64_t experts, EpShape* s) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return false;
   if (tokens <= 0 || tokens > (1 << 24) || hidden <= 0 || (hidden % 64) != 0 || hidden > (1 << 20)) return false;
+  if (hidden > 8 * 256 * kRetChunks) return false;
   if (top_k <= 0 || top_k > 64 || experts <= 0 || experts > 1024 || (experts % world) != 0 || top_k > experts) return false;
   s->world = int(world);
   s->rank = int(rank);
@@ -356,7 +407,8 @@ extern "C" int hb200_ep_gather(const void* base, const int32_t* sorted_slots, co
 
 // Return: o [padded rows, H] bf16 (leading dimension ldo) are the second grouped GEMM's rows, row_of_slot the padded
 // row of every receive slot, w_row the routing weight per padded row.  Stores one routing-weighted, pre-reduced
-// bf16 row per (source, token) that has pairs here into the source's return area.  Follow with hb200_peer_barrier.
+// row (fp16 values and a power-of-two factor) per (source, token) that has pairs here into the source's return
+// area.  Follow with hb200_peer_barrier.
 extern "C" int hb200_ep_return(const void* o_bf16, int64_t ldo, const int32_t* row_of_slot, const float* w_row,
                                void* const* bases, int64_t world, int64_t rank, int64_t tokens, int64_t hidden,
                                int64_t top_k, int64_t experts, void* stream) {
@@ -367,8 +419,7 @@ extern "C" int hb200_ep_return(const void* o_bf16, int64_t ldo, const int32_t* r
   if (!make_shape(world, rank, tokens, hidden, top_k, experts, &s)) return HB200_ERR_UNSUPPORTED;
   if (!make_peers(bases, s.world, &peers)) return HB200_ERR_INVALID_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(o_bf16) % 16) return HB200_ERR_INVALID_ARGUMENT;
-  const int64_t items = int64_t(s.world) * s.tokens * (s.hidden / 8);
-  ep_return_kernel<<<grid_for(items, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  ep_return_kernel<<<unsigned(int64_t(s.world) * s.tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o_bf16), ldo, row_of_slot, w_row, peers, peers.base[s.rank], s, ep_layout(s));
   return launch_status();
 }

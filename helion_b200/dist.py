@@ -343,7 +343,7 @@ class ExpertParallel:
     """NVFP4 MoE layer over expert-parallel ranks whose exchange is done by this library's own kernels over peer
     memory (``csrc/moe_ep.cu``): tokens travel as NVFP4 rows (codes, block scales, one global scale per token: about
     2.3 KB per (token, expert) pair at hidden 4096 instead of 8 KB in bf16), every expert rank returns ONE
-    routing-weighted, pre-reduced bf16 row per (token, rank), receive areas have a capacity that follows from the
+    routing-weighted, pre-reduced 2-byte row per (token, rank), receive areas have a capacity that follows from the
     shapes, and nothing is read on the host: a step is a fixed sequence of launches and two barrier kernels.
 
     ``tokens`` is the number of tokens per rank (fixed at construction: the symmetric buffer is sized from it).
@@ -351,8 +351,9 @@ class ExpertParallel:
     experts, the gate/up bundle interleaved with :func:`moe.interleave_gate_up`.
 
     Numerics: every (token, slot) pair is computed exactly as on one GPU; the sum over a token's slots is taken per
-    expert rank first (fp32, slot order, rounded to bf16) and over ranks second, so results agree with the one-GPU
-    layer to bf16 rounding of the partial sums, not bit for bit.
+    expert rank first (fp32, slot order; it travels as fp16 values with a power-of-two row factor, 11 significant
+    bits) and over ranks second, so results agree with the one-GPU layer up to a last-place flip of the bf16
+    result, not bit for bit.
     """
 
     def __init__(self, device: torch.device, tokens: int, hidden: int, top_k: int, num_experts: int, group=None,

@@ -377,9 +377,9 @@ int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, con
  * zero-filled buffer of hb200_ep_buffer_bytes(...) bytes; bases[i] is rank i's buffer as mapped into this process.
  * A step: hb200_ep_dispatch, hb200_peer_barrier, [hb200_ep_collect, sort + schedule, hb200_ep_gather, the two grouped
  * GEMMs], hb200_ep_return, hb200_peer_barrier, hb200_ep_combine.  Rows travel as NVFP4 (codes + block scales + one
- * global scale per token), results as ONE routing-weighted bf16 row per (token, expert rank).  The receive areas
+ * global scale per token), results as ONE routing-weighted row per (token, expert rank), fp16 values with a power-of-two row factor.  The receive areas
  * have a capacity that follows from the shapes (tokens * min(top_k, E/W) pairs per source), so no count is ever
- * read on the host.  Peer memory is only stored to; nothing is multicast.  hidden % 64 == 0, experts % world == 0.
+ * read on the host.  Peer memory is only stored to; nothing is multicast.  hidden % 64 == 0, hidden <= 8192, experts % world == 0.
  * No counterpart in the reference (its distributed examples push to peers and signal the same way:
  * examples/distributed/all_gather_matmul.py:36-87). */
 int64_t hb200_ep_buffer_bytes(int64_t world, int64_t tokens, int64_t hidden, int64_t top_k, int64_t experts);

@@ -68,11 +68,10 @@ def test_emulated_ranks_match_the_one_gpu_layer(world, t_local, h, inter, e, k):
         torch.cuda.synchronize()
         got = torch.cat([ep.combine() for ep in ranks])
         assert status_ok()
-        # the sum over a token's slots is taken per expert rank first (rounded to bf16), then over ranks
-        assert rel_err(got, single) <= 1e-2
-        if world == 1:
-            # one rank: one partial sum per token, which is the one-GPU combine itself
-            assert torch.equal(got, single)
+        # the sum over a token's slots is taken per expert rank first (11 significant bits), then over ranks, then
+        # rounded to bf16: against the one-GPU layer that is at most a last-place flip of the bf16 result
+        assert rel_err(got, single) <= 2.0**-7
+        assert float((got != single).float().mean()) <= 0.2
 
 
 def test_a_rank_that_receives_nothing_and_experts_without_tokens():
@@ -93,7 +92,7 @@ def test_a_rank_that_receives_nothing_and_experts_without_tokens():
         ep.run_experts(shard(w_gu_i, world, r), shard(w_d, world, r))
     got = torch.cat([ep.combine() for ep in ranks])
     assert status_ok()
-    assert torch.equal(got, single)  # every token's pairs sit on one rank: the same sum in the same order
+    assert rel_err(got, single) <= 2.0**-7  # every token's pairs sit on one rank: the same sum, re-rounded once
 
 
 def test_shapes_the_exchange_does_not_take():

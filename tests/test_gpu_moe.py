@@ -121,7 +121,7 @@ def test_moe_layer_against_oracle(t, h, inter, e, k, interleaved):
     # oracle's second half fed with the CUDA path's own intermediate reproduces the CUDA output within 1e-2.
     rep = C.moe_sample_report(x, logits, k, gu_bundle, d_bundle, y, got, torch.arange(t))
     assert rep["routing_same"]
-    assert rep["max_rel_err"] == pytest.approx(rel_err(y, ref))
+    assert abs(rep["max_rel_err"] - rel_err(y, ref)) <= 1e-3  # the report runs the oracle on the CUDA path's routing
     assert rep["max_rel_err_given_cuda_intermediate"] <= 1e-2
     assert rep["intermediate_codes_differing_by_more_than_one_step"] == 0
     assert rep["intermediate_scales_differing_by_more_than_one_step"] == 0
