@@ -40,6 +40,18 @@ struct F16Args {
   int groups;
 };
 
+// Direct mode (heterogeneous groups): every group has operands and an output of its own, with its own N and K.
+// The tensor maps and the per-group extents ride in kernel parameter space; a launch takes up to kDirectGroups.
+constexpr int kDirectGroups = 8;
+struct DirectMaps {
+  CUtensorMap a[kDirectGroups], b[kDirectGroups];
+};
+struct DirectGroups {
+  void* out[kDirectGroups];
+  int64_t ldc[kDirectGroups];
+  int m[kDirectGroups], n[kDirectGroups], k[kDirectGroups];
+};
+
 __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(
@@ -57,9 +69,12 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, bool bf16) {
          (uint32_t(m >> 4) << 24);
 }
 
-template <typename T>
+// DIRECT: the operands of tile (group, ...) come through that group's own tensor maps (row coordinates are local to
+// the group's matrices), its K and N are the group's, and the rows go to the group's own output.
+template <typename T, bool DIRECT>
 __global__ void __launch_bounds__(kF16Threads, 1)
 grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ DirectMaps dmaps, const __grid_constant__ DirectGroups dgroups,
                         const F16Args g) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr int ACC = 2;
@@ -74,8 +89,13 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_kb = (g.k + 63) / 64;
   const int num_tiles = g.num_row_tiles * g.n_tiles;
+  // K and N of a tile's group; a column tile past the group's N is skipped by every role alike
+  auto group_k = [&](int grp) -> int { return DIRECT ? dgroups.k[grp] : g.k; };
+  auto group_n = [&](int grp) -> int { return DIRECT ? dgroups.n[grp] : g.n; };
+  auto skip = [&](const int4& rt, int n_blk) -> bool {
+    return rt.x < 0 || rt.x >= g.groups || rt.w <= 0 || n_blk * kF16BlockN >= group_n(rt.x);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kF16Stages; ++s) {
@@ -101,15 +121,35 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const uint32_t tmem_base = *tmem_slot;
 
   // tile -> (row tile, column tile); all column tiles of a row tile run back to back
-  auto row_tile = [&](int tile) -> int4 { return g.tiles[tile / g.n_tiles]; };
+  auto row_tile = [&](int tile) -> int4 {
+    if constexpr (!DIRECT) {
+      return g.tiles[tile / g.n_tiles];
+    } else {
+      // groups own ceil(m / 128) consecutive row tiles each (groups with nothing to do have n == 0 and own none)
+      int rt = tile / g.n_tiles;
+      for (int i = 0; i < g.groups; ++i) {
+        const int own = dgroups.n[i] > 0 ? (dgroups.m[i] + 127) >> 7 : 0;
+        if (rt < own) {
+          const int rows = min(128, dgroups.m[i] - rt * 128);
+          return make_int4(i, rt * 128, rows, rows);
+        }
+        rt -= own;
+      }
+      return make_int4(-1, 0, 0, 0);
+    }
+  };
 
   if (warp == 0) {
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
       const int n_blk = tile % g.n_tiles;
+      if (skip(rt, n_blk)) continue;
+      const int num_kb = (group_k(rt.x) + 63) / 64;
+      const CUtensorMap* ma = DIRECT ? &dmaps.a[rt.x] : &tmap_a;
+      const CUtensorMap* mb = DIRECT ? &dmaps.b[rt.x] : &tmap_b;
+      const int b_row = DIRECT ? n_blk * kF16BlockN : rt.x * g.n + n_blk * kF16BlockN;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % kF16Stages;
         if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / kF16Stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -117,8 +157,8 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         uint8_t* st = smem + s * kF16StageBytes;
         if (elect_one()) {
           mbar_arrive_expect_tx(bar, kF16StageBytes);
-          tma_load_2d(smem_u32(st), &tmap_a, kb * 64, rt.y, bar);
-          tma_load_2d(smem_u32(st + kF16ABytes), &tmap_b, kb * 64, rt.x * g.n + n_blk * kF16BlockN, bar);
+          tma_load_2d(smem_u32(st), ma, kb * 64, rt.y, bar);
+          tma_load_2d(smem_u32(st + kF16ABytes), mb, kb * 64, b_row, bar);
         }
         __syncwarp();
       }
@@ -129,7 +169,9 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
+      if (skip(rt, tile % g.n_tiles)) continue;
+      const int k_g = group_k(rt.x);
+      const int num_kb = (k_g + 63) / 64;
       const int acc = tc % ACC;
       const uint32_t acc_ph = (tc / ACC) & 1;
       ++tc;
@@ -142,7 +184,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         tcgen05_fence_after();
         uint8_t* st = smem + s * kF16StageBytes;
         const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + kF16ABytes);
-        const int k_left = g.k - kb * 64;
+        const int k_left = k_g - kb * 64;
         const int steps = k_left >= 64 ? 4 : (k_left + 15) / 16;  // K tail: TMA zero-fills past K
         if (elect_one()) {
           for (int a = 0; a < steps; ++a) {
@@ -160,14 +202,12 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
   } else {
     const int quarter = warp & 3;
-    T* out = static_cast<T*>(g.out);
-    const bool vec_ok = (g.ldc * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(g.out) % 16) == 0;
     uint32_t tc = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int4 rt = row_tile(tile);
-      if (rt.x < 0 || rt.x >= g.groups || rt.w <= 0) continue;
       const int n_blk = tile % g.n_tiles;
+      if (skip(rt, n_blk)) continue;
       const int acc = tc % ACC;
       const uint32_t acc_ph = (tc / ACC) & 1;
       ++tc;
@@ -175,7 +215,12 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       tcgen05_fence_after();
       const int r_in = quarter * 32 + lane;
       const int64_t row = int64_t(rt.y) + r_in;
-      const bool store = r_in < rt.w && row >= 0 && row < g.rows_total;  // a tile list built from bad sizes cannot write outside
+      const int rows_total = DIRECT ? dgroups.m[rt.x] : g.rows_total;
+      const int n_g = group_n(rt.x);
+      const int64_t ldc = DIRECT ? dgroups.ldc[rt.x] : g.ldc;
+      T* out = DIRECT ? static_cast<T*>(dgroups.out[rt.x]) : static_cast<T*>(g.out);
+      const bool vec_ok = (ldc * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0;
+      const bool store = r_in < rt.w && row >= 0 && row < rows_total;  // a tile list built from bad sizes cannot write outside
       const float keep = r_in < rt.z ? 1.0f : 0.0f;  // rows between "valid" and "store" are written as zero
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * kF16BlockN;
 #pragma unroll 1
@@ -184,7 +229,7 @@ grouped_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
         const int col = n_blk * kF16BlockN + c * 32;
-        if (store && col < g.n) store_row_chunk<T>(out + row * g.ldc + col, r, keep, g.n - col, vec_ok);
+        if (store && col < n_g) store_row_chunk<T>(out + row * ldc + col, r, keep, n_g - col, vec_ok);
       }
       tcgen05_fence_before();
       mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
@@ -206,6 +251,20 @@ bool make_f16_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, i
   if (!fn) return false;
   const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
+            dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same map for a matrix whose rows are `pitch` elements apart (a view into a larger allocation).
+bool make_f16_map_pitched(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t pitch, int box_rows,
+                          bool bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(pitch) * 2};
   const cuuint32_t box[2] = {64, cuuint32_t(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
@@ -396,16 +455,73 @@ extern "C" int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, c
   const int grid = int(tiles < sms ? tiles : sms);
   constexpr size_t smem = size_t(kF16Stages) * kF16StageBytes + (2 * kF16Stages + 4) * 8 + 16 + 1024;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const DirectMaps no_maps{};
+  const DirectGroups no_groups{};
   if (is_bf16) {
-    auto kernel = grouped_gemm_f16_kernel<__nv_bfloat16>;
+    auto kernel = grouped_gemm_f16_kernel<__nv_bfloat16, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
-    kernel<<<grid, kF16Threads, smem, s>>>(ta, tb, g);
+    kernel<<<grid, kF16Threads, smem, s>>>(ta, tb, no_maps, no_groups, g);
   } else {
-    auto kernel = grouped_gemm_f16_kernel<__half>;
+    auto kernel = grouped_gemm_f16_kernel<__half, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
-    kernel<<<grid, kF16Threads, smem, s>>>(ta, tb, g);
+    kernel<<<grid, kF16Threads, smem, s>>>(ta, tb, no_maps, no_groups, g);
   }
   return launch_status();
+}
+
+// Direct mode of the reference's grouped GEMM (pretuned_kernels/grouped_gemm/grouped_gemm.py:213-327): group i is an
+// NT GEMM of its own, out_i[m_i, n_i] = A_i[m_i, k_i] . B_i[n_i, k_i]^T, with operands and output anywhere in
+// device memory (the reference passes a device table of pointers and strides; here the host arrays those tables
+// were built from).  All pointer / size arrays are HOST arrays of `groups` entries; lda / ldb / ldc are row pitches in
+// elements (unit stride along K and N).  One launch per eight groups.  k_i % 8 == 0, bases 16-byte aligned.
+extern "C" int hb200_grouped_gemm_f16_direct(const void* const* a_ptrs, const void* const* b_ptrs, void* const* out_ptrs,
+                                             const int64_t* m, const int64_t* n, const int64_t* k, const int64_t* lda,
+                                             const int64_t* ldb, const int64_t* ldc, int64_t groups, int is_bf16,
+                                             void* stream) {
+  using namespace hb200;
+  if (!a_ptrs || !b_ptrs || !out_ptrs || !m || !n || !k || !lda || !ldb || !ldc || groups < 0) return HB200_ERR_INVALID_ARGUMENT;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr size_t smem = size_t(kF16Stages) * kF16StageBytes + (2 * kF16Stages + 4) * 8 + 16 + 1024;
+  for (int64_t g0 = 0; g0 < groups; g0 += kDirectGroups) {
+    const int cnt = int(groups - g0 < kDirectGroups ? groups - g0 : kDirectGroups);
+    DirectMaps maps{};
+    DirectGroups dg{};
+    int64_t row_tiles = 0, max_n = 0;
+    for (int i = 0; i < cnt; ++i) {
+      const int64_t gi = g0 + i;
+      if (m[gi] < 0 || n[gi] < 0 || k[gi] < 0 || lda[gi] < k[gi] || ldb[gi] < k[gi] || ldc[gi] < n[gi]) return HB200_ERR_INVALID_ARGUMENT;
+      if (m[gi] > 0x7fffff00 || n[gi] > 0x7fffff00 || k[gi] > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+      dg.m[i] = int(m[gi]); dg.n[i] = int(n[gi]); dg.k[i] = int(k[gi]);
+      dg.out[i] = out_ptrs[gi]; dg.ldc[i] = ldc[gi];
+      if (m[gi] == 0 || n[gi] == 0 || k[gi] == 0) { dg.n[i] = 0; continue; }  // nothing to do (k == 0 leaves out untouched)
+      if (!a_ptrs[gi] || !b_ptrs[gi] || !out_ptrs[gi]) return HB200_ERR_INVALID_ARGUMENT;
+      if ((k[gi] % 8) != 0 || (lda[gi] % 8) != 0 || (ldb[gi] % 8) != 0) return HB200_ERR_UNSUPPORTED;  // 16-byte row pitch for TMA
+      if (reinterpret_cast<uintptr_t>(a_ptrs[gi]) % 16 || reinterpret_cast<uintptr_t>(b_ptrs[gi]) % 16) return HB200_ERR_UNSUPPORTED;
+      if (!make_f16_map_pitched(&maps.a[i], a_ptrs[gi], m[gi], k[gi], lda[gi], 128, is_bf16 != 0)) return HB200_ERR_CUDA;
+      if (!make_f16_map_pitched(&maps.b[i], b_ptrs[gi], n[gi], k[gi], ldb[gi], kF16BlockN, is_bf16 != 0)) return HB200_ERR_CUDA;
+      row_tiles += ceil_div64(m[gi], 128);
+      if (n[gi] > max_n) max_n = n[gi];
+    }
+    if (row_tiles == 0 || max_n == 0) continue;
+    if (row_tiles > 0xffffff) return HB200_ERR_UNSUPPORTED;
+    // no tile list in this mode: the kernel derives (group, first row) of a row tile from the groups' row counts
+    F16Args g{nullptr, 0, 0, 0, nullptr, int(row_tiles), int(ceil_div64(max_n, kF16BlockN)), 0, cnt};
+    const int64_t tiles = row_tiles * g.n_tiles;
+    const int grid = int(tiles < sms ? tiles : sms);
+    if (is_bf16) {
+      auto kernel = grouped_gemm_f16_kernel<__nv_bfloat16, true>;
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+      kernel<<<grid, kF16Threads, smem, s>>>(maps.a[0], maps.b[0], maps, dg, g);
+    } else {
+      auto kernel = grouped_gemm_f16_kernel<__half, true>;
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+      kernel<<<grid, kF16Threads, smem, s>>>(maps.a[0], maps.b[0], maps, dg, g);
+    }
+    if (launch_status() != HB200_OK) return HB200_ERR_CUDA;
+  }
+  return HB200_OK;
 }
 
 extern "C" int hb200_build_row_tiles(const int32_t* group_offsets, int64_t groups, int32_t* row_tiles,

@@ -99,8 +99,10 @@ struct GemvArgs {
   float alpha;
 };
 
-template <bool X_FP4, bool VEC16>
-__global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs a) {
+// U: weight loads a thread keeps in flight per round.  4 for matrices that fill the machine several times over
+// (four CTAs per SM); 8 for small ones, which are bound by the latency of dependent rounds, not by occupancy.
+template <bool X_FP4, bool VEC16, int U>
+__global__ void __launch_bounds__(kGemvThreads, U == 4 ? 4 : 2) nvfp4_gemv_kernel(const GemvArgs a) {
   extern __shared__ uint4 xs[];
   __shared__ float part[kMaxSplit][kRowsPerCta];
 
@@ -123,6 +125,7 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
   const uint4* xp = xs + j;
 
   float acc = 0.f;
+  if (n_split > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");  // waited for before the reduction
 
   // The CTA's K range is consumed in chunks of kChunkIters iterations so the
   // staged activation stays small enough for several CTAs per SM.
@@ -130,10 +133,6 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
   for (int64_t c_begin = k_begin; c_begin < k_end; c_begin += int64_t(kChunkIters) * kIterK) {
     const int64_t c_end = min(k_end, c_begin + int64_t(kChunkIters) * kIterK);
     const int n_iter = int((c_end - c_begin + kIterK - 1) / kIterK);
-    if (c_begin != k_begin) __syncthreads();  // previous chunk fully consumed
-    stage_x<X_FP4>(xs, a.x, a.x_scale, c_begin, c_end, n_iter);
-    __syncthreads();
-
     const uint8_t* wp = a.w + (row_ok ? row : 0) * k_bytes + (c_begin >> 1) + j * 16;
     // scale bytes of groups (2j, 2j+1) of this lane's row, inside column tile j/2 of the iteration
     const uint8_t* sp =
@@ -161,8 +160,26 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
       return *reinterpret_cast<const unsigned short*>(sp + int64_t(it) * (4 * 512));
     };
 
-    constexpr int U = 4;
+    // The first weight and scale loads of the chunk do not depend on the staged activation: they are issued
+    // before it is staged, so their latency overlaps the activation's (on a small matrix a CTA's whole share
+    // is these few loads, and the two latencies in a row were a third of the kernel).
+    uint4 w0[U];
+    uint32_t sc0[U];
+    const bool head = full_iter >= U;
+    if (head) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) { w0[u] = load_w(u); sc0[u] = load_s(u); }
+    }
+    if (c_begin != k_begin) __syncthreads();  // previous chunk fully consumed
+    stage_x<X_FP4>(xs, a.x, a.x_scale, c_begin, c_end, n_iter);
+    __syncthreads();
+
     int it = 0;
+    if (head) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) consume(w0[u], sc0[u], u);
+      it = U;
+    }
 #pragma unroll 1
     for (; it + U <= full_iter; it += U) {
       uint4 w[U];
@@ -209,9 +226,9 @@ __global__ void __launch_bounds__(kGemvThreads) nvfp4_gemv_kernel(const GemvArgs
     return;
   }
   // split-K: every CTA deposits its 32 partial sums in the leader's shared
-  // memory.  The first sync guarantees the leader is resident before the
-  // remote store, the second publishes the stores.
-  cluster.sync();
+  // memory.  The first barrier (arrived at when the kernel started, waited for only here, so it costs
+  // nothing by now) guarantees the leader is resident before the remote store, the second publishes the stores.
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
   if (j == 0) {
     float* dst = cluster.map_shared_rank(&part[0][0], 0);
     dst[split * kRowsPerCta + warp * 4 + q] = acc;
@@ -246,11 +263,14 @@ int launch_gemv(const GemvArgs& base, cudaStream_t stream) {
   // four CTAs cover one 128-row scale tile (rows l + 32q), so tiles are launched whole
   const int64_t row_groups = ceil_div64(a.n, 128) * 4;
   const int64_t total_iters = ceil_div64(a.k, kIterK);
-  // Split K over a cluster until the grid can fill the machine (>= 4 CTAs per
-  // SM) while every CTA keeps at least 4 iterations.
+  // Split K over a cluster until every SM has two CTAs, while every CTA keeps at least 4 iterations.  Measured
+  // on 19 to 47 MB matrices (in-graph, microseconds for cluster sizes 1 / 2 / 4 / 8): 8192 x 4096: 9.5 / 8.6 / 10.1 /
+  // 15.8; 8192 x 8192: 15.6 / 12.4 / 14.1 / 17.1; 15360 x 5120: 14.2 / 16.4 / 19.5 / 30.8: the cluster barrier and
+  // the reduction through distributed shared memory cost more than the extra CTAs bring beyond that point.
   int split = 1;
-  const int64_t want = int64_t(sm_count()) * 4;
-  while (split < kMaxSplit && row_groups * split < want && total_iters / (split * 2) >= 4) split *= 2;
+  const int64_t want = int64_t(sm_count()) * 2;
+  while (split < 4 && row_groups * split < want && total_iters / (split * 2) >= 4) split *= 2;
+
   a.iters_per_split = int(ceil_div64(total_iters, split));
   if (row_groups > 0x7fffffff) return HB200_ERR_UNSUPPORTED;
   const size_t smem = size_t(kChunkIters) * kIterK * 2;
@@ -267,8 +287,11 @@ int launch_gemv(const GemvArgs& base, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, nvfp4_gemv_kernel<X_FP4, VEC16>, a) != cudaSuccess) return HB200_ERR_CUDA;
-  return HB200_OK;
+  // small grids (at most three CTAs per SM): the deeper kernel
+  const bool deep = row_groups * split <= int64_t(sm_count()) * 3 && a.iters_per_split >= 8;
+  const cudaError_t rc = deep ? cudaLaunchKernelEx(&cfg, nvfp4_gemv_kernel<X_FP4, VEC16, 8>, a)
+                              : cudaLaunchKernelEx(&cfg, nvfp4_gemv_kernel<X_FP4, VEC16, 4>, a);
+  return rc == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
 }
 
 template <bool X_FP4>

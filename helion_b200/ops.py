@@ -11,6 +11,7 @@ CUDA stream.  There is no CPU or eager fallback: non-CUDA tensors raise.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 
 import torch
@@ -80,7 +81,10 @@ _TC_WORKSPACES: dict[tuple[int, int | str], Tensor] = {}
 _TC_RETIRED: list[Tensor] = []  # outgrown graph workspaces, kept alive for the graphs that captured them
 _TC_LOCK = threading.Lock()
 _TC_MIN_BYTES = 1 << 22
-_TC_MIN_WEIGHT_ELEMS = 1 << 21  # below this a launch is latency-bound and the SIMT kernels do as well
+_TC_MIN_WEIGHT_ELEMS = int(os.environ.get("HB200_TC_MIN_ELEMS", 1 << 21))  # below this the SIMT kernel is faster alone
+# a single row: measured alone (19 to 66 MB of weights) the SIMT kernel is 2 to 6 us faster; from about 130 MB on
+# the tensor-core kernel wins (8192 x 28672: 36.9 against 38.9 us, 57344 x 8192: 55 against 65 us)
+_TC_MIN_WEIGHT_ELEMS_1ROW = int(os.environ.get("HB200_TC_MIN_ELEMS_1ROW", 100_000_000))
 
 
 def tc_workspace(device: torch.device, nbytes: int) -> Tensor:
@@ -151,13 +155,14 @@ def device_status(reset: bool = False) -> int:
 
 
 def _tc_eligible(n: int, k: int, batch: int) -> bool:
-    return k % 32 == 0 and n >= 128 and 1 <= batch <= 32 and n * k >= _TC_MIN_WEIGHT_ELEMS
+    floor = _TC_MIN_WEIGHT_ELEMS_1ROW if batch == 1 else _TC_MIN_WEIGHT_ELEMS
+    return k % 32 == 0 and n >= 128 and 1 <= batch <= 32 and n * k >= floor
 
 
 def _gemv_path(path: str, n: int, k: int, batch: int) -> str:
     if path == "auto":
-        # The tensor-core kernel streams a 70B-class layer 11 % faster than the SIMT one for a single activation
-        # row and its cost barely grows with rows; small matrices (latency-bound) and K % 32 != 0 stay on SIMT.
+        # The tensor-core kernel streams the large matrices of a 70B-class layer faster than the SIMT one and its
+        # cost barely grows with rows; small matrices (latency-bound) and K % 32 != 0 stay on SIMT.
         return "tc" if _tc_eligible(n, k, batch) else "simt"
     if path not in ("simt", "mma", "tc"):
         raise ValueError(f"path must be 'auto', 'simt', 'mma' or 'tc'; got {path!r}")
