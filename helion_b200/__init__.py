@@ -8,7 +8,10 @@ library ``libhelion_b200.so`` declared in ``include/helion_b200.h``.
 """
 
 from . import layouts
+from .grouped import grouped_gemm
 from .grouped import grouped_gemm_deepgemm
+from .grouped import grouped_gemm_direct
+from .grouped import grouped_gemm_split_sizes
 from .grouped import grouped_gemm_jagged
 from .grouped import grouped_gemm_jagged_persistent
 from .grouped import moe_matmul_ogs
@@ -29,11 +32,16 @@ from .ops import dynamic_per_token_scaled_fp8_quant
 from .ops import scaled_mm
 from .ops import silu_mul_fp8
 from .ops import rms_norm_dynamic_per_token_quant
+from .ops import rms_norm_nvfp4_quant
+from .ops import silu_and_mul_nvfp4_quant
 from .ops import rms_norm_per_block_quant
 from .ops import silu_and_mul_per_block_quant
 
 __all__ = [
+    "grouped_gemm",
     "grouped_gemm_deepgemm",
+    "grouped_gemm_direct",
+    "grouped_gemm_split_sizes",
     "grouped_gemm_jagged",
     "grouped_gemm_jagged_persistent",
     "moe_matmul_ogs",
@@ -51,6 +59,8 @@ __all__ = [
     "scaled_mm",
     "silu_mul_fp8",
     "rms_norm_dynamic_per_token_quant",
+    "rms_norm_nvfp4_quant",
+    "silu_and_mul_nvfp4_quant",
     "rms_norm_per_block_quant",
     "silu_and_mul_per_block_quant",
     "swizzle_fp8_scales",

@@ -4,6 +4,7 @@
 * :func:`moe_matmul_ogs_helion_kernel_args_gen` -- ``examples/moe_matmul_ogs.py:89-124``, without the host read
 * :func:`grouped_gemm_jagged` / :func:`grouped_gemm_jagged_persistent` -- ``examples/grouped_gemm.py:52-225``
 * :func:`grouped_gemm_deepgemm` -- ``pretuned_kernels/grouped_gemm_deepgemm/grouped_gemm_deepgemm.py:172-224``
+* :func:`grouped_gemm` (direct mode, per-group N and K) -- ``pretuned_kernels/grouped_gemm/grouped_gemm.py:213-327``
 
 The kernel wants both operands K-major.  The reference's ``W [E, K, N]`` and ``B [K, N]`` are N-major, so these
 wrappers transpose them on the device first (a copy the caller can avoid by keeping weights K-major and calling
@@ -195,3 +196,111 @@ def grouped_gemm_deepgemm(a_packed: Tensor, b_grouped: Tensor, worklist: Tensor)
 @grouped_gemm_deepgemm.register_fake
 def _(a_packed, b_grouped, worklist):
     return a_packed.new_empty((a_packed.shape[0], b_grouped.shape[1]))
+
+
+# ------------------------------------------------------------------ direct mode (heterogeneous groups)
+@torch.library.custom_op("helion_b200::grouped_gemm_direct", mutates_args=("outputs",))
+def grouped_gemm_direct(group_a: list[Tensor], group_b: list[Tensor], outputs: list[Tensor]) -> None:
+    """``outputs[i] <- group_a[i] @ group_b[i].T`` (fp32 accumulate) for groups with their own M, N and K:
+    ``group_a[i] [M_i, K_i]``, ``group_b[i] [N_i, K_i]``, ``outputs[i] [M_i, N_i]``, all fp16 or all bf16, unit stride
+    along the last dimension, any row pitch, anywhere in device memory.  One launch per eight groups; nothing is
+    allocated or copied (K_i % 8 == 0)."""
+    import ctypes
+
+    groups = len(group_a)
+    if len(group_b) != groups or len(outputs) != groups:
+        raise ValueError("group_a, group_b and outputs must have one entry per group")
+    if groups == 0:
+        return
+    _require_cuda(*group_a, *group_b, *outputs)
+    dtype = group_a[0].dtype
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"operands must be bfloat16 or float16, got {dtype}")
+    for a, b, o in zip(group_a, group_b, outputs):
+        if a.dtype is not dtype or b.dtype is not dtype or o.dtype is not dtype:
+            raise TypeError("all operands and outputs must share one 2-byte dtype")
+        if a.dim() != 2 or b.dim() != 2 or o.dim() != 2 or a.shape[1] != b.shape[1] or o.shape != (a.shape[0], b.shape[0]):
+            raise ValueError(f"group shapes do not form A[M,K] @ B[N,K].T -> [M,N]: {tuple(a.shape)}, {tuple(b.shape)}, {tuple(o.shape)}")
+        if (a.numel() and a.stride(1) != 1) or (b.numel() and b.stride(1) != 1) or (o.numel() and o.stride(1) != 1):
+            raise ValueError("operands and outputs need unit stride along their last dimension")
+
+    def arr(ctype, values):
+        return (ctype * groups)(*values)
+
+    pitch = lambda t: t.stride(0) if t.shape[0] > 1 else max(t.shape[1], 1)  # noqa: E731
+    args = (
+        arr(ctypes.c_void_p, [t.data_ptr() for t in group_a]), arr(ctypes.c_void_p, [t.data_ptr() for t in group_b]),
+        arr(ctypes.c_void_p, [t.data_ptr() for t in outputs]),
+        arr(ctypes.c_int64, [t.shape[0] for t in group_a]), arr(ctypes.c_int64, [t.shape[0] for t in group_b]),
+        arr(ctypes.c_int64, [t.shape[1] for t in group_a]),
+        arr(ctypes.c_int64, [pitch(t) for t in group_a]), arr(ctypes.c_int64, [pitch(t) for t in group_b]),
+        arr(ctypes.c_int64, [pitch(t) for t in outputs]),
+    )
+    with torch.cuda.device(group_a[0].device):
+        _lib.call("hb200_grouped_gemm_f16_direct", *args, groups, int(dtype is torch.bfloat16), _stream())
+
+
+@grouped_gemm_direct.register_fake
+def _(group_a, group_b, outputs):
+    return None
+
+
+_DIRECT_PLANS: dict[tuple, tuple] = {}
+
+
+def grouped_gemm(a_placeholder: Tensor, b_placeholder: Tensor, layout: Tensor, n_sizes: Tensor, k_sizes: Tensor,
+                 out_placeholder: Tensor, direct_pointers: Tensor, direct_strides: Tensor,
+                 problem_signature: tuple[int, ...]) -> Tensor:
+    """Grouped ``A_g[M_g, K_g] @ B_g[N_g, K_g].T`` with direct runtime metadata: drop-in for ``grouped_gemm``
+    (pretuned_kernels/grouped_gemm/grouped_gemm.py:213-253) as ``_prepare_helion`` (:261-327) calls it.
+
+    ``direct_pointers`` (int64 ``[G, 3]``: A, B, out) and ``direct_strides`` (int32 ``[G, 3, 2]``) are the device
+    tables the reference builds from host values; ``problem_signature`` = ``(G, M_0, N_0, K_0, M_1, ...)`` carries
+    the real per-group sizes (the placeholders, ``layout``, ``n_sizes`` and ``k_sizes`` repeat them in forms this
+    kernel does not need).  The tables are read back once per (table, signature) and the launch plan is cached, so
+    later calls -- including captured ones -- touch no host-device copy; the first call must come before capture.
+    Operand dtype is the placeholders'.  Returns ``out_placeholder``.
+    """
+    import ctypes
+
+    del layout, n_sizes, k_sizes  # the padded row layout and the size vectors restate problem_signature
+    groups = int(problem_signature[0])
+    sizes = [tuple(int(v) for v in problem_signature[1 + 3 * g : 4 + 3 * g]) for g in range(groups)]
+    dtype = a_placeholder.dtype
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"operands must be bfloat16 or float16, got {dtype}")
+    if direct_pointers.shape != (groups, 3) or direct_pointers.dtype is not torch.int64:
+        raise ValueError(f"direct_pointers must be int64 [{groups}, 3]")
+    if direct_strides.shape != (groups, 3, 2):
+        raise ValueError(f"direct_strides must be [{groups}, 3, 2]")
+    _require_cuda(direct_pointers, direct_strides)
+    key = (direct_pointers.data_ptr(), direct_pointers._version, direct_strides.data_ptr(), direct_strides._version,
+           tuple(problem_signature), dtype)
+    plan = _DIRECT_PLANS.get(key)
+    if plan is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("grouped_gemm reads its pointer table back on the first call: call it once before capturing")
+        ptrs = direct_pointers.cpu().tolist()
+        strides = direct_strides.cpu().tolist()
+        for g, st in enumerate(strides):
+            if any(s[1] != 1 for s in st if sizes[g][0] and sizes[g][1] and sizes[g][2]):
+                raise ValueError("grouped_gemm needs unit stride along K (A, B) and N (out)")
+
+        def arr(ctype, values):
+            return (ctype * groups)(*values)
+
+        plan = (
+            arr(ctypes.c_void_p, [p[0] for p in ptrs]), arr(ctypes.c_void_p, [p[1] for p in ptrs]),
+            arr(ctypes.c_void_p, [p[2] for p in ptrs]),
+            arr(ctypes.c_int64, [s[0] for s in sizes]), arr(ctypes.c_int64, [s[1] for s in sizes]),
+            arr(ctypes.c_int64, [s[2] for s in sizes]),
+            arr(ctypes.c_int64, [max(st[0][0], sz[2]) for st, sz in zip(strides, sizes)]),
+            arr(ctypes.c_int64, [max(st[1][0], sz[2]) for st, sz in zip(strides, sizes)]),
+            arr(ctypes.c_int64, [max(st[2][0], sz[1]) for st, sz in zip(strides, sizes)]),
+        )
+        if len(_DIRECT_PLANS) > 256:
+            _DIRECT_PLANS.clear()
+        _DIRECT_PLANS[key] = plan
+    with torch.cuda.device(direct_pointers.device):
+        _lib.call("hb200_grouped_gemm_f16_direct", *plan, groups, int(dtype is torch.bfloat16), _stream())
+    return out_placeholder

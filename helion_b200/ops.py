@@ -410,6 +410,54 @@ def _(x, global_scale):
     )
 
 
+def _nvfp4_row_outputs(x: Tensor, rows: int, k: int):
+    codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    padded = rows % 128 != 0 or (k // 16) % 4 != 0
+    scales = (torch.zeros if padded else torch.empty)(swizzled_scale_numel(rows, k // 16), dtype=torch.uint8, device=x.device)
+    return codes, scales, torch.empty((rows,), dtype=torch.float32, device=x.device)
+
+
+@torch.library.custom_op("helion_b200::rms_norm_nvfp4_quant", mutates_args=())
+def _rms_norm_nvfp4_op(x: Tensor, weight: Tensor, epsilon: float) -> tuple[Tensor, Tensor, Tensor]:
+    _require_cuda(x, weight)
+    rows, k = x.shape
+    codes, scales, g = _nvfp4_row_outputs(x, rows, k)
+    if rows and k:
+        with torch.cuda.device(x.device):
+            _lib.call("hb200_rms_norm_nvfp4_quant", x.data_ptr(), weight.data_ptr(), codes.data_ptr(), scales.data_ptr(),
+                      g.data_ptr(), rows, k, x.stride(0), float(epsilon), _stream())
+    return codes, scales.view(_FP8), g
+
+
+@torch.library.custom_op("helion_b200::silu_and_mul_nvfp4_quant", mutates_args=())
+def _silu_mul_nvfp4_op(x: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+    _require_cuda(x)
+    rows, two_k = x.shape
+    k = two_k // 2
+    codes, scales, g = _nvfp4_row_outputs(x, rows, k)
+    if rows and k:
+        with torch.cuda.device(x.device):
+            _lib.call("hb200_nvfp4_quantize_rows", x.data_ptr(), codes.data_ptr(), scales.data_ptr(), g.data_ptr(),
+                      rows, k, x.stride(0), None, 1, None, None, 1, _stream())
+    return codes, scales.view(_FP8), g
+
+
+def _fake_nvfp4_rows(x, k):
+    rows = x.shape[0]
+    return (x.new_empty((rows, k // 2), dtype=torch.uint8), x.new_empty((swizzled_scale_numel(rows, k // 16),), dtype=_FP8),
+            x.new_empty((rows,), dtype=torch.float32))
+
+
+@_rms_norm_nvfp4_op.register_fake
+def _(x, weight, epsilon):
+    return _fake_nvfp4_rows(x, x.shape[1])
+
+
+@_silu_mul_nvfp4_op.register_fake
+def _(x):
+    return _fake_nvfp4_rows(x, x.shape[1] // 2)
+
+
 _OUT_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
@@ -843,3 +891,44 @@ def nvfp4_quantize(x: Tensor, global_scale: Tensor | None = None) -> tuple[Tenso
     if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
     return _nvfp4_quantize_op(x, global_scale)
+
+
+def _row_major_bf16(name: str, x: Tensor) -> Tensor:
+    if x.dim() != 2:
+        raise ValueError(f"{name} must be a 2D tensor")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError(f"{name} must be torch.bfloat16, got {x.dtype}")
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return x
+
+
+def rms_norm_nvfp4_quant(input: Tensor, weight: Tensor, epsilon: float) -> tuple[Tensor, Tensor, Tensor]:  # noqa: A002
+    """RMSNorm(weight) fused with per-token NVFP4 quantisation: bf16 ``[T, H]`` ->
+    ``(packed e2m1 [T, H/2] uint8, swizzled e4m3 scales for [T, H/16], per-token global scale [T])``.
+
+    The NVFP4 form of ``rms_norm_dynamic_per_token_quant``: the normalisation is that operator's
+    (pretuned_kernels/rms_norm_dynamic_per_token_quant/rms_norm_dynamic_per_token_quant.py:131-150), the quantiser
+    :func:`nvfp4_quantize`'s per-token mode; the normalised row never reaches memory.  The outputs are the activation
+    operand of :func:`nvfp4_gemv_fp4in` / :func:`nvfp4_scaled_matmul` (fold the per-token scale into ``alpha`` or the
+    consumer's row scale).
+    """
+    x = _row_major_bf16("input", input)
+    if x.shape[1] % 16:
+        raise ValueError(f"hidden size must be divisible by 16, got {x.shape[1]}")
+    if weight.dtype is not torch.bfloat16 or weight.numel() != x.shape[1]:
+        raise ValueError(f"weight must be bfloat16 with {x.shape[1]} values")
+    return _rms_norm_nvfp4_op(x, _aligned(weight.reshape(-1).contiguous()), float(epsilon))
+
+
+def silu_and_mul_nvfp4_quant(input: Tensor) -> tuple[Tensor, Tensor, Tensor]:  # noqa: A002
+    """``y = bf16(silu(input[:, :d]) * input[:, d:])`` fused with per-token NVFP4 quantisation of ``y``:
+    bf16 ``[T, 2d]`` -> ``(packed e2m1 [T, d/2], swizzled e4m3 scales for [T, d/16], per-token global scale [T])``.
+
+    The NVFP4 form of ``silu_and_mul_per_block_quant`` (gate first:
+    pretuned_kernels/silu_and_mul_per_block_quant/silu_and_mul_per_block_quant.py:97-105); ``y`` never reaches memory.
+    """
+    x = _row_major_bf16("input", input)
+    if x.shape[1] % 32:
+        raise ValueError(f"the last dimension must be 2 * d with d divisible by 16, got {x.shape[1]}")
+    return _silu_mul_nvfp4_op(x)

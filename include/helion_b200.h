@@ -112,6 +112,16 @@ int hb200_per_token_group_fp8_quant(const void* input, void* output_q, void* out
 int hb200_nvfp4_quantize(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
                          int64_t rows, int64_t k, int64_t ldx, int per_token, void* stream);
 
+/* RMSNorm fused with per-token NVFP4 quantisation (the NVFP4 form of rms_norm_dynamic_per_token_quant, whose
+ * normalisation arithmetic it keeps: pretuned_kernels/rms_norm_dynamic_per_token_quant/
+ * rms_norm_dynamic_per_token_quant.py:131-150): x [rows, k] bf16 (row pitch ldx), weight [k] bf16 -> codes
+ * [rows, k/2], swizzled scales for [rows, k/16], global_scale[rows] = row_amax / (6 * 448).  The reference has no
+ * NVFP4 producer (it leans on vLLM's scaled_fp4_quant, pretuned_kernels/nvfp4_gemv/nvfp4_gemv.py:241-246).
+ * The SiLU-mul form of the same producer is hb200_nvfp4_quantize_rows with silu_mul = 1. */
+int hb200_rms_norm_nvfp4_quant(const void* x_bf16, const void* weight_bf16, void* codes, void* scales_swizzled,
+                               float* global_scale, int64_t rows, int64_t k, int64_t ldx, float epsilon,
+                               void* stream);
+
 /* ------------------------------------------------------------ NVFP4 GEMM
  * D[M, N] = out_dtype(alpha * A[M, K] . B[N, K]^T), both operands packed e2m1
  * and K-major, e4m3 block scales in SWIZZLE_32_4_4 order for logical [M, K/16]
@@ -190,6 +200,17 @@ int hb200_moe_combine(const void* expert_out_bf16, int64_t ld, const int32_t* ro
 int hb200_grouped_gemm_f16(const void* a, const void* b, void* out, const int32_t* row_tiles,
                            int64_t num_row_tiles, int64_t a_rows, int64_t n, int64_t k, int64_t groups,
                            int64_t ldc, int is_bf16, void* stream);
+
+/* Direct mode of the reference's grouped GEMM (pretuned_kernels/grouped_gemm/grouped_gemm.py:213-327): group i is an
+ * NT GEMM of its own, out_i[m_i, n_i] = A_i[m_i, k_i] . B_i[n_i, k_i]^T (fp32 accumulate), with per-group N and K
+ * and operands / outputs anywhere in device memory.  The reference hands its kernel device tables of pointers and
+ * strides built from host values; this entry point takes those host values: every array argument is a HOST array
+ * of `groups` entries, lda / ldb / ldc are row pitches in elements (unit stride along K and N).  Groups with
+ * m, n or k == 0 are skipped (their outputs are left as they are).  k_i % 8 == 0, row pitches of A and B % 8 == 0,
+ * operand bases 16-byte aligned (HB200_ERR_UNSUPPORTED otherwise).  One launch per eight groups. */
+int hb200_grouped_gemm_f16_direct(const void* const* a_ptrs, const void* const* b_ptrs, void* const* out_ptrs,
+                                  const int64_t* m, const int64_t* n, const int64_t* k, const int64_t* lda,
+                                  const int64_t* ldb, const int64_t* ldc, int64_t groups, int is_bf16, void* stream);
 
 /* Row tiles of a jagged layout from device-resident group offsets [groups + 1]
  * (no host read): one entry per 128 rows of every group, unused entries marked.

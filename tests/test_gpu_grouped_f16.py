@@ -211,3 +211,93 @@ def test_grouped_gemm_graph_replay_after_mutating_inputs():
     graph2.replay()
     assert status_ok()
     assert rel_err(yj, O.grouped_gemm_jagged(a.cpu(), bj.cpu(), offs.cpu())) <= 1e-2
+
+
+# the seven cases of benchmarks/cute/compare_grouped_gemm_backends.py:102-116 (M, N, K per group): the default small
+# parity case and the CUTLASS-example shapes with M and N tails
+def _doc_case(m1, n3):
+    return ((8192, 1280, 32), (m1, 384, 1536), (640, 1280, 16), (640, n3, 16))
+
+
+DIRECT_CASES = {
+    "default_small_parity": ((128, 128, 128), (512, 128, 128), (128, 256, 128)),
+    "doc_no_mn_tail": _doc_case(128, 128), "doc_no_mn_g3_192_extra_full": _doc_case(128, 192),
+    "doc_original": _doc_case(16, 160), "doc_mtail_g1_g3_192_extra_full": _doc_case(16, 192),
+    "doc_mtail_g1_only": _doc_case(16, 128), "doc_ntail_g3_160": _doc_case(128, 160),
+}
+
+
+def _reference_args(problems, group_a, group_b, outputs):
+    """The arguments _prepare_helion builds (pretuned_kernels/grouped_gemm/grouped_gemm.py:261-327)."""
+    dev = group_a[0].device
+    aligned = [(m + 127) // 128 * 128 for m, _, _ in problems]
+    layout = torch.cat([torch.cat([torch.full((m,), g, dtype=torch.int32), torch.full((am - m,), -1, dtype=torch.int32)])
+                        for g, ((m, _, _), am) in enumerate(zip(problems, aligned))]).to(dev)
+    max_n, max_k = max(p[1] for p in problems), max(p[2] for p in problems)
+
+    def placeholder(shape):
+        base = torch.empty(max(1, shape[-1]), device=dev, dtype=group_a[0].dtype)
+        return torch.as_strided(base, shape, (0,) * (len(shape) - 1) + (1,))
+
+    pointers = torch.tensor([(a.data_ptr(), b.data_ptr(), o.data_ptr()) for a, b, o in zip(group_a, group_b, outputs)],
+                            dtype=torch.int64, device=dev)
+    strides = torch.tensor([(tuple(a.stride()), tuple(b.stride()), tuple(o.stride())) for a, b, o in zip(group_a, group_b, outputs)],
+                           dtype=torch.int32, device=dev)
+    signature = (len(problems),) + tuple(v for p in problems for v in p)
+    return (placeholder((sum(aligned), max_k)), placeholder((len(problems), max_n, max_k)), layout,
+            torch.tensor([p[1] for p in problems], dtype=torch.int32, device=dev),
+            torch.tensor([p[2] for p in problems], dtype=torch.int32, device=dev),
+            placeholder((sum(aligned), max_n)), pointers, strides, signature)
+
+
+@pytest.mark.parametrize("case", sorted(DIRECT_CASES))
+def test_direct_mode_heterogeneous_groups(case):
+    """Per-group M, N and K with separate operand and output tensors, through the reference's own call signature
+    (device pointer and stride tables) and through the list form; checked as check_correctness does (fp32 matmul of
+    the same operands), then replayed from a CUDA graph after the inputs changed."""
+    problems = DIRECT_CASES[case]
+    gen = torch.Generator().manual_seed(0)
+    group_a = [torch.randn(m, k, generator=gen).to(torch.float16).to(DEV) for m, _, k in problems]
+    group_b = [torch.randn(n, k, generator=gen).to(torch.float16).to(DEV) for _, n, k in problems]
+    outputs = [torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV) for m, n, _ in problems]
+
+    def check():
+        assert status_ok()
+        for a, b, o in zip(group_a, group_b, outputs):
+            assert rel_err(o, (a.float() @ b.float().t()).half()) <= 1e-2
+
+    args = _reference_args(problems, group_a, group_b, outputs)
+    out = hb.grouped_gemm(*args)
+    assert out is args[5]
+    check()
+    for o in outputs:
+        o.fill_(float("nan"))
+    hb.grouped_gemm_direct(group_a, group_b, outputs)
+    check()
+    graph, _ = _graph(lambda: hb.grouped_gemm(*args))
+    for t in group_a + group_b:
+        t.normal_()
+    for o in outputs:
+        o.fill_(float("nan"))
+    graph.replay()
+    check()
+
+
+def test_direct_mode_views_empty_groups_and_bf16():
+    gen = torch.Generator().manual_seed(4)
+    big_a = torch.randn(300, 512, generator=gen).to(torch.bfloat16).to(DEV)
+    big_o = torch.full((300, 1024), -7.0, dtype=torch.bfloat16, device=DEV)
+    group_a = [big_a[:130, 64:192], big_a[130:, 256:320], torch.empty(0, 64, dtype=torch.bfloat16, device=DEV)]
+    group_b = [torch.randn(200, 128, generator=gen).to(torch.bfloat16).to(DEV), torch.randn(72, 64, generator=gen).to(torch.bfloat16).to(DEV),
+               torch.randn(16, 64, generator=gen).to(torch.bfloat16).to(DEV)]
+    outputs = [big_o[:130, 8:208], big_o[130:, 512:584], torch.empty(0, 16, dtype=torch.bfloat16, device=DEV)]
+    hb.grouped_gemm_direct(group_a, group_b, outputs)
+    assert status_ok()
+    for a, b, o in zip(group_a[:2], group_b[:2], outputs[:2]):
+        assert rel_err(o, (a.float() @ b.float().t()).to(torch.bfloat16)) <= 1e-2
+    untouched = torch.ones_like(big_o, dtype=torch.bool)
+    untouched[:130, 8:208] = False
+    untouched[130:, 512:584] = False
+    assert bool((big_o[untouched] == -7.0).all())  # views: nothing outside a group's own columns is written
+    with pytest.raises(_lib.HelionB200Error):
+        hb.grouped_gemm_direct([big_a[:8, :12]], [group_b[0][:8, :12]], [big_o[:8, :8]])  # K % 8 != 0

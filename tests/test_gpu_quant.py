@@ -360,3 +360,66 @@ def test_against_outputs_of_the_reference_kernels(golden):
     rep = C.rms_quant_report(xr, w, 1e-6, q, s)
     print("rms against the reference kernel's output:", rep)
     assert rep["rows_not_explained_by_2ulp_of_rms"] == 0
+
+
+# ------------------------------------------------------------------ fused NVFP4 producers
+def _unswizzle_bytes(s, rows, cols):
+    return O.unswizzle_scales(s.cpu(), rows, cols).view(torch.uint8)
+
+
+@pytest.mark.parametrize("t,h", [(3, 256), (130, 2048), (64, 4096), (17, 7168), (4, 16384)])
+def test_rms_norm_nvfp4_quant_against_the_oracle(t, h):
+    """RMSNorm -> per-token NVFP4 in one kernel against the oracle's two steps (the normalisation of
+    rms_norm_dynamic_per_token_quant, then the NVFP4 quantiser).  A row must match bit for bit, or match with its
+    fp32 rms moved by at most two units in the last place (summation order)."""
+    g = torch.Generator().manual_seed(t + h)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)
+    w = (torch.rand(h, generator=g) + 0.5).to(torch.bfloat16)
+    codes, scales, gs = hb.rms_norm_nvfp4_quant(x.to(DEV), w.to(DEV), 1e-6)
+    torch.cuda.synchronize()
+    codes, sc, gs = codes.cpu(), _unswizzle_bytes(scales, t, h // 16), gs.cpu()
+    left = torch.ones(t, dtype=torch.bool)
+    for nudge in (0, -1, 1, -2, 2):
+        rms = O.rms_norm_row_rms(x, 1e-6)
+        rms = (rms.view(torch.int32) + nudge).view(torch.float32)
+        normed = (x.float() * rms).to(torch.bfloat16) * w[None, :]
+        oc, osc, og = O.nvfp4_quantize(normed, per_token=True)
+        ok = (codes == oc).all(dim=1) & (sc == _unswizzle_bytes(osc, t, h // 16)).all(dim=1) & (gs == og)
+        left &= ~ok
+        if not left.any():
+            break
+    assert not left.any(), f"{int(left.sum())} of {t} rows differ beyond a 2-ulp change of rms"
+
+
+@pytest.mark.parametrize("t,d", [(5, 256), (200, 1536), (33, 4096)])
+def test_silu_and_mul_nvfp4_quant_against_the_oracle(t, d):
+    """SiLU-mul -> per-token NVFP4 in one kernel: y is pinned bit for bit to the reference function evaluated by
+    torch on this device (exp() differs from the CPU's in the last place), the quantiser to the oracle's."""
+    g = torch.Generator().manual_seed(t + d)
+    x = torch.randn(t, 2 * d, generator=g).to(torch.bfloat16).to(DEV)
+    codes, scales, gs = hb.silu_and_mul_nvfp4_quant(x)
+    xf = x.float()
+    y = (xf[:, :d] / (1.0 + torch.exp(-xf[:, :d])) * xf[:, d:]).to(torch.bfloat16)  # on the device
+    oc, osc, og = O.nvfp4_quantize(y.cpu(), per_token=True)
+    assert torch.equal(codes.cpu(), oc) and torch.equal(gs.cpu(), og)
+    assert torch.equal(_unswizzle_bytes(scales, t, d // 16), _unswizzle_bytes(osc, t, d // 16))
+    # and it is what the separate quantiser makes of the same y
+    c2, s2, g2 = hb.nvfp4_quantize(y)
+    assert torch.equal(codes, c2) and torch.equal(gs, g2) and torch.equal(scales.view(torch.uint8), s2.view(torch.uint8))
+
+
+def test_fused_nvfp4_producers_feed_the_gemv():
+    """The producers' outputs are the activation operand of the NVFP4 GEMV: RMSNorm -> NVFP4 -> W4A4 GEMV equals
+    the oracle GEMV on the oracle-quantised normalised row."""
+    g = torch.Generator().manual_seed(7)
+    n, k = 512, 2048
+    x = torch.randn(1, k, generator=g).to(torch.bfloat16)
+    w_norm = (torch.rand(k, generator=g) + 0.5).to(torch.bfloat16)
+    wp, ws, wg = O.nvfp4_quantize(torch.randn(n, k, generator=g) * 0.02)
+    codes, scales, gs = hb.rms_norm_nvfp4_quant(x.to(DEV), w_norm.to(DEV), 1e-6)
+    alpha = float(wg) * float(gs[0])
+    y = hb.nvfp4_gemv_fp4in(wp.to(DEV), codes.reshape(-1), ws.to(DEV), scales, alpha)
+    ref = O.nvfp4_gemv_fp4in(wp, codes.reshape(-1).cpu(), ws, scales.cpu(), alpha)
+    yc, rc = y.float().cpu(), ref.float()
+    floor = rc.pow(2).mean().sqrt()
+    assert float(((yc - rc).abs() / torch.maximum(rc.abs(), floor)).max()) <= 1e-2
