@@ -1111,6 +1111,69 @@ def sub_scaled_mm(args, dev, timer) -> dict:
     return hbm_record(ms, med, nbytes, tokens=m, shapes=len(SCALED_MM_KN), library_us=lms * 1e3, library_median_us=lmed * 1e3)
 
 
+# (groups, expected rows per group, N, K) of the reference's bf16 grouped-GEMM manifest
+# (benchmarks/cute/deepgemm_selected_path.py:62-71); the real group sizes are expected * U(0.7, 1.3) from
+# random.Random(0), aligned to 128 rows, as official_actual_ms / make_case (:104-113, 209-238) draw them
+GROUPED_F16_SHAPES = [(4, 8192, 6144, 7168), (4, 8192, 7168, 3072), (4, 8192, 4096, 4096), (4, 8192, 4096, 2048),
+                      (8, 4096, 6144, 7168), (8, 4096, 7168, 3072), (8, 4096, 4096, 4096), (8, 4096, 4096, 2048)]
+# (M, N, K) per group of the direct-mode cases (benchmarks/cute/compare_grouped_gemm_backends.py:102-116)
+GROUPED_DIRECT_CASES = {"default_small_parity": ((128, 128, 128), (512, 128, 128), (128, 256, 128)),
+                        "doc_original": ((8192, 1280, 32), (16, 384, 1536), (640, 1280, 16), (640, 160, 16)),
+                        "doc_no_mn_tail": ((8192, 1280, 32), (128, 384, 1536), (640, 1280, 16), (640, 128, 16))}
+
+
+def sub_grouped_f16(args, dev, timer) -> dict:
+    """The bf16 / fp16 grouped GEMM on the reference's manifests: the worklist form on its eight large shapes and
+    the direct (heterogeneous) form on three of its small cases; cuBLAS, one matmul per group, under the same
+    protocol beside each."""
+    import random
+
+    import helion_b200 as hb
+
+    peaks = measured_peaks()
+    rng = random.Random(0)
+    out = {"worklist": {}, "direct": {}}
+    gen = torch.Generator(device=dev).manual_seed(8)
+    for groups, expect, n, k in GROUPED_F16_SHAPES:
+        actual = [int(expect * rng.uniform(0.7, 1.3)) for _ in range(groups)]
+        aligned = [(m + 127) // 128 * 128 for m in actual]
+        total = sum(aligned)
+        a = torch.randn(total, k, device=dev, dtype=torch.bfloat16, generator=gen)
+        b = torch.randn(groups, n, k, device=dev, dtype=torch.bfloat16, generator=gen)
+        rows, start = [], 0
+        for grp, (m, am) in enumerate(zip(actual, aligned)):
+            a[start + m : start + am] = 0
+            rows.append((grp, start, m, am))
+            start += am
+        wl = torch.tensor(rows, dtype=torch.int32, device=dev)
+        y = hb.grouped_gemm_deepgemm(a, b, wl)
+        grp, s0, m, _ = rows[-1]
+        parity = rel_err(y[s0 : s0 + 256], (a[s0 : s0 + 256].float() @ b[grp].float().t()))
+
+        def library():
+            return [a[s0_ : s0_ + am_] @ b[g_].t() for g_, s0_, _, am_ in rows]
+
+        ms, med = timer.run2(graphed(lambda: hb.grouped_gemm_deepgemm(a, b, wl))[0], 5, 3)
+        lms, _ = timer.run2(graphed(library)[0], 5, 3)
+        flops = 2 * sum(actual) * n * k
+        tf = flops / (ms * 1e-3) / 1e12
+        out["worklist"][f"{groups}x{expect}x{n}x{k}"] = {
+            "us": ms * 1e3, "median_us": med * 1e3, "TFLOPs": tf, "frac_of_measured_bf16": tf / peaks["bf16_tflops"],
+            "library_us": lms * 1e3, "parity_max_rel_err": parity}
+        del a, b, y
+    for name, problems in GROUPED_DIRECT_CASES.items():
+        ga = [torch.randn(m, k, device=dev, dtype=torch.float16, generator=gen) for m, _, k in problems]
+        gb = [torch.randn(nn, k, device=dev, dtype=torch.float16, generator=gen) for _, nn, k in problems]
+        go = [torch.empty(m, nn, device=dev, dtype=torch.float16) for m, nn, _ in problems]
+        hb.grouped_gemm_direct(ga, gb, go)
+        parity = max(rel_err(o, a_.float() @ b_.float().t()) for a_, b_, o in zip(ga, gb, go))
+        ms, med = timer.run2(graphed(lambda: hb.grouped_gemm_direct(ga, gb, go))[0], 20, 3)
+        lms, _ = timer.run2(graphed(lambda: [torch.matmul(a_, b_.t(), out=o) for a_, b_, o in zip(ga, gb, go)])[0], 20, 3)
+        out["direct"][name] = {"us": ms * 1e3, "median_us": med * 1e3, "library_us": lms * 1e3, "parity_max_rel_err": parity,
+                               "TFLOPs": 2 * sum(m * nn * k for m, nn, k in problems) / (ms * 1e-3) / 1e12}
+    return out
+
+
 def sub_tp_decode_layer(args, dev, rank, world, timer) -> dict:
     """Config 4 column-parallel over the ranks (fused peer-store gather), 1 and 8 rows."""
     import helion_b200 as hb
@@ -1215,7 +1278,8 @@ def wl_all(args, dev, rank, world, timer):
     if world == 1:
         for name, fn in (("gemv_config0_8192x4096", sub_gemv_config0), ("gemv_decode_sweep_70b_layer", sub_gemv_decode_sweep),
                          ("gemv_reference_published_shapes", sub_gemv_published_shapes), ("quant_producers_16384_tokens", sub_quant),
-                         ("moe_8192_tokens_128_experts_top8", sub_moe), ("scaled_mm_decode_shapes", sub_scaled_mm)):
+                         ("moe_8192_tokens_128_experts_top8", sub_moe), ("scaled_mm_decode_shapes", sub_scaled_mm),
+                         ("grouped_gemm_bf16_manifests", sub_grouped_f16)):
             subs[name] = guarded(fn, args, dev, timer)
             torch.cuda.empty_cache()
         for name, cpu in (("gemv_decode_sweep_70b_layer", "gemv"), ("quant_producers_16384_tokens", "quant"),

@@ -688,10 +688,15 @@ def silu_and_mul_per_block_quant(
     assert input.stride()[-1] == 1
     assert out.stride()[-1] == 1
     if input.dtype is not torch.bfloat16:
-        raise TypeError(f"input must be torch.bfloat16, got {input.dtype}")
-    if not scales.is_contiguous():
-        raise ValueError("scales must be contiguous")
-    _silu_mul_quant_op(out, input, scales, group_size, scale_ub)
+        raise TypeError(f"input must be torch.bfloat16, got {input.dtype}")  # (the reference also takes fp16 / fp32)
+    if scales.is_contiguous():
+        _silu_mul_quant_op(out, input, scales, group_size, scale_ub)
+    else:
+        # a strided or transposed scale view (the reference writes scales by index, so any view works there):
+        # the kernel writes a contiguous buffer, which is then copied into the view
+        tmp = torch.empty(scales.shape, dtype=scales.dtype, device=scales.device)
+        _silu_mul_quant_op(out, input, tmp, group_size, scale_ub)
+        scales.copy_(tmp)
 
 
 def rms_norm_dynamic_per_token_quant(

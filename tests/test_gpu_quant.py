@@ -423,3 +423,14 @@ def test_fused_nvfp4_producers_feed_the_gemv():
     yc, rc = y.float().cpu(), ref.float()
     floor = rc.pow(2).mean().sqrt()
     assert float(((yc - rc).abs() / torch.maximum(rc.abs(), floor)).max()) <= 1e-2
+
+
+def test_silu_scales_may_be_a_transposed_view():
+    """The reference writes scales by index, so a transposed (column-major) scale tensor works there."""
+    x = torch.randn(24, 2 * 512, generator=torch.Generator().manual_seed(13)).to(torch.bfloat16).to(DEV)
+    q = torch.empty(24, 512, dtype=FP8, device=DEV)
+    s_t = torch.empty(4, 24, device=DEV).t()  # [24, 4] with strides (1, 24)
+    assert not s_t.is_contiguous()
+    hb.silu_and_mul_per_block_quant(q, x, s_t, 128, None, True)
+    qd, sd = O.silu_and_mul_per_block_quant(x, 128)
+    assert count_diff(q, qd) == 0 and torch.equal(s_t, sd)
