@@ -60,6 +60,8 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_bf16in_tp": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P],
     "hb200_nvfp4_scaled_matmul_tp": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_float, c_int, _P],
     "hb200_peer_barrier": [_P, _I64, _I64, _P, _P],
+    "hb200_nvfp4_gemv_bf16in_rs": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_float, _P],
+    "hb200_tp_reduce_partials": [_P, _P, _I64, _I64, _I64, _I64, _P],
     "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],
     "hb200_moe_route_top_k": [_P, c_int, _I64, _I64, _I64, _P, _P, _P],
     "hb200_silu_mul_fp8": [_P, _P, _P, _I64, _I64, _I64, c_int, _P],

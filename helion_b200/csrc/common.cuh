@@ -26,12 +26,29 @@ __host__ __device__ inline int64_t swizzled_scale_offset(int64_t row, int64_t co
 
 // Where a kernel writes its bf16 result rows: one buffer, or the same place in the buffer of every rank of a
 // tensor-parallel group (peer-mapped pointers), at column col0 of rows of ld elements.
+// Reduce-scatter form (scatter_rows > 0, a rank that holds a K shard): the fp32 partial of output row r goes to rank
+// r / scatter_rows only, into that rank's fp32 buffer [world, batch_cap, scatter_rows] at [src_rank, b, r % scatter_rows]
+// (ptr[] then hold those buffers); the owner adds the partials up in rank order (hb200_tp_reduce_partials).
 struct OutSpec {
   __nv_bfloat16* ptr[8];
   int count;
   int64_t ld;
   int64_t col0;
+  int64_t scatter_rows;
+  int src_rank, batch_cap;
 };
+
+// One output value (row = output column index, b = activation row) as every GEMV kernel writes it.
+__device__ __forceinline__ void store_out(const OutSpec& o, int b, int64_t row, float value) {
+  if (o.scatter_rows > 0) {
+    const int64_t owner = row / o.scatter_rows;
+    float* dst = reinterpret_cast<float*>(o.ptr[owner]);
+    dst[(int64_t(o.src_rank) * o.batch_cap + b) * o.scatter_rows + (row - owner * o.scatter_rows)] = value;
+    return;
+  }
+  const __nv_bfloat16 v = __float2bfloat16_rn(value);
+  for (int p = 0; p < o.count; ++p) o.ptr[p][int64_t(b) * o.ld + o.col0 + row] = v;
+}
 
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();

@@ -219,10 +219,7 @@ __global__ void __launch_bounds__(kGemvThreads, U == 4 ? 4 : 2) nvfp4_gemv_kerne
   acc += __shfl_xor_sync(0xffffffffu, acc, 4);
 
   if (n_split == 1) {
-    if (j == 0 && row_ok) {
-      const __nv_bfloat16 v = __float2bfloat16_rn(acc * a.alpha);
-      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][a.out.col0 + row] = v;
-    }
+    if (j == 0 && row_ok) store_out(a.out, 0, row, acc * a.alpha);
     return;
   }
   // split-K: every CTA deposits its 32 partial sums in the leader's shared
@@ -239,10 +236,7 @@ __global__ void __launch_bounds__(kGemvThreads, U == 4 ? 4 : 2) nvfp4_gemv_kerne
     const int64_t r = tile * 128 + ((blockIdx.x & 3) << 3) + w2 + 32 * q2;
     float s = 0.f;
     for (int i = 0; i < n_split; ++i) s += part[i][threadIdx.x];
-    if (r < a.n) {
-      const __nv_bfloat16 v = __float2bfloat16_rn(s * a.alpha);
-      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][a.out.col0 + r] = v;
-    }
+    if (r < a.n) store_out(a.out, 0, r, s * a.alpha);
   }
 }
 

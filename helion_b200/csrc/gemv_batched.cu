@@ -204,8 +204,7 @@ __global__ void __launch_bounds__(kThreads) nvfp4_gemv_batched_kernel(const Batc
       if (r >= a.n) continue;
       float s = 0.f;
       for (int i = 0; i < n_split; ++i) s += buf[size_t(i) * (NT * 8 * kRows) + e];
-      const __nv_bfloat16 v = __float2bfloat16_rn(s * a.alpha);
-      for (int p = 0; p < a.out.count; ++p) a.out.ptr[p][int64_t(b) * a.out.ld + a.out.col0 + r] = v;
+      store_out(a.out, b, r, s * a.alpha);
     }
   }
 }
@@ -341,5 +340,33 @@ extern "C" int hb200_nvfp4_gemv_bf16in_tp(const void* weight_packed, const void*
   o.ld = n_total;
   o.col0 = col0;
   return hb200::gemv_dispatch_all(weight_packed, x_bf16, weight_scale, o, n, k, batch, alpha, false,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+// Row-parallel form with a fused reduce-scatter: this rank holds the K shard [N, K_local] of the weight and the
+// matching columns of the activations, computes its fp32 partial of all N outputs and stores the partial of output
+// column c into the buffer of the rank that owns it (c / (n / world)), at [this rank, row, c % (n / world)] of that
+// rank's fp32 [world, batch, n / world] buffer (partial_ptrs[i] = rank i's buffer as mapped here).  After
+// hb200_peer_barrier every rank adds up the world partials of its own columns with hb200_tp_reduce_partials.  Peer
+// memory is only stored to.  The pattern of examples/distributed/matmul_reduce_scatter.py:36-120 (which exchanges
+// through loads of the peers' buffers instead).  n % world == 0; runs on the SIMT (one row) / warp-MMA kernels.
+extern "C" int hb200_nvfp4_gemv_bf16in_rs(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                                          void* const* partial_ptrs, int64_t world, int64_t rank, int64_t n,
+                                          int64_t k_local, int64_t batch, float alpha, void* stream) {
+  if (!partial_ptrs || world < 1 || world > 8 || rank < 0 || rank >= world) return HB200_ERR_INVALID_ARGUMENT;
+  const int rc = check_gemv_args(weight_packed, x_bf16, weight_scale, n, k_local, batch);
+  if (rc != HB200_OK) return rc;
+  if (n % world) return HB200_ERR_INVALID_ARGUMENT;
+  if (n == 0 || batch == 0) return HB200_OK;
+  hb200::OutSpec o{};
+  for (int i = 0; i < world; ++i) {
+    if (!partial_ptrs[i] || reinterpret_cast<uintptr_t>(partial_ptrs[i]) % 4) return HB200_ERR_INVALID_ARGUMENT;
+    o.ptr[i] = static_cast<__nv_bfloat16*>(partial_ptrs[i]);
+  }
+  o.count = int(world);
+  o.scatter_rows = n / world;
+  o.src_rank = int(rank);
+  o.batch_cap = int(batch);
+  return hb200::gemv_dispatch_all(weight_packed, x_bf16, weight_scale, o, n, k_local, batch, alpha, false,
                                   static_cast<cudaStream_t>(stream));
 }

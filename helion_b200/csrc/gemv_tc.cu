@@ -284,8 +284,7 @@ nvfp4_gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           float y = 0.f;
 #pragma unroll
           for (int t = 0; t < TERMS; ++t) y = fmaf(v[j + t], g.col_scale ? g.col_scale[c0 + j + t] : 1.f, y);
-          const __nv_bfloat16 o = __float2bfloat16_rn(y * g.alpha);
-          for (int p = 0; p < g.out.count; ++p) g.out.ptr[p][int64_t(b) * g.out.ld + g.out.col0 + row] = o;
+          store_out(g.out, b, row, y * g.alpha);
         }
       }
     };

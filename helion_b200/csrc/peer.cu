@@ -65,6 +65,18 @@ int peer_device_status(int reset) {
   return v;
 }
 
+// out[b, c] = bf16(sum over ranks, ascending, of partials[rank, b, c]) in fp32.
+__global__ void __launch_bounds__(256)
+tp_reduce_partials_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ out, int world, int64_t items,
+                          int64_t cols, int64_t ld_out) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += int64_t(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    for (int r = 0; r < world; ++r) s += partials[int64_t(r) * items + i];
+    const int64_t b = i / cols;
+    out[b * ld_out + (i - b * cols)] = __float2bfloat16_rn(s);
+  }
+}
+
 int peer_set_wait_budget(long long cycles) {
   return cudaMemcpyToSymbol(g_peer_wait_cycles, &cycles, sizeof(cycles)) == cudaSuccess ? HB200_OK : HB200_ERR_CUDA;
 }
@@ -84,5 +96,21 @@ extern "C" int hb200_peer_barrier(void* const* flag_ptrs, int64_t world, int64_t
   a.rank = int(rank);
   a.world = int(world);
   hb200::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return hb200::launch_status();
+}
+
+// Second half of the fused reduce-scatter (after hb200_nvfp4_gemv_bf16in_rs and hb200_peer_barrier): adds the `world`
+// fp32 partials [world, batch, cols] that the ranks stored into this rank's buffer, in rank order, and writes
+// bf16 out[batch, cols] (row pitch ld_out elements).  The sum order is fixed, so results do not depend on timing.
+extern "C" int hb200_tp_reduce_partials(const void* partials_f32, void* out_bf16, int64_t world, int64_t batch,
+                                        int64_t cols, int64_t ld_out, void* stream) {
+  if (!partials_f32 || !out_bf16 || world < 1 || world > 8 || batch < 0 || cols < 0 || ld_out < cols)
+    return HB200_ERR_INVALID_ARGUMENT;
+  const int64_t items = batch * cols;
+  if (items == 0) return HB200_OK;
+  const int64_t need = (items + 255) / 256;
+  const int grid = int(need < 1184 ? need : 1184);
+  hb200::tp_reduce_partials_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(partials_f32), static_cast<__nv_bfloat16*>(out_bf16), int(world), items, cols, ld_out);
   return hb200::launch_status();
 }

@@ -48,6 +48,22 @@ def shard_weight_rows(packed: Tensor, scales: Tensor, world: int, rank: int) -> 
     return packed[lo:hi], flat[(lo // 128) * col_tiles * 512 : (hi // 128) * col_tiles * 512]
 
 
+def shard_weight_k(packed: Tensor, scales: Tensor, world: int, rank: int) -> tuple[Tensor, Tensor]:
+    """Slice a K-major NVFP4 weight ``[N, K/2]`` and its swizzled scales to the K range of ``rank`` (row parallelism:
+    ``K / world`` must be a multiple of 64 so that whole scale column tiles move).  The scale buffer is ordered by
+    (row tile, column tile), so a K range is one contiguous run of 512-byte tiles inside every row tile."""
+    n, kb = packed.shape
+    k = 2 * kb
+    if k % world or (k // world) % 64:
+        raise ValueError(f"K ({k}) must split into {world} shards that are multiples of 64")
+    k_local = k // world
+    col_tiles, local_tiles = -(-(k // 16) // 4), k_local // 64
+    row_tiles = -(-n // 128)
+    tiles = scales.reshape(-1).view(torch.uint8).reshape(row_tiles, col_tiles, 512)
+    part = tiles[:, rank * local_tiles : (rank + 1) * local_tiles].reshape(-1)
+    return packed[:, rank * (k_local // 2) : (rank + 1) * (k_local // 2)].contiguous(), part.contiguous().view(scales.dtype)
+
+
 def all_gather_columns(y_local: Tensor, group=None) -> Tensor:
     """``[M, N/g]`` per rank -> ``[M, N]`` on every rank (rank-major column blocks)."""
     world = dist.get_world_size(group)
@@ -195,6 +211,44 @@ class TensorParallel:
         if barrier:
             self.barrier()
         return buf[:m]
+
+    def scatter_buffers(self, rows: int, n_total: int, buffers: int = 2) -> GatheredOutput:
+        """Ring of fp32 ``[world, rows, n_total / world]`` partial-sum buffers for :meth:`gemv_row_parallel`."""
+        if n_total % self.world:
+            raise ValueError(f"{n_total} output columns do not split evenly over {self.world} ranks")
+        locals_, arrays = [], []
+        for _ in range(buffers):
+            t, arr = self._symmetric(self.world * rows * (n_total // self.world), torch.float32)
+            locals_.append(t.view(self.world, rows, n_total // self.world))
+            arrays.append(arr)
+        self._sync_all()
+        return GatheredOutput(locals_, arrays)
+
+    def gemv_row_parallel(self, weight_kshard: Tensor, scale_kshard: Tensor, x_kshard: Tensor, partials: GatheredOutput,
+                          alpha: float = 1.0) -> Tensor:
+        """Row-parallel projection with a fused reduce-scatter: this rank holds the weight's K shard ``[N, K/world/2]``
+        (see :func:`shard_weight_k`) and ``x_kshard [M, K/world]`` (1 <= M <= 32); every rank ends up with its own
+        ``[M, N/world]`` column slice of ``x @ W.T`` (bf16): partial sums go straight from the kernel into the owning
+        rank's buffer, a barrier kernel, then the owner adds them in rank order."""
+        from . import _lib
+
+        m, k_local = x_kshard.shape
+        n = weight_kshard.shape[0]
+        buf, ptrs = partials.next()
+        if buf.shape != (self.world, m, n // self.world) or buf.dtype is not torch.float32:
+            raise ValueError("partial-sum ring does not match [world, M, N / world] fp32")
+        if weight_kshard.shape[1] * 2 != k_local:
+            raise ValueError("weight shard and activation shard disagree on K")
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            _lib.call("hb200_nvfp4_gemv_bf16in_rs", weight_kshard.data_ptr(), x_kshard.data_ptr(), scale_kshard.data_ptr(),
+                      ptrs, self.world, self.rank, n, k_local, m, float(alpha), stream)
+        self.barrier()
+        out = torch.empty(m, n // self.world, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.call("hb200_tp_reduce_partials", buf.data_ptr(), out.data_ptr(), self.world, m, n // self.world,
+                      out.stride(0), stream)
+        return out
 
     def matmul(self, a_packed: Tensor, scale_a: Tensor, b_local: Tensor, scale_b_local: Tensor, out: GatheredOutput,
                alpha: float = 1.0, barrier: bool = True) -> Tensor:

@@ -385,6 +385,18 @@ int hb200_nvfp4_gemv_bf16in_tp(const void* weight_packed, const void* x_bf16, co
                                void* const* out_ptrs, int64_t world, int64_t n, int64_t k, int64_t batch,
                                int64_t n_total, int64_t col0, float alpha, void* stream);
 
+/* Row-parallel GEMV / skinny GEMM with a fused reduce-scatter (a K-sharded projection such as `down`): this rank
+ * holds weight columns [N, K_local] and the matching activation columns, computes its fp32 partial of all N
+ * outputs and stores the partial of output column c into the fp32 [world, batch, N / world] buffer of the rank
+ * that owns c, at [this rank, row, c % (N / world)].  After hb200_peer_barrier, hb200_tp_reduce_partials adds the
+ * partials of this rank's columns in rank order.  The pattern of examples/distributed/matmul_reduce_scatter.py:36-120,
+ * with stores to the owners instead of loads from the peers.  N % world == 0. */
+int hb200_nvfp4_gemv_bf16in_rs(const void* weight_packed, const void* x_bf16, const void* weight_scale,
+                               void* const* partial_ptrs, int64_t world, int64_t rank, int64_t n, int64_t k_local,
+                               int64_t batch, float alpha, void* stream);
+int hb200_tp_reduce_partials(const void* partials_f32, void* out_bf16, int64_t world, int64_t batch, int64_t cols,
+                             int64_t ld_out, void* stream);
+
 /* out_dtype 0 = bf16, 1 = fp16.  Needs m >= 256, n >= 256, K % 32 == 0, n_total % 8 == 0, col0 % 8 == 0
  * (HB200_ERR_UNSUPPORTED otherwise: compute locally and gather with a collective). */
 int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, const void* scale_a,

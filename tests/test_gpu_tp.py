@@ -111,6 +111,53 @@ def test_matmul_slices_land_in_every_buffer(m, n, k, world):
         assert torch.equal(buf, want)
 
 
+@pytest.mark.parametrize("batch,world", [(1, 2), (4, 4), (17, 2), (1, 8)])
+def test_row_parallel_partials_reduce_to_the_full_product(batch, world):
+    """K-sharded projection with the fused reduce-scatter, ranks emulated one after the other on one GPU: every
+    rank's kernel stores its fp32 partials into the owners' buffers, then each owner adds them in rank order."""
+    n, k = 1024, 4096
+    codes, scales = random_weight(n, k, 17 + batch)
+    x = torch.randn(batch, k, generator=torch.Generator().manual_seed(batch)).to(torch.bfloat16).to(DEV)
+    full = hb.nvfp4_gemv_bf16in_batched(codes, x, scales, 0.5, path="simt" if batch == 1 else "mma")
+    cols = n // world
+    bufs = [torch.full((world, batch, cols), float("nan"), dtype=torch.float32, device=DEV) for _ in range(world)]
+    ptrs = ptr_array(bufs)
+    stream = torch.cuda.current_stream().cuda_stream
+    k_local = k // world
+    for rank in range(world):
+        w_r, s_r = D.shard_weight_k(codes, scales, world, rank)
+        x_r = x[:, rank * k_local : (rank + 1) * k_local].contiguous()
+        _lib.call("hb200_nvfp4_gemv_bf16in_rs", w_r.data_ptr(), x_r.data_ptr(), s_r.data_ptr(), ptrs, world, rank, n,
+                  k_local, batch, 0.5, stream)
+    assert device_status_ok()
+    for rank in range(world):
+        assert torch.isfinite(bufs[rank]).all()  # every slot was written by its source rank
+        out = torch.empty(batch, cols, dtype=torch.bfloat16, device=DEV)
+        _lib.call("hb200_tp_reduce_partials", bufs[rank].data_ptr(), out.data_ptr(), world, batch, cols, cols, stream)
+        want = full[:, rank * cols : (rank + 1) * cols]
+        # the K range is summed in `world` pieces instead of one: the last bf16 place may move
+        torch.testing.assert_close(out.float(), want.float(), rtol=1e-2, atol=1e-2 * float(full.float().abs().mean()))
+        # and the owner's sum is exactly the fp32 sum of the partials in rank order
+        acc = torch.zeros(batch, cols, device=DEV)
+        for r in range(world):
+            acc += bufs[rank][r]
+        assert torch.equal(out, acc.to(torch.bfloat16))
+
+
+def test_shard_weight_k_moves_whole_scale_tiles():
+    n, k = 256, 512
+    g = torch.Generator().manual_seed(2)
+    packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, generator=g)
+    logical = (torch.rand(n, k // 16, generator=g) + 0.5).to(torch.float8_e4m3fn)
+    scales = O.swizzle_scales(logical)
+    for r in range(4):
+        p, s = D.shard_weight_k(packed, scales, 4, r)
+        assert torch.equal(p, packed[:, r * 64 : (r + 1) * 64])
+        assert torch.equal(s.view(torch.uint8), O.swizzle_scales(logical[:, r * 8 : (r + 1) * 8]).view(torch.uint8))
+    with pytest.raises(ValueError, match="multiples of 64"):
+        D.shard_weight_k(packed, scales, 16, 0)
+
+
 def test_matmul_tp_rejects_what_the_pair_kernel_cannot_take():
     a = torch.zeros(128, 64, dtype=torch.uint8, device=DEV)
     s = torch.zeros(128 * 8, dtype=torch.uint8, device=DEV)
@@ -167,6 +214,15 @@ def _two_rank_worker(rank: int, world: int, port: int, result):
             ok &= bool(torch.equal(yv, D.column_parallel_gemv(w_r, s_r, x, 1.0)))
             ym = tp.matmul(a, sa, w_r, s_r, ring_m, 1.0)
             ok &= bool(torch.equal(ym, D.column_parallel_matmul(a, sa, w_r, s_r)))
+        # row-parallel projection with the fused reduce-scatter against the one-GPU product
+        full = hb.nvfp4_gemv_bf16in_batched(codes.to(dev), x, scales.to(dev), 1.0, path="mma")
+        w_k, s_k = D.shard_weight_k(codes.to(dev), scales.to(dev), world, rank)
+        x_k = x[:, rank * (k // world) : (rank + 1) * (k // world)].contiguous()
+        ring_p = tp.scatter_buffers(8, n)
+        for _ in range(4):
+            yk = tp.gemv_row_parallel(w_k, s_k, x_k, ring_p, 1.0)
+            want = full[:, rank * (n // world) : (rank + 1) * (n // world)]
+            ok &= bool(torch.allclose(yk.float(), want.float(), rtol=1e-2, atol=1e-2 * float(full.float().abs().mean())))
         torch.cuda.synchronize()
         ok &= _lib.load().hb200_device_status(1) == 0
         result[rank] = int(ok)
