@@ -77,6 +77,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_selftest_bounded_wait": [_P],
     "hb200_build_worklist_tiles": [_P, _I64, _I64, _P, _I64, _P],
     "hb200_build_split_tiles": [_P, c_int, _I64, _I64, _I64, _P, _I64, _P],
+    "hb200_nvfp4_quantize_scatter": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P],
     "hb200_rms_norm_nvfp4_quant": [_P, _P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
     "hb200_grouped_gemm_f16_direct": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, c_int, _P],
     "hb200_ep_buffer_bytes": [_I64, _I64, _I64, _I64, _I64],

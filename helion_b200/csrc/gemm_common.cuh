@@ -18,10 +18,30 @@ constexpr int kAtomsPerStage = 4;
 template <typename OutT>
 __device__ __forceinline__ void store_row_chunk(OutT* dst, const uint32_t (&r)[32], float alpha, int valid, bool vec_ok);
 
+// 32 bytes in one instruction (sm_100 has 256-bit global stores): a whole sector per lane, half the store
+// instructions of 16-byte stores.  dst must be 32-byte aligned.
+__device__ __forceinline__ void stg_v8(void* dst, const uint32_t (&p)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(p[0]), "r"(p[1]), "r"(p[2]),
+               "r"(p[3]), "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7])
+               : "memory");
+}
+
 template <>
 __device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], float alpha,
                                                                int valid, bool vec_ok) {
-  if (valid >= 32 && vec_ok) {
+  if (valid >= 32 && vec_ok && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      uint32_t p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 16 + 2 * j]) * alpha,
+                                                       __uint_as_float(r[v * 16 + 2 * j + 1]) * alpha);
+        p[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      stg_v8(dst + v * 16, p);
+    }
+  } else if (valid >= 32 && vec_ok) {
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       uint32_t p[4];
@@ -43,7 +63,17 @@ __device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* ds
 template <>
 __device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const uint32_t (&r)[32], float alpha, int valid,
                                                         bool vec_ok) {
-  if (valid >= 32 && vec_ok) {
+  if (valid >= 32 && vec_ok && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      uint32_t p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        p[j] = h2_as_u32(__floats2half2_rn(__uint_as_float(r[v * 16 + 2 * j]) * alpha,
+                                           __uint_as_float(r[v * 16 + 2 * j + 1]) * alpha));
+      stg_v8(dst + v * 16, p);
+    }
+  } else if (valid >= 32 && vec_ok) {
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       uint32_t p[4];

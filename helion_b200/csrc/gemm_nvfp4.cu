@@ -343,10 +343,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                          fabsf(__uint_as_float(packed[j] & 0xffff0000u))));
               }
               __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + int64_t(row) * g.ldc + n_blk * 128 + cgroup * 32;
+              if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {  // 32 bytes per store: whole sectors
+                const uint32_t lo[8] = {packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]};
+                const uint32_t hi[8] = {packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14], packed[15]};
+                stg_v8(dst, lo);
+                stg_v8(dst + 16, hi);
+              } else {
 #pragma unroll
-              for (int v = 0; v < 4; ++v)
-                *reinterpret_cast<uint4*>(dst + v * 8) =
-                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                for (int v = 0; v < 4; ++v)
+                  *reinterpret_cast<uint4*>(dst + v * 8) =
+                      make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+              }
               atomicMax(reinterpret_cast<int*>(g.row_amax + row), __float_as_int(amax));
             }
             continue;

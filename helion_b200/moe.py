@@ -212,20 +212,27 @@ def _quantize_rows(x: Tensor, k: int, sched: MoeSchedule, src_div: int, item_sca
     return codes, scales, gscale
 
 
-def _quantize_and_gather(x: Tensor, sched: MoeSchedule, top_k: int):
-    """Quantise every token row once (per-token global scale), then copy the packed rows into the
-    expert-sorted padded layout -- an eighth of the arithmetic of quantising every (token, slot) pair."""
+def _quantize_and_gather(x: Tensor, sched: MoeSchedule, top_k: int, fused: bool = True):
+    """Quantise every token row once (per-token global scale) and place its packed row at the rows of all its
+    (token, slot) pairs in the expert-sorted padded layout -- an eighth of the arithmetic of quantising every pair.
+    ``fused``: one kernel that writes the top-k copies itself (K % 64 == 0, K <= 4096); otherwise the quantiser
+    followed by a row-gather kernel (same bytes)."""
     from .ops import nvfp4_quantize
 
     t, k = x.shape
     if k % 32:
         return _quantize_rows(x, k, sched, top_k, None, False, gather=True)
-    codes_t, scales_t, g_t = nvfp4_quantize(x)
     rows = sched.max_tiles * 128
     dev = x.device
     codes = torch.empty(rows, k // 2, dtype=torch.uint8, device=dev)
     scales = torch.empty(swizzled_scale_numel(rows, k // 16), dtype=torch.uint8, device=dev)
     gscale = torch.zeros(rows, dtype=torch.float32, device=dev)
+    if fused and k % 64 == 0 and k <= 4096 and top_k <= 32 and x.stride(0) % 8 == 0:
+        with torch.cuda.device(dev):
+            _lib.call("hb200_nvfp4_quantize_scatter", x.data_ptr(), codes.data_ptr(), scales.data_ptr(), gscale.data_ptr(),
+                      sched.row_of_pair.data_ptr(), t, top_k, k, x.stride(0), _stream())
+        return codes, scales, gscale
+    codes_t, scales_t, g_t = nvfp4_quantize(x)
     with torch.cuda.device(dev):
         _lib.call(
             "hb200_moe_gather_rows", codes_t.data_ptr(), scales_t.data_ptr(), g_t.data_ptr(), codes.data_ptr(),

@@ -112,6 +112,16 @@ int hb200_per_token_group_fp8_quant(const void* input, void* output_q, void* out
 int hb200_nvfp4_quantize(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
                          int64_t rows, int64_t k, int64_t ldx, int per_token, void* stream);
 
+/* Per-token NVFP4 quantisation with fan-out, the dispatch step of the NVFP4 MoE layer in one pass: token t of
+ * x [tokens, k] (bf16, row pitch ldx) is quantised once and its packed row, block scales and global scale are
+ * written to the rows dst_rows[t * fanout .. (t + 1) * fanout) of the expert-sorted padded layout (negative
+ * entries are skipped).  Same bytes as hb200_nvfp4_quantize + hb200_moe_gather_rows.  k % 64 == 0, k <= 4096,
+ * fanout <= 32.  No counterpart in the reference (its MoE example gathers bf16 rows inside the GEMM,
+ * examples/moe_matmul_ogs.py:58-66). */
+int hb200_nvfp4_quantize_scatter(const void* x_bf16, void* codes, void* scales_swizzled, float* global_scale,
+                                 const int32_t* dst_rows, int64_t tokens, int64_t fanout, int64_t k, int64_t ldx,
+                                 void* stream);
+
 /* RMSNorm fused with per-token NVFP4 quantisation (the NVFP4 form of rms_norm_dynamic_per_token_quant, whose
  * normalisation arithmetic it keeps: pretuned_kernels/rms_norm_dynamic_per_token_quant/
  * rms_norm_dynamic_per_token_quant.py:131-150): x [rows, k] bf16 (row pitch ldx), weight [k] bf16 -> codes

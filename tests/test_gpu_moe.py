@@ -205,3 +205,24 @@ def test_fused_routing_breaks_ties_by_expert_index():
     w, e = M.route_top_k(logits, 4)
     assert e[0].tolist() == [0, 1, 2, 3] and e[1].tolist() == [40, 0, 1, 2]
     assert torch.allclose(w[0], torch.full((4,), 1 / 64, device=DEV))
+
+
+@pytest.mark.parametrize("t,h,e,k", [(300, 512, 16, 4), (1000, 4096, 32, 8), (77, 2048, 8, 2), (64, 256, 8, 1)])
+def test_fused_quantise_and_scatter_equals_quantiser_plus_gather(t, h, e, k):
+    """The one-pass dispatch (quantise a token once, write its row to all its pairs' rows) writes the same bytes as
+    the quantiser followed by the row gather, in every row a pair owns."""
+    g = torch.Generator().manual_seed(t + h)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16).to(DEV)
+    logits = torch.randn(t, e, generator=g).to(DEV)
+    _, experts = M.route_top_k(logits, k)
+    sched = M.build_schedule(experts, e)
+    c1, s1, g1 = M._quantize_and_gather(x, sched, k, fused=True)
+    c2, s2, g2 = M._quantize_and_gather(x, sched, k, fused=False)
+    torch.cuda.synchronize()
+    rows = sched.row_of_pair.long()
+    assert torch.equal(c1[rows], c2[rows]) and torch.equal(g1[rows], g2[rows])
+    cols = h // 16
+    u1 = C.swizzled_rows(s1.cpu(), rows.cpu(), cols)
+    u2 = C.swizzled_rows(s2.cpu(), rows.cpu(), cols)
+    assert torch.equal(u1, u2)
+    assert bool((g1[rows] > 0).all())
