@@ -8,6 +8,7 @@ every operator raises ``RuntimeError``.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p
 from ctypes import c_float
 from ctypes import c_int
@@ -16,7 +17,8 @@ from ctypes import c_void_p
 from pathlib import Path
 import threading
 
-LIB_PATH = Path(__file__).resolve().parent / "libhelion_b200.so"
+# HELION_B200_LIB names another build of the library (same ABI), e.g. one with different tuning constants
+LIB_PATH = Path(os.environ.get("HELION_B200_LIB") or Path(__file__).resolve().parent / "libhelion_b200.so")
 
 HB200_OK = 0
 HB200_ERR_INVALID_ARGUMENT = -1
@@ -56,6 +58,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_grouped_matmul_256": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, c_int, _P],
     "hb200_moe_sort_pairs": [_P, c_int, _I64, _I64, _P, _P, _P, _P],
     "hb200_nvfp4_grouped_matmul_silu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, _P],
+    "hb200_nvfp4_grouped_matmul_silu_256": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, c_float, _P],
     "hb200_nvfp4_quantize_rows_amax": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P],
     "hb200_nvfp4_gemv_bf16in_tp": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_float, _P],
     "hb200_nvfp4_scaled_matmul_tp": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_float, c_int, _P],

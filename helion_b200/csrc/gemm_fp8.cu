@@ -1,4 +1,5 @@
-// Row-wise scaled FP8 matrix multiply for sm_100a (tcgen05 kind::f8f6f4, fp32 accumulate):
+// Row-wise scaled FP8 matrix multiply for sm_100a (tcgen05 kind::f8f6f4, fp32 accumulate; for int8 operands
+// kind::i8 with an int32 accumulator that is converted to fp32 once, after the whole K range is summed):
 //   c[m, n] = cast(scale_a[m] * acc[m, n] * scale_b[n]) + bias[n],   acc = a[m, :] . b[:, n]
 // a [M, K] row-major, b [K, N] with unit stride along K (the weight stored [N, K]); scales per tensor or per
 // row / column; the bias is added after the cast, in the output type.  This is the operator of
@@ -76,6 +77,29 @@ __device__ __forceinline__ void mma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t
 __host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int format) {
   return (1u << 4) | (uint32_t(format) << 7) | (uint32_t(format) << 10) | (uint32_t(n >> 3) << 17) |
          (uint32_t(m >> 4) << 24);
+}
+
+// The integer form (int8 x int8 -> int32, pretuned_kernels/scaled_mm/scaled_mm.py:53): kind::i8, the accumulator
+// holds int32 (bits 4-5 = 2), operand format 1 = signed 8-bit; the same shapes, strides and K per instruction.
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Accumulator words travel as float registers whatever they hold (fp32, or the bits of an int32 in the integer
+// form): `wide` turns one into the fp32 value the scales multiply, `add_acc` adds two partial sums of a tile.
+__device__ __forceinline__ float wide(float v, bool is_int) { return is_int ? __int2float_rn(__float_as_int(v)) : v; }
+__device__ __forceinline__ float add_acc(float a, float b, bool is_int) {
+  return is_int ? __int_as_float(__float_as_int(a) + __float_as_int(b)) : a + b;
 }
 
 __device__ __forceinline__ void fp8_epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -229,7 +253,8 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       }
     }
   } else if (warp == 1) {
-    const uint32_t idesc = make_idesc_f8(128, g.cols, format);
+    const bool is_int = format == 2;
+    const uint32_t idesc = is_int ? make_idesc_i8(128, g.cols) : make_idesc_f8(128, g.cols, format);
     uint32_t it = 0, sc = 0;
     bool ok = true;
     for (int i = 0; i < work_count && ok; ++i, ++sc) {
@@ -252,7 +277,8 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             // 32 K-elements = 32 bytes further along the 128-byte swizzled row
             const uint64_t wdesc = make_smem_desc(w_addr + a * 32, 16, 1024, kSwizzle128B);
             const uint64_t xdesc = make_smem_desc(x_addr + a * 32, 16, 1024, kSwizzle128B);
-            mma_f8(tmem_d, wdesc, xdesc, idesc, (kb != kb0 || a != 0) ? 1u : 0u);
+            if (is_int) mma_i8(tmem_d, wdesc, xdesc, idesc, (kb != kb0 || a != 0) ? 1u : 0u);
+            else mma_f8(tmem_d, wdesc, xdesc, idesc, (kb != kb0 || a != 0) ? 1u : 0u);
           }
           tcgen05_commit(smem_u32(&empty_bar[s]));
         }
@@ -263,6 +289,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
   } else {
     const int quarter = warp & 3;
+    const bool is_int = format == 2;
     const int r_in = quarter * 32 + lane;  // weight row inside the tile = accumulator lane
     OutT* out = static_cast<OutT*>(g.out);
     const OutT* bias = static_cast<const OutT*>(g.bias);
@@ -299,7 +326,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           for (int j = 0; j < 16; ++j) {
             const int m_idx = m0 + c0 + j;
             const float sa = g.scale_a_per_row ? (m_idx < g.m ? __ldg(g.scale_a + m_idx) : 0.f) : sa_all;
-            OutT o = from_float<OutT>(sb * (sa * v[j]));
+            OutT o = from_float<OutT>(sb * (sa * wide(v[j], is_int)));
             if (bias) o = from_float<OutT>(as_float(o) + bias_n);
             turn[j * 32 + lane] = o;
           }
@@ -322,7 +349,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           const int m_idx = m0 + c0 + j;
           if (m_idx < g.m) {
             const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : sa_all;
-            OutT o = from_float<OutT>(sb * (sa * v[j]));
+            OutT o = from_float<OutT>(sb * (sa * wide(v[j], is_int)));
             if (bias) o = from_float<OutT>(as_float(o) + bias_n);
             out[int64_t(m_idx) * g.ldc + n_idx] = o;
           }
@@ -411,7 +438,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
 #pragma unroll
-              for (int j = 0; j < CW; ++j) v[j] += t[q][j];
+              for (int j = 0; j < CW; ++j) v[j] = add_acc(v[j], t[q][j], is_int);
             }
           }
 #pragma unroll
@@ -445,11 +472,11 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         for (int q = 0; q < CLUSTER; ++q) t[q] = mine[(q * per + i) * 128];
         float v = t[0];
 #pragma unroll
-        for (int q = 1; q < CLUSTER; ++q) v += t[q];  // rank order = ascending K: a fixed summation order
+        for (int q = 1; q < CLUSTER; ++q) v = add_acc(v, t[q], format == 2);  // rank order = ascending K: a fixed summation order
         const int m_idx = c_m0 + i * CLUSTER;
         if (m_idx < g.m) {
           const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : c_sa_all;
-          OutT o = from_float<OutT>(c_sb * (sa * v));
+          OutT o = from_float<OutT>(c_sb * (sa * wide(v, format == 2)));
           if (bias) o = from_float<OutT>(as_float(o) + c_bias);
           out[int64_t(m_idx) * g.ldc] = o;
         }
@@ -622,7 +649,7 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
   using namespace hb200;
   if (!a || !b || !c || !scale_a || !scale_b) return HB200_ERR_INVALID_ARGUMENT;
   if (m <= 0 || n <= 0 || k <= 0 || lda < k || ldb < k || ldc < n) return HB200_ERR_INVALID_ARGUMENT;
-  if (fp8_format != 0 && fp8_format != 1) return HB200_ERR_INVALID_ARGUMENT;
+  if (fp8_format < 0 || fp8_format > 2) return HB200_ERR_INVALID_ARGUMENT;
   if (out_dtype < 0 || out_dtype > 2) return HB200_ERR_INVALID_ARGUMENT;
   // TMA: 16-byte aligned bases and row pitches
   if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b) % 16 || (lda % 16) != 0 || (ldb % 16) != 0)

@@ -588,6 +588,33 @@ extern "C" int hb200_nvfp4_grouped_matmul_silu(const void* a_packed, const void*
   return dispatch_gemm<__nv_bfloat16>(a_packed, b_packed, g, int(groups), s);
 }
 
+// hb200_nvfp4_grouped_matmul_silu for a row layout whose groups are padded to multiples of 256 rows
+// (hb200_moe_build_schedule_256): 256 x 256 tiles on CTA pairs, the same epilogue, the same values bit for bit;
+// falls back to the 128-row kernel for shapes the pair kernel does not take.
+extern "C" int hb200_nvfp4_grouped_matmul_silu_256(const void* a_packed, const void* b_packed, const void* scale_a,
+                                                   const void* scale_b, void* y_out, float* row_amax,
+                                                   const int32_t* tile_info, int64_t max_m_tiles, int64_t n, int64_t k,
+                                                   int64_t groups, int64_t ldy, const float* row_scale,
+                                                   const float* group_alpha, float alpha, void* stream) {
+  using namespace hb200;
+  const bool pair_ok = a_packed && b_packed && scale_a && scale_b && y_out && row_amax && tile_info && max_m_tiles > 0 &&
+                       (max_m_tiles % 2) == 0 && n > 0 && (n % 256) == 0 && k > 0 && (k % 32) == 0 && groups > 0 &&
+                       ldy >= n / 2 && (ldy % 8) == 0 && max_m_tiles * 128 <= 0x7fffff00 && n * groups <= 0x7fffff00 &&
+                       k <= 0x7fffff00 && reinterpret_cast<uintptr_t>(a_packed) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(b_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(scale_a) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(scale_b) % 16 == 0 && reinterpret_cast<uintptr_t>(tile_info) % 8 == 0 &&
+                       reinterpret_cast<uintptr_t>(y_out) % 16 == 0;
+  if (pair_ok) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(row_amax, 0, size_t(max_m_tiles) * 128 * sizeof(float), s) != cudaSuccess) return HB200_ERR_CUDA;
+    const int rc = pair::launch_grouped_pair(a_packed, b_packed, scale_a, scale_b, y_out, tile_info, max_m_tiles, n, k,
+                                             groups, ldy, row_scale, group_alpha, alpha, 0, s, row_amax);
+    if (rc != HB200_ERR_UNSUPPORTED) return rc;
+  }
+  return hb200_nvfp4_grouped_matmul_silu(a_packed, b_packed, scale_a, scale_b, y_out, row_amax, tile_info, max_m_tiles,
+                                         n, k, groups, ldy, row_scale, group_alpha, alpha, stream);
+}
+
 // Reads (and optionally clears) the sticky device status set by kernels whose
 // bounded waits ran out.  Synchronises the device.
 namespace hb200 {

@@ -75,6 +75,10 @@ struct PairArgs {
   const int2* tile_info;
   const float* row_scale;    // optional fp32 factor per row of A
   const float* group_alpha;  // optional fp32 factor per group
+  // SiLU-mul epilogue (grouped bf16 only): the 256 columns of a tile are 128 gate columns followed by the 128 up
+  // columns of the same outputs; the kernel writes y = bf16(silu(gate) * up) [rows, n / 2] with leading dimension
+  // ldc and folds every row's max |y| into row_amax (fp32 bits, compared as integers).
+  float* row_amax;
 };
 
 struct PairTile {
@@ -102,7 +106,7 @@ __device__ __forceinline__ PairTile decode_pair_tile(const PairArgs& g, int tile
 
 // TP: the tensor-parallel form (every tile also goes to the peers).  It trades one stage of the operand ring
 // for output staging boxes twice as wide, so that a store over NVLink writes 128 contiguous bytes per row.
-template <typename OutT, bool TP>
+template <typename OutT, bool TP, bool SILU = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -288,14 +292,53 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       if (g.row_scale != nullptr && row < g.m) alpha *= g.row_scale[row];
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + cgroup * 64;
       uint32_t r[2][32];
-      tmem_ld_32x32b_x32(taddr, r[0]);
-      tmem_ld_32x32b_x32(taddr + 32, r[1]);
+      if constexpr (SILU) {
+        // 32 gate columns and the 32 up columns of the same outputs
+        const uint32_t tbase = tmem_base + (uint32_t(quarter * 32) << 16);
+        tmem_ld_32x32b_x32(tbase + cgroup * 32, r[0]);
+        tmem_ld_32x32b_x32(tbase + 128 + cgroup * 32, r[1]);
+      } else {
+        tmem_ld_32x32b_x32(taddr, r[0]);
+        tmem_ld_32x32b_x32(taddr + 32, r[1]);
+      }
       tmem_ld_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(free_bar);
       const int col = n_blk * kTileN + cgroup * 64;
-      if constexpr (sizeof(OutT) == 2 && TP) {
+      if constexpr (SILU) {
+        const int valid_rows = g.tile_info[2 * m_blk + int(rank)].y;  // of this CTA's 128 rows
+        if (quarter * 32 + lane < valid_rows) {
+          uint32_t packed[16];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float y[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              // gate and up rounded to bf16 first, as a bf16 activation pipeline holds them
+              const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[0][2 * j + h]) * alpha));
+              const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[1][2 * j + h]) * alpha));
+              y[h] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
+            }
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(y[0], y[1]);
+            packed[j] = *reinterpret_cast<const uint32_t*>(&pk);
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(packed[j] << 16)), fabsf(__uint_as_float(packed[j] & 0xffff0000u))));
+          }
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + int64_t(row) * g.ldc + n_blk * 128 + cgroup * 32;
+          if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {  // 32 bytes per store: whole sectors
+            const uint32_t lo[8] = {packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]};
+            const uint32_t hi[8] = {packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14], packed[15]};
+            stg_v8(dst, lo);
+            stg_v8(dst + 16, hi);
+          } else {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          }
+          atomicMax(reinterpret_cast<int*>(g.row_amax + row), __float_as_int(amax));
+        }
+      } else if constexpr (sizeof(OutT) == 2 && TP) {
         // The four warps of a lane quarter fill one box of 32 rows x 256 columns; its first warp then sends every
         // row, 512 contiguous bytes, to this rank and to every peer with one bulk copy per destination.
         uint8_t* qbox = stage_out + quarter * (32 * kRowPitchTp);
@@ -422,7 +465,7 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
     tout = ta;  // unused by the fp32 epilogue
   }
   PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(ceil_div64(m, 256)), int(ceil_div64(n, 256)), 0, {}, 0,
-             nullptr, nullptr, nullptr};
+             nullptr, nullptr, nullptr, nullptr};
   if (tp) {
     g.col0 = int(peers.col0);
     // the copies over NVLink are issued first, the local one last
@@ -461,9 +504,9 @@ inline int launch_gemm_pair(const void* a, const void* b, const void* sfa, const
 inline int launch_grouped_pair(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
                                const int32_t* tile_info, int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups,
                                int64_t ldc, const float* row_scale, const float* group_alpha, float alpha,
-                               int out_dtype, cudaStream_t stream) {
+                               int out_dtype, cudaStream_t stream, float* row_amax = nullptr) {
   if ((max_m_tiles % 2) != 0 || (n % 256) != 0 || (k % 32) != 0 || out_dtype == 2 || (ldc % 8) != 0 ||
-      reinterpret_cast<uintptr_t>(out) % 16)
+      reinterpret_cast<uintptr_t>(out) % 16 || (row_amax != nullptr && out_dtype != 0))
     return HB200_ERR_UNSUPPORTED;
   const int64_t m = max_m_tiles * 128;
   CUtensorMap ta, tb, tsa, tsb, tout;
@@ -471,16 +514,24 @@ inline int launch_grouped_pair(const void* a, const void* b, const void* sfa, co
   if (!make_operand_map(&ta, a, m, k / 2, 128) || !make_operand_map(&tb, b, n * groups, k / 2, 128)) return HB200_ERR_CUDA;
   if (!make_scale_map(&tsa, sfa, max_m_tiles * col_tiles) || !make_scale_map(&tsb, sfb, (n / 128) * groups * col_tiles))
     return HB200_ERR_CUDA;
-  if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) return HB200_ERR_CUDA;
+  if (row_amax != nullptr) {
+    tout = ta;  // the SiLU-mul epilogue stores rows directly
+  } else if (!make_output_map16(&tout, out, m, n, ldc, out_dtype == 0)) {
+    return HB200_ERR_CUDA;
+  }
   PairArgs g{out, ldc, int(m), int(n), int(k), alpha, int(max_m_tiles / 2), int(n / 256), 0, {}, 0,
-             reinterpret_cast<const int2*>(tile_info), row_scale, group_alpha};
+             reinterpret_cast<const int2*>(tile_info), row_scale, group_alpha, row_amax};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = g.m_tiles * g.n_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   if (pairs == 0) return HB200_OK;
   constexpr size_t smem = size_t(kStages2) * kStageBytes2 + kOutStageBytes + (3 * kStages2 + 2) * 8 + 16 + 1024;
-  if (out_dtype == 0) {
+  if (row_amax != nullptr) {
+    auto kernel = nvfp4_gemm_pair_kernel<__nv_bfloat16, false, true>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
+    kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);
+  } else if (out_dtype == 0) {
     auto kernel = nvfp4_gemm_pair_kernel<__nv_bfloat16, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
     kernel<<<2 * pairs, kThreads2, smem, stream>>>(ta, tb, tsa, tsb, tout, g);

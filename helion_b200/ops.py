@@ -349,7 +349,7 @@ def _scaled_mm_op(c: Tensor, a: Tensor, b_nk: Tensor, scale_a: Tensor, scale_b: 
             a.data_ptr(), b_nk.data_ptr(), c.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), _ptr(bias),
             m, n, k, a.stride(0), b_nk.stride(0), c.stride(0),
             int(scale_a.numel() > 1), int(scale_b.numel() > 1),
-            int(a.dtype is torch.float8_e5m2), _SCALED_MM_OUT[c.dtype],
+            2 if a.dtype is torch.int8 else int(a.dtype is torch.float8_e5m2), _SCALED_MM_OUT[c.dtype],
             _ptr(ws), ws.numel() if ws is not None else 0, _stream(),
         )
 
@@ -816,12 +816,13 @@ def silu_mul_fp8(input: Tensor, scale: Tensor) -> Tensor:  # noqa: A002
 def scaled_mm(
     c: Tensor, a: Tensor, b: Tensor, scale_a: Tensor, scale_b: Tensor, bias: Tensor | None = None,
 ) -> None:
-    """FP8 scaled matrix multiply ``c = scale_a * (a @ b) * scale_b + bias``, in place on ``c``.
+    """FP8 or int8 scaled matrix multiply ``c = scale_a * (a @ b) * scale_b + bias``, in place on ``c``.
 
     Drop-in for ``scaled_mm`` (pretuned_kernels/scaled_mm/scaled_mm.py:18-84): ``a [M, K]`` with unit stride
     along K, ``b [K, N]`` with ``b.stride(0) == 1`` (the weight stored ``[N, K]``), scales ``[1]``, ``[1, 1]``,
     ``[M]`` / ``[M, 1]`` (``scale_a``) or ``[N]`` / ``[N, 1]`` (``scale_b``), optional ``bias [N]`` in ``c``'s dtype,
-    added after the cast to that dtype.  The reference's assertions are kept; its int8 form is not built.
+    added after the cast to that dtype.  The reference's assertions are kept.  int8 operands accumulate in int32
+    (scaled_mm.py:53), converted to fp32 once after the whole K range.
     """
     M, K = a.shape  # noqa: N806
     N = b.shape[1]  # noqa: N806
@@ -839,8 +840,8 @@ def scaled_mm(
     assert out_dtype.is_floating_point
     if bias is not None:
         assert bias.numel() == N and bias.dtype == out_dtype
-    if a.dtype not in (_FP8, torch.float8_e5m2):
-        raise TypeError(f"a and b must be float8_e4m3fn or float8_e5m2, got {a.dtype}")
+    if a.dtype not in (_FP8, torch.float8_e5m2, torch.int8):
+        raise TypeError(f"a and b must be float8_e4m3fn, float8_e5m2 or int8, got {a.dtype}")
     if out_dtype not in _SCALED_MM_OUT:
         raise TypeError(f"c must be bfloat16, float16 or float32, got {out_dtype}")
     if c.shape != (M, N) or c.stride(1) != 1:

@@ -259,7 +259,8 @@ int hb200_silu_mul_fp8(void* out, const void* input, const float* scale, int64_t
  * K-major storage [N, K] with row pitch ldb (the reference's b [K, N] with b.stride(0) == 1), c [M, N] with row
  * pitch ldc, pitches in elements.  scale_a / scale_b are fp32, one value or one per row of a / column of b
  * (scale_a_per_row / scale_b_per_col); bias is [N] in the output type or null and is added after the cast, as
- * the reference does.  fp8_format 0 = e4m3, 1 = e5m2 (both operands); out_dtype 0 bf16, 1 fp16, 2 fp32.
+ * the reference does.  fp8_format 0 = e4m3, 1 = e5m2, 2 = int8 (both operands; int8 runs kind::i8 with an int32
+ * accumulator, converted to fp32 once after the whole K range, scaled_mm.py:53); out_dtype 0 bf16, 1 fp16, 2 fp32.
  * Needs 16-byte aligned a and b and lda % 16 == ldb % 16 == 0 (HB200_ERR_UNSUPPORTED otherwise).
  * The (tile, K block) units are dealt to the CTAs in equal contiguous ranges; tiles shared between CTAs are
  * summed in a fixed order through `workspace`: caller-owned device memory of
@@ -329,6 +330,14 @@ int hb200_nvfp4_grouped_matmul_silu(const void* a_packed, const void* b_packed, 
                                     const void* scale_b, void* y_out, float* row_amax, const int32_t* tile_info,
                                     int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups, int64_t ldy,
                                     const float* row_scale, const float* group_alpha, float alpha, void* stream);
+
+/* The same call for a row layout whose groups are padded to multiples of 256 rows (hb200_moe_build_schedule_256;
+ * max_m_tiles still counts 128-row tiles and is even): 256 x 256 tiles on CTA pairs, the same values bit for bit.
+ * Shapes the pair kernel does not take run on the 128-row kernel.  No counterpart in the reference. */
+int hb200_nvfp4_grouped_matmul_silu_256(const void* a_packed, const void* b_packed, const void* scale_a,
+                                        const void* scale_b, void* y_out, float* row_amax, const int32_t* tile_info,
+                                        int64_t max_m_tiles, int64_t n, int64_t k, int64_t groups, int64_t ldy,
+                                        const float* row_scale, const float* group_alpha, float alpha, void* stream);
 
 /* Per-token NVFP4 quantisation of rows whose maxima are already known (row_amax from the call above): row
  * r = row_idx[i] (i when null) of x [*, ldx] -> codes, swizzled scales, global_scale[r] = row_amax[r] / (6 * 448)

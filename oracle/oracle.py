@@ -306,7 +306,8 @@ def scaled_mm(
     """scaled_mm (pretuned_kernels/scaled_mm/scaled_mm.py:18-84): fp32 accumulation of ``a [M, K] @ b [K, N]``
     (FP8 operands, products exact), ``scale_a * acc`` then ``scale_b.T * acc`` in fp32, the cast to the output
     type, and only then the bias, added in the output type.  The accumulation runs in fp64 and is rounded to
-    fp32 once: the reference leaves the summation order to the tiling."""
+    fp32 once: the reference leaves the summation order to the tiling.  For int8 operands the reference accumulates
+    in int32 and converts to fp32 once (scaled_mm.py:53,66); fp64 holds those sums exactly, so this is that value."""
     m, _k = a.shape
     n = b.shape[1]
     acc = (a.to(torch.float64) @ b.to(torch.float64)).to(torch.float32)

@@ -169,6 +169,64 @@ def test_silu_epilogue_is_bit_identical_to_the_two_kernel_form():
     assert torch.equal(amax[rows], want.float().abs().amax(dim=1))
 
 
+def test_pair_tiles_over_256_row_padding_give_the_same_layer_bit_for_bit(monkeypatch):
+    """CTA-pair grouped GEMMs (SiLU-mul epilogue included) over experts padded to 256 rows, against the 128-row form;
+    skewed routing, so some experts are empty and some 256-row tiles hold one valid half only."""
+    t, h, inter, e, k = 1024, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16).to(DEV)
+    logits = torch.randn(t, e, generator=g).to(DEV)
+    logits[:, 5] = -30.0
+    logits[:, 0] += 1.5
+    w_gu = M.interleave_gate_up(M.quantize_expert_weights((torch.randn(e, 2 * inter, h, generator=g) * 0.02).to(DEV)))
+    w_d = M.quantize_expert_weights((torch.randn(e, h, inter, generator=g) * 0.02).to(DEV))
+    monkeypatch.delenv("HB200_MOE_PAD", raising=False)
+    got128 = {}
+    y128 = M.nvfp4_moe(x, logits, k, w_gu, w_d, intermediates=got128)
+    monkeypatch.setenv("HB200_MOE_PAD", "256")
+    got256 = {}
+    y256 = M.nvfp4_moe(x, logits, k, w_gu, w_d, intermediates=got256)
+    torch.cuda.synchronize()
+    assert _lib.load().hb200_device_status(1) == 0
+    assert got128["sched"].pad == 128 and got256["sched"].pad == 256
+    r128, r256 = got128["sched"].row_of_pair.long(), got256["sched"].row_of_pair.long()
+    assert torch.equal(got128["y"][r128], got256["y"][r256])
+    assert torch.equal(got128["a2"][r128], got256["a2"][r256])
+    assert torch.equal(y128, y256)
+
+
+def test_layer_replays_from_a_cuda_graph_after_its_inputs_change():
+    """Capture the whole layer (routing, sort, schedule, both grouped GEMMs, combine), then change tokens and router
+    logits in place and replay: the routing, the per-expert row counts and the tile list all change on the device,
+    nothing is read back (the pattern of test/test_cute_deepgemm_selected.py:391-405)."""
+    t, h, inter, e, k = 384, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(13)
+    w_gu = M.interleave_gate_up(M.quantize_expert_weights((torch.randn(e, 2 * inter, h, generator=g) * 0.02).to(DEV)))
+    w_d = M.quantize_expert_weights((torch.randn(e, h, inter, generator=g) * 0.02).to(DEV))
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16).to(DEV)
+    logits = torch.randn(t, e, generator=g).to(DEV)
+    for _ in range(2):
+        M.nvfp4_moe(x, logits, k, w_gu, w_d)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = M.nvfp4_moe(x, logits, k, w_gu, w_d)
+    for seed, skew in ((14, None), (15, 3), (16, 0)):
+        g2 = torch.Generator().manual_seed(seed)
+        x.copy_(torch.randn(t, h, generator=g2).to(torch.bfloat16))
+        new_logits = torch.randn(t, e, generator=g2)
+        if skew is not None:
+            new_logits[:, skew] += 4.0  # most tokens now take this expert: other experts shrink or empty out
+        logits.copy_(new_logits)
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = y.clone()
+        eager = M.nvfp4_moe(x, logits, k, w_gu, w_d)
+        torch.cuda.synchronize()
+        assert _lib.load().hb200_device_status(1) == 0
+        assert torch.equal(replayed, eager)
+
+
 def test_device_weight_quantiser_matches_oracle():
     torch.manual_seed(5)
     w = torch.randn(3, 128, 256) * 0.02

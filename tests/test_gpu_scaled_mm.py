@@ -159,7 +159,7 @@ def test_the_reference_assertions_and_the_abi_errors():
     with pytest.raises(AssertionError):
         hb.scaled_mm(c, a, b, one, one, torch.zeros(128, dtype=torch.float16, device=DEV))
     with pytest.raises(TypeError):
-        hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)
+        hb.scaled_mm(c, a.view(torch.uint8), b.view(torch.uint8), one, one)
     lib = _lib.load()
     m, k, n = 16, 4096, 24576
     a, b, _ = random_case(m, k, n, seed=2)
@@ -173,3 +173,39 @@ def test_the_reference_assertions_and_the_abi_errors():
     assert lib.hb200_fp8_scaled_mm(*bad, None, 0, None) == _lib.HB200_ERR_UNSUPPORTED
     torch.cuda.synchronize()
     assert torch.isnan(c).all()  # nothing ran
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("m,k,n", [
+    (1, 512, 256), (16, 2048, 2048), (17, 1040, 200), (64, 6144, 2048), (256, 1024, 512), (300, 512, 384), (33, 16, 128),
+    (16, 8192, 1024),   # thread-block clusters, K split across their CTAs: int32 partial sums through shared memory
+    (64, 2048, 12288),  # whole tiles
+    (16, 4096, 24576),  # stream-K ranges: int32 partial sums through the workspace
+    (64, 25600, 5120),  # sums beyond 2^24: the single conversion to fp32 rounds
+])
+def test_int8_operands_accumulate_in_int32_bit_exact(m, k, n, out_dtype):
+    """The integer form (pretuned_kernels/scaled_mm/scaled_mm.py:53): int32 accumulation is exact, so the result is
+    the oracle's, bit for bit, whatever the split of the K range."""
+    g = torch.Generator().manual_seed(m + k + n)
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, generator=g)
+    b = torch.randint(-128, 128, (n, k), dtype=torch.int8, generator=g).t()
+    if k >= 25600:
+        a, b = a.abs().clamp(max=127).to(torch.int8), b.abs().clamp(max=127).to(torch.int8)  # large same-sign sums
+    sa = (torch.rand(m, 1, generator=g) + 0.5) * 1e-3
+    sb = (torch.rand(n, generator=g) + 0.5) * 1e-3
+    bias = (torch.rand(n, generator=g) - 0.5).to(out_dtype)
+    for s_a, s_b, bb in ((sa, sb, bias), (sa[:1], sb[:1], None)):
+        c = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+        hb.scaled_mm(c, a.to(DEV), b.to(DEV), s_a.to(DEV), s_b.to(DEV), None if bb is None else bb.to(DEV))
+        assert device_status_ok()
+        ref = O.scaled_mm(a, b, s_a, s_b, bb, out_dtype)
+        assert torch.equal(c.cpu(), ref)
+
+
+def test_int8_and_fp8_operands_must_not_be_mixed():
+    a = torch.zeros(16, 64, dtype=torch.int8, device=DEV)
+    b = torch.zeros(32, 64, dtype=FP8, device=DEV).t()
+    c = torch.empty(16, 32, dtype=torch.bfloat16, device=DEV)
+    one = torch.ones(1, device=DEV)
+    with pytest.raises(AssertionError):
+        hb.scaled_mm(c, a, b, one, one)

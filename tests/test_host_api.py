@@ -104,7 +104,9 @@ def test_fp8_consumers_validate_and_have_no_cpu_fallback():
     with pytest.raises(AssertionError):
         hb.scaled_mm(c, a, b, one, one, torch.zeros(32))  # bias not in c's dtype
     with pytest.raises(TypeError):
-        hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)  # the int8 form is not built
+        hb.scaled_mm(c, a.view(torch.uint8), b.view(torch.uint8), one, one)  # neither FP8 nor int8
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        hb.scaled_mm(c, a.view(torch.int8), b.view(torch.int8), one, one)  # the int8 form, like the FP8 one, needs the GPU
     x = torch.zeros(4, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         hb.silu_mul_fp8(x, one)
