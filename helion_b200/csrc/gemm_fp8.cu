@@ -32,6 +32,12 @@ namespace hb200 {
 
 __device__ int g_device_status_fp8 = 0;
 
+}  // namespace hb200
+
+#include "gemm_dense_pair.cuh"
+
+namespace hb200 {
+
 namespace {
 
 using namespace sm100;
@@ -43,6 +49,7 @@ constexpr int kFp8MaxStages = 10;
 constexpr int kFp8CounterBytes = 16384; // arrival counters at the start of the workspace
 constexpr int kFp8MaxTiles = kFp8CounterBytes / 4;
 constexpr int kFp8MinUnits = 4;         // K blocks per CTA below which more CTAs only add partial sums
+constexpr int kPairMinTokens = 384;     // from here on the CTA-pair kernel (activations on the M side) takes over
 
 struct Fp8Args {
   void* out;
@@ -655,6 +662,13 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
   if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b) % 16 || (lda % 16) != 0 || (ldb % 16) != 0)
     return HB200_ERR_UNSUPPORTED;
   if (m > 0x7fffff00 || n > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
+  // prefill shapes: 256 x 256 tiles on CTA pairs, activations on the M side (no workspace)
+  if (m >= kPairMinTokens) {
+    const int rc = dense_pair::launch(a, b, c, scale_a, scale_b, bias, m, n, k, lda, ldb, ldc, scale_a_per_row,
+                                      scale_b_per_col, fp8_format, out_dtype, device_sms(),
+                                      static_cast<cudaStream_t>(stream));
+    if (rc != HB200_ERR_UNSUPPORTED) return rc;
+  }
   Fp8Plan p;
   if (!make_fp8_plan(m, n, k, device_sms(), &p)) return HB200_ERR_UNSUPPORTED;
   if (p.workspace_bytes > 0) {

@@ -209,3 +209,60 @@ def test_int8_and_fp8_operands_must_not_be_mixed():
     one = torch.ones(1, device=DEV)
     with pytest.raises(AssertionError):
         hb.scaled_mm(c, a, b, one, one)
+
+
+PREFILL = [(384, 512, 256), (1000, 1040, 520), (2048, 4096, 1024), (513, 208, 1000), (4096, 2048, 2304), (640, 144, 130)]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("m,k,n", PREFILL)
+def test_prefill_shapes_on_cta_pairs(m, k, n, out_dtype):
+    """From 384 tokens on the activations ride the M side of 256 x 256 CTA-pair tiles; ragged M, N and K edges, and
+    an output pitch the TMA stores cannot take (n = 130: the decode kernel runs instead)."""
+    a, b, g = random_case(m, k, n, seed=m + k + n)
+    sa = (torch.rand(m, 1, generator=g) + 0.5).to(DEV)
+    sb = (torch.rand(n, generator=g) + 0.5).to(DEV)
+    bias = (torch.rand(n, generator=g) - 0.5).to(out_dtype).to(DEV)
+    c = torch.full((m + 3, n), float("nan"), dtype=out_dtype, device=DEV)
+    hb.scaled_mm(c[:m], a, b, sa, sb, bias)
+    assert device_status_ok()
+    check(c[:m], a, b, sa, sb, bias)
+    assert torch.isnan(c[m:]).all()  # rows past M are not written
+    c2 = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    hb.scaled_mm(c2, a, b, sa[:1], sb[:1], None)
+    assert device_status_ok()
+    check(c2, a, b, sa[:1], sb[:1], None)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,k,n", PREFILL)
+def test_prefill_shapes_int8_bit_exact(m, k, n, out_dtype):
+    g = torch.Generator().manual_seed(m + k + n)
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, generator=g)
+    b = torch.randint(-128, 128, (n, k), dtype=torch.int8, generator=g).t()
+    sa = (torch.rand(m, 1, generator=g) + 0.5) * 1e-3
+    sb = (torch.rand(n, generator=g) + 0.5) * 1e-3
+    bias = (torch.rand(n, generator=g) - 0.5).to(out_dtype)
+    c = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    hb.scaled_mm(c, a.to(DEV), b.to(DEV), sa.to(DEV), sb.to(DEV), bias.to(DEV))
+    assert device_status_ok()
+    assert torch.equal(c.cpu(), O.scaled_mm(a, b, sa, sb, bias, out_dtype))
+
+
+def test_prefill_is_deterministic_and_replays_from_a_graph():
+    m, k, n = 1024, 2048, 1536
+    a, b, g = random_case(m, k, n, seed=77)
+    sa = (torch.rand(m, 1, generator=g) + 0.5).to(DEV)
+    sb = (torch.rand(n, generator=g) + 0.5).to(DEV)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    hb.scaled_mm(c, a, b, sa, sb)
+    first = c.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        hb.scaled_mm(c, a, b, sa, sb)
+    a2, _, _ = random_case(m, k, n, seed=78)
+    a.copy_(a2)
+    graph.replay()
+    assert device_status_ok()
+    assert not torch.equal(c, first)
+    check(c, a, b, sa, sb, None)
