@@ -1108,8 +1108,34 @@ def sub_scaled_mm(args, dev, timer) -> dict:
     steps = max(20, args.steps)
     ms, med = timer.run2(graphed(ours)[0], steps, 3)
     lms, lmed = timer.run2(graphed(library)[0], steps, 3)
-    return hbm_record(ms, med, nbytes, tokens=m, shapes=len(SCALED_MM_KN), library_us=lms * 1e3, library_median_us=lmed * 1e3)
+    rec = hbm_record(ms, med, nbytes, tokens=m, shapes=len(SCALED_MM_KN), library_us=lms * 1e3, library_median_us=lmed * 1e3)
+    del cases
+    # prefill shapes (tensor-bound): the CTA-pair kernel, FP8 and int8, the library's FP8 kernel beside them
+    peaks = measured_peaks()
+    rec["prefill"] = {}
+    for pm, pk, pn in SCALED_MM_PREFILL:
+        sc = 1.0 / math.sqrt(pk)
+        a = (sc * torch.randn(pm, pk, device=dev, generator=g)).to(torch.float8_e4m3fn)
+        b = (sc * torch.randn(pn, pk, device=dev, generator=g)).to(torch.float8_e4m3fn).t()
+        ai = torch.randint(-128, 128, (pm, pk), dtype=torch.int8, device=dev, generator=g)
+        bi = torch.randint(-128, 128, (pn, pk), dtype=torch.int8, device=dev, generator=g).t()
+        sa = torch.rand(pm, 1, device=dev, generator=g) + 0.5
+        sb = torch.rand(1, pn, device=dev, generator=g) + 0.5
+        cc = torch.empty(pm, pn, dtype=torch.bfloat16, device=dev)
+        t8, m8 = timer.run2(graphed(lambda: hb.scaled_mm(cc, a, b, sa, sb.reshape(-1)))[0], 10, 3)
+        ti, mi = timer.run2(graphed(lambda: hb.scaled_mm(cc, ai, bi, sa, sb.reshape(-1)))[0], 10, 3)
+        tl, ml = timer.run2(graphed(lambda: torch._scaled_mm(a, b, scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16))[0], 10, 3)
+        flops = 2.0 * pm * pn * pk
+        rec["prefill"][f"{pm}x{pk}x{pn}"] = {
+            "fp8_us": t8 * 1e3, "fp8_median_us": m8 * 1e3, "int8_us": ti * 1e3, "library_fp8_us": tl * 1e3,
+            "fp8_TFLOPs": flops / (t8 * 1e-3) / 1e12,
+            "frac_of_2x_measured_bf16": flops / (t8 * 1e-3) / 1e12 / (2 * peaks["bf16_tflops"])}
+        del a, b, ai, bi, cc
+    return rec
 
+
+# (M, K, N): prefill-sized calls of the same operator (the reference tunes it on 16 and 64 tokens only)
+SCALED_MM_PREFILL = [(1024, 4096, 4096), (4096, 4096, 4096), (8192, 4096, 6144), (8192, 8192, 8192)]
 
 # (groups, expected rows per group, N, K) of the reference's bf16 grouped-GEMM manifest
 # (benchmarks/cute/deepgemm_selected_path.py:62-71); the real group sizes are expected * U(0.7, 1.3) from

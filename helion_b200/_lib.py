@@ -65,6 +65,10 @@ SIGNATURES: dict[str, list] = {
     "hb200_peer_barrier": [_P, _I64, _I64, _P, _P],
     "hb200_nvfp4_gemv_bf16in_rs": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_float, _P],
     "hb200_tp_reduce_partials": [_P, _P, _I64, _I64, _I64, _I64, _P],
+    "hb200_dense_matmul": [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_int, _P],
+    "hb200_ag_matmul": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, ctypes.c_uint32, c_int, _P],
+    "hb200_matmul_rs": [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_int, _P],
+    "hb200_reduce_slots": [_P, _P, _I64, _I64, _I64, _I64, c_int, _P],
     "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],
     "hb200_moe_route_top_k": [_P, c_int, _I64, _I64, _I64, _P, _P, _P],
     "hb200_silu_mul_fp8": [_P, _P, _P, _I64, _I64, _I64, c_int, _P],

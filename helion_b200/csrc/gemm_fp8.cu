@@ -32,11 +32,11 @@ namespace hb200 {
 
 __device__ int g_device_status_fp8 = 0;
 
-}  // namespace hb200
 
-#include "gemm_dense_pair.cuh"
-
-namespace hb200 {
+// CTA-pair kernel for prefill shapes (gemm_dense.cu)
+int dense_pair_scaled_mm(const void* a, const void* b, void* c, const float* scale_a, const float* scale_b,
+                         const void* bias, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                         int scale_a_per_row, int scale_b_per_col, int format, int out_dtype, cudaStream_t stream);
 
 namespace {
 
@@ -664,9 +664,8 @@ extern "C" int hb200_fp8_scaled_mm(const void* a, const void* b, void* c, const 
   if (m > 0x7fffff00 || n > 0x7fffff00 || k > 0x7fffff00) return HB200_ERR_UNSUPPORTED;
   // prefill shapes: 256 x 256 tiles on CTA pairs, activations on the M side (no workspace)
   if (m >= kPairMinTokens) {
-    const int rc = dense_pair::launch(a, b, c, scale_a, scale_b, bias, m, n, k, lda, ldb, ldc, scale_a_per_row,
-                                      scale_b_per_col, fp8_format, out_dtype, device_sms(),
-                                      static_cast<cudaStream_t>(stream));
+    const int rc = dense_pair_scaled_mm(a, b, c, scale_a, scale_b, bias, m, n, k, lda, ldb, ldc, scale_a_per_row,
+                                        scale_b_per_col, fp8_format, out_dtype, static_cast<cudaStream_t>(stream));
     if (rc != HB200_ERR_UNSUPPORTED) return rc;
   }
   Fp8Plan p;

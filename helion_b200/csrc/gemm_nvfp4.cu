@@ -622,6 +622,8 @@ int f16_device_status(int reset);
 int peer_device_status(int reset);
 int gemv_tc_device_status(int reset);
 int fp8_device_status(int reset);
+int dense_device_status(int reset);
+int dense_set_wait_budget(long long cycles);
 int f16_set_wait_budget(long long cycles);
 int peer_set_wait_budget(long long cycles);
 int gemv_tc_set_wait_budget(long long cycles);
@@ -654,6 +656,7 @@ extern "C" int hb200_set_wait_budget_cycles(int64_t cycles) {
   if (rc == HB200_OK) rc = peer_set_wait_budget(cycles);
   if (rc == HB200_OK) rc = gemv_tc_set_wait_budget(cycles);
   if (rc == HB200_OK) rc = fp8_set_wait_budget(cycles);
+  if (rc == HB200_OK) rc = dense_set_wait_budget(cycles);
   return rc;
 }
 
@@ -676,5 +679,6 @@ extern "C" int hb200_device_status(int reset) {
   const int p = hb200::peer_device_status(reset);
   const int t = hb200::gemv_tc_device_status(reset);
   const int f = hb200::fp8_device_status(reset);
-  return v != 0 ? v : (w != 0 ? w : (p != 0 ? p : (t != 0 ? t : f)));
+  const int d = hb200::dense_device_status(reset);
+  return v != 0 ? v : (w != 0 ? w : (p != 0 ? p : (t != 0 ? t : (f != 0 ? f : d))));
 }

@@ -95,6 +95,135 @@ def column_parallel_matmul(a_packed: Tensor, scale_a: Tensor, b_local: Tensor, s
     return all_gather_columns(y, group)
 
 
+# ------------------------------------------------------------------ fused matmul + collective
+def dense_matmul(a: Tensor, b: Tensor, out: Tensor | None = None) -> Tensor:
+    """``a [M, K] @ b [K, N]`` in bf16 or fp16 on CTA pairs (256 x 256 tiles, fp32 accumulate); the one-GPU form of
+    the two fused kernels below.  ``b`` is taken K-major (``b.stride(0) == 1``, the weight stored ``[N, K]``);
+    anything else is copied into that layout first."""
+    from . import _lib
+    from .ops import _require_cuda
+
+    _require_cuda(a, b)
+    if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
+        raise TypeError("dense_matmul takes bfloat16 or float16 operands of one type")
+    m, k = a.shape
+    if b.shape[0] != k:
+        raise ValueError(f"b {tuple(b.shape)} does not match a {tuple(a.shape)}")
+    n = b.shape[1]
+    b_nk = _k_major(b)
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if out is None:
+        out = torch.empty(m, n, dtype=a.dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.call("hb200_dense_matmul", a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), m, n, k, a.stride(0),
+                  b_nk.stride(0), out.stride(0), int(a.dtype is torch.bfloat16),
+                  torch.cuda.current_stream(a.device).cuda_stream)
+    return out
+
+
+def _k_major(b: Tensor) -> Tensor:
+    """``b [K, N]`` -> its ``[N, K]`` storage with unit stride along K (a view when ``b`` already is K-major)."""
+    b_nk = b.t()
+    if b_nk.stride(1) != 1 or b_nk.stride(0) % 8 or b_nk.data_ptr() % 16:
+        b_nk = b_nk.contiguous()
+    return b_nk
+
+
+class FusedMatmulCollectives:
+    """All-gather + matmul and matmul + reduce-scatter as single kernels over peer memory, the B200 forms of
+    ``helion_all_gather_matmul`` (examples/distributed/all_gather_matmul.py:145-196) and
+    ``helion_matmul_reduce_scatter`` (examples/distributed/matmul_reduce_scatter.py:118-140).
+
+    The reference gathers with the copy engine on a second stream and lets a Triton matmul wait on progress
+    flags; here the GEMM kernel itself carries four CTAs that push the local shard to every rank and count
+    arrivals on the destination, while its other CTAs take the row tiles in arrival order.  For the
+    reduce-scatter the GEMM's epilogue stores every tile into the owner's receive buffer; a barrier kernel and
+    a slot reduction (rank order, fp32) follow.  Symmetric buffers are allocated on first use per shape.
+    """
+
+    def __init__(self, device: torch.device, group=None):
+        self._tp = TensorParallel(device, group)
+        self.device, self.world, self.rank = device, self._tp.world, self._tp.rank
+        self._gather = {}
+        self._recv = {}
+
+    def all_gather_matmul(self, a_shared: Tensor, b: Tensor, splits_per_rank: int = 1) -> tuple[Tensor, Tensor]:
+        """``a_shared [M / world, K]`` (this rank's rows), ``b [K, N]`` -> ``(gathered a [M, K], gathered a @ b)``.
+        The gathered copy lives in a symmetric buffer that the next call with the same shape overwrites."""
+        from . import _lib
+        from .ops import _require_cuda
+
+        _require_cuda(a_shared, b)
+        if a_shared.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a_shared.dtype:
+            raise TypeError("all_gather_matmul takes bfloat16 or float16 operands of one type")
+        rows, k = a_shared.shape
+        if b.shape[0] != k:
+            raise ValueError(f"b {tuple(b.shape)} does not match a_shared {tuple(a_shared.shape)}")
+        n = b.shape[1]
+        if rows % splits_per_rank or (rows // splits_per_rank) % 256:
+            raise ValueError("rows per rank must split into chunks that are multiples of 256 rows")
+        a_shared = a_shared.contiguous()
+        b_nk = _k_major(b)
+        key = (rows, k, a_shared.dtype, splits_per_rank)
+        st = self._gather.get(key)
+        if st is None:
+            buf, buf_ptrs = self._tp._symmetric(self.world * rows * k, a_shared.dtype)
+            prog, prog_ptrs = self._tp._symmetric(max(64, self.world * splits_per_rank), torch.int32)
+            self._tp._sync_all()  # the counters are zero everywhere before the first push
+            st = self._gather[key] = dict(buf=buf.view(self.world * rows, k), buf_ptrs=buf_ptrs, prog=prog,
+                                          prog_ptrs=prog_ptrs, calls=0)
+        st["calls"] += 1
+        c = torch.empty(self.world * rows, n, dtype=a_shared.dtype, device=self.device)
+        # nobody overwrites a gather buffer that its owner's previous call still reads
+        self._tp.barrier()
+        with torch.cuda.device(self.device):
+            _lib.call("hb200_ag_matmul", a_shared.data_ptr(), st["buf_ptrs"], st["prog_ptrs"], b_nk.data_ptr(),
+                      c.data_ptr(), rows, n, k, b_nk.stride(0), c.stride(0), self.world, self.rank, splits_per_rank,
+                      st["calls"], int(a_shared.dtype is torch.bfloat16),
+                      torch.cuda.current_stream(self.device).cuda_stream)
+        return st["buf"], c
+
+    def matmul_reduce_scatter(self, a: Tensor, b: Tensor) -> Tensor:
+        """``a [M, K_local]``, ``b [K_local, N]`` (this rank's K shard) -> rows ``[rank M / world, +M / world)`` of the
+        sum over ranks of ``a @ b``.  Every partial product is rounded to the operand type before it travels, and
+        the owner adds the partials in rank order in fp32, as the reference kernel does."""
+        from . import _lib
+        from .ops import _require_cuda
+
+        _require_cuda(a, b)
+        if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
+            raise TypeError("matmul_reduce_scatter takes bfloat16 or float16 operands of one type")
+        m, k = a.shape
+        if b.shape[0] != k:
+            raise ValueError(f"b {tuple(b.shape)} does not match a {tuple(a.shape)}")
+        n = b.shape[1]
+        if m % (256 * self.world):
+            raise ValueError("M must be a multiple of 256 rows per rank")
+        rows = m // self.world
+        if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+            a = a.contiguous()
+        b_nk = _k_major(b)
+        key = (m, n, a.dtype)
+        st = self._recv.get(key)
+        if st is None:
+            ring = [self._tp._symmetric(m * n, a.dtype) for _ in range(2)]
+            self._tp._sync_all()
+            st = self._recv[key] = dict(ring=ring, turn=0)
+        slots, slot_ptrs = st["ring"][st["turn"]]
+        st["turn"] ^= 1  # two buffers alternate: a peer may push the next step while this rank still reduces
+        out = torch.empty(rows, n, dtype=a.dtype, device=self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        is_bf16 = int(a.dtype is torch.bfloat16)
+        with torch.cuda.device(self.device):
+            _lib.call("hb200_matmul_rs", a.data_ptr(), b_nk.data_ptr(), slot_ptrs, m, n, k, a.stride(0), b_nk.stride(0),
+                      self.world, self.rank, is_bf16, stream)
+            self._tp.barrier()
+            _lib.call("hb200_reduce_slots", slots.data_ptr(), out.data_ptr(), self.world, rows, n, out.stride(0), is_bf16,
+                      stream)
+        return out
+
+
 # ------------------------------------------------------------------ fused column parallelism
 class GatheredOutput:
     """A ring of ``[rows, n_total]`` output buffers in symmetric memory, mapped into every rank.

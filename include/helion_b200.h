@@ -416,6 +416,41 @@ int hb200_nvfp4_gemv_bf16in_rs(const void* weight_packed, const void* x_bf16, co
 int hb200_tp_reduce_partials(const void* partials_f32, void* out_bf16, int64_t world, int64_t batch, int64_t cols,
                              int64_t ld_out, void* stream);
 
+/* ------------------------------------------------ dense bf16 / fp16 GEMM on CTA pairs and its fused collectives
+ * c [M, N] = a [M, K] . b^T, b given K-major as [N, K]; pitches in elements; fp32 accumulate; 256 x 256 tiles on CTA
+ * pairs with two accumulators in tensor memory.  M, N >= 256, 16-byte aligned a, b, c, lda % 8 == ldb % 8 ==
+ * ldc % 8 == 0 (HB200_ERR_UNSUPPORTED otherwise).  The one-GPU form of the two calls below; stands where the
+ * reference's distributed examples call a Helion matmul (examples/distributed/all_gather_matmul.py:95-141). */
+int hb200_dense_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                       int64_t ldb, int64_t ldc, int is_bf16, void* stream);
+
+/* All-gather + matmul in one kernel (helion_all_gather_matmul, examples/distributed/all_gather_matmul.py:145-196):
+ * c [world * rows_local, N] = gathered a . b^T.  a_shard: this rank's rows [rows_local, K], contiguous.
+ * gather_ptrs[i] / progress_ptrs[i]: rank i's gather buffer [world * rows_local, K] (contiguous) and its arrival
+ * counters (uint32 [world * splits], zero before the first call, never reset), as mapped into this process
+ * (symmetric memory); entry `rank` is this rank's own.  Four CTAs of the kernel copy the shard, in `splits` chunks,
+ * into every rank's buffer and count arrivals on the destination; the other CTAs take the row tiles in arrival
+ * order and wait (bounded, system-scope acquire) for a chunk's counter before its first load.  call_number counts
+ * the calls on this buffer set from 1: a chunk has landed when its counter reads 4 * call_number.  All ranks call
+ * with the same shapes and call_number; the caller puts a barrier between calls (a rank must not overwrite a peer's
+ * buffer while the peer still reads it).  (rows_local / splits) % 256 == 0, K % 8 == 0, N >= 256, ldc % 8 == 0. */
+int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, void* const* progress_ptrs, const void* b, void* c,
+                    int64_t rows_local, int64_t n, int64_t k, int64_t ldb, int64_t ldc, int64_t world, int64_t rank,
+                    int64_t splits, uint32_t call_number, int is_bf16, void* stream);
+
+/* Matmul + reduce-scatter, first half (matmul_reduce_scatter_kernel, examples/distributed/matmul_reduce_scatter.py:
+ * 37-115): a [M, K_local] . b^T (b K-major [N, K_local]) is this rank's partial product; the epilogue rounds it to the
+ * operand type and stores rows [d R, d R + R), R = M / world, into slot `rank` of recv_ptrs[d], rank d's receive
+ * buffer [world, R, N] (contiguous, symmetric memory), with TMA stores; nothing is loaded from peer memory.
+ * M % (256 * world) == 0, N % 8 == 0, N >= 256.  Follow with hb200_peer_barrier and hb200_reduce_slots. */
+int hb200_matmul_rs(const void* a, const void* b, void* const* recv_ptrs, int64_t m, int64_t n, int64_t k, int64_t lda,
+                    int64_t ldb, int64_t world, int64_t rank, int is_bf16, void* stream);
+
+/* Second half: out [rows, cols] (row pitch ld_out) = cast(sum over s, ascending, of fp32(slots[s, rows, cols])).
+ * The order is fixed, so results do not depend on timing.  cols % 8 == 0, ld_out % 8 == 0, 16-byte aligned. */
+int hb200_reduce_slots(const void* slots, void* out, int64_t world, int64_t rows, int64_t cols, int64_t ld_out,
+                       int is_bf16, void* stream);
+
 /* out_dtype 0 = bf16, 1 = fp16.  Needs m >= 256, n >= 256, K % 32 == 0, n_total % 8 == 0, col0 % 8 == 0
  * (HB200_ERR_UNSUPPORTED otherwise: compute locally and gather with a collective). */
 int hb200_nvfp4_scaled_matmul_tp(const void* a_packed, const void* b_packed, const void* scale_a,
