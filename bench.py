@@ -1187,6 +1187,22 @@ def sub_grouped_f16(args, dev, timer) -> dict:
             "us": ms * 1e3, "median_us": med * 1e3, "TFLOPs": tf, "frac_of_measured_bf16": tf / peaks["bf16_tflops"],
             "library_us": lms * 1e3, "parity_max_rel_err": parity}
         del a, b, y
+    # the dense CTA-pair kernel (the one-GPU form of the fused matmul + collective kernels) beside cuBLAS
+    out["dense_pair"] = {}
+    from helion_b200 import dist as D
+
+    for dm, dn, dk in ((4096, 6656, 16384), (8192, 8192, 8192)):
+        a = torch.randn(dm, dk, device=dev, dtype=torch.bfloat16, generator=gen)
+        b = (torch.randn(dn, dk, device=dev, dtype=torch.float32, generator=gen) / dk**0.5).to(torch.bfloat16).t()
+        cc = torch.empty(dm, dn, dtype=torch.bfloat16, device=dev)
+        parity = rel_err(D.dense_matmul(a, b)[:256], a[:256].float() @ b.float())
+        ms, med = timer.run2(graphed(lambda: D.dense_matmul(a, b, out=cc))[0], 10, 3)
+        lms, _ = timer.run2(graphed(lambda: torch.matmul(a, b, out=cc))[0], 10, 3)
+        tf = 2.0 * dm * dn * dk / (ms * 1e-3) / 1e12
+        out["dense_pair"][f"{dm}x{dn}x{dk}"] = {"us": ms * 1e3, "median_us": med * 1e3, "TFLOPs": tf,
+                                                "frac_of_measured_bf16": tf / peaks["bf16_tflops"],
+                                                "library_us": lms * 1e3, "parity_max_rel_err": parity}
+        del a, b, cc
     for name, problems in GROUPED_DIRECT_CASES.items():
         ga = [torch.randn(m, k, device=dev, dtype=torch.float16, generator=gen) for m, _, k in problems]
         gb = [torch.randn(nn, k, device=dev, dtype=torch.float16, generator=gen) for _, nn, k in problems]
@@ -1286,6 +1302,71 @@ def sub_ep_moe(args, dev, rank, world, timer) -> dict:
     return tensor_record(ms, med, moe_flops(), parity=parity, phases_us=ep.phase_times(x, logits, w_gu_i, w_d))
 
 
+def sub_fused_matmul(args, dev, rank, world, timer) -> dict:
+    """The reference's distributed examples at the all-gather example's shape (M = 4096, N = 6656, K = 16384, bf16:
+    examples/distributed/all_gather_matmul.py:258): all-gather + matmul and matmul + reduce-scatter as single
+    kernels over peer memory, beside the process group's collective plus the same GEMM kernel.  Eager launches
+    (the all-gather form takes a call number per launch)."""
+    import torch.distributed as dist
+
+    from helion_b200 import dist as D
+
+    m, n, k = 4096, 6656, 16384
+    peaks = measured_peaks()
+    fm = D.FusedMatmulCollectives(dev)
+    g = torch.Generator(device=dev).manual_seed(40 + rank)
+    out = {}
+    # all-gather + matmul: every rank holds M / world rows of a, and all of b
+    rows = m // world
+    splits = 2 if (rows // 2) % 256 == 0 else 1
+    shard = torch.randn(rows, k, device=dev, dtype=torch.bfloat16, generator=g)
+    gb = torch.Generator(device=dev).manual_seed(39)
+    b = (torch.randn(n, k, device=dev, dtype=torch.float32, generator=gb) / k**0.5).to(torch.bfloat16).t()
+    full = torch.empty(m, k, dtype=torch.bfloat16, device=dev)
+
+    def unfused_ag():
+        dist.all_gather_into_tensor(full, shard)
+        return D.dense_matmul(full, b)
+
+    _, c = fm.all_gather_matmul(shard, b, splits_per_rank=splits)
+    same = bool(torch.equal(c, unfused_ag()))
+    ms, med = timer.run2(lambda: fm.all_gather_matmul(shard, b, splits_per_rank=splits), 10, 3)
+    ums, umed = timer.run2(unfused_ag, 10, 3)
+    gms, _ = timer.run2(lambda: D.dense_matmul(full, b), 10, 3)
+    flops = 2.0 * m * n * k
+    out["all_gather_matmul"] = {
+        "us": ms * 1e3, "median_us": med * 1e3, "collective_then_matmul_us": ums * 1e3, "matmul_alone_us": gms * 1e3,
+        "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac_of_measured_bf16": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "fused_equals_collective": same, "splits_per_rank": splits,
+        "nvlink_bytes_in_per_rank": (world - 1) * rows * k * 2}
+    del full, c, shard
+    # matmul + reduce-scatter: every rank holds a K shard of a and of b
+    k_local = k // world
+    a = torch.randn(m, k_local, device=dev, dtype=torch.bfloat16, generator=g)
+    bl = (torch.randn(n, k_local, device=dev, dtype=torch.float32, generator=g) / k**0.5).to(torch.bfloat16).t()
+    recv = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
+
+    def unfused_rs():
+        dist.reduce_scatter_tensor(recv, D.dense_matmul(a, bl))
+        return recv
+
+    got = fm.matmul_reduce_scatter(a, bl)
+    parts = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    dist.all_gather(parts, D.dense_matmul(a, bl))
+    want = sum(p.float() for p in parts)[rank * (m // world) : (rank + 1) * (m // world)].to(torch.bfloat16)
+    same = bool(torch.equal(got, want))
+    del parts, want
+    ms, med = timer.run2(lambda: fm.matmul_reduce_scatter(a, bl), 10, 3)
+    ums, umed = timer.run2(unfused_rs, 10, 3)
+    gms, _ = timer.run2(lambda: D.dense_matmul(a, bl), 10, 3)
+    flops = 2.0 * m * n * k_local
+    out["matmul_reduce_scatter"] = {
+        "us": ms * 1e3, "median_us": med * 1e3, "matmul_then_collective_us": ums * 1e3, "matmul_alone_us": gms * 1e3,
+        "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac_of_measured_bf16": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "equals_ordered_sum_of_partials": same, "nvlink_bytes_out_per_rank": (world - 1) * (m // world) * n * 2}
+    return out
+
+
 def guarded(fn, *a) -> dict:
     """A failing side workload must not cost the run its headline: record the error instead."""
     try:
@@ -1316,6 +1397,8 @@ def wl_all(args, dev, rank, world, timer):
         subs["gemv_decode_layer_column_parallel"] = guarded(sub_tp_decode_layer, args, dev, rank, world, timer)
         torch.cuda.empty_cache()
         subs["moe_expert_parallel"] = guarded(sub_ep_moe, args, dev, rank, world, timer)
+        torch.cuda.empty_cache()
+        subs["fused_matmul_collectives_bf16"] = guarded(sub_fused_matmul, args, dev, rank, world, timer)
     r["extra"]["workloads"] = subs
     return r
 

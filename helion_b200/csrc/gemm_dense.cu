@@ -14,11 +14,12 @@
 //
 // MODE 1, all-gather + matmul (examples/distributed/all_gather_matmul.py:36-141): every rank holds rows_local rows
 // of a; c = gathered a . b.  The last kPushPairs CTA pairs of the grid do not compute: they copy this rank's shard,
-// chunk by chunk, into every rank's gather buffer (bulk loads into shared memory, bulk stores to local and peer
-// memory, peers in ring order) and, when a chunk has landed, add one arrival per push CTA to that chunk's progress
-// counter on the destination (a system-scope release reduction).  The compute pairs take the tiles in the order the
-// chunks arrive (own shard first, then the ring backwards); before the first load of a chunk's rows the producer warp
-// waits (system-scope acquire, bounded) until the counter shows all arrivals of this call.  Counters only grow: call
+// chunk by chunk, into every peer's gather buffer (bulk loads into shared memory, several in flight, each followed
+// by a bulk store to peer memory; peers in ring order) and, when a chunk has landed, add one arrival per push CTA to
+// that chunk's progress counter on the destination (a system-scope release reduction); the local copy of the shard
+// comes last.  The compute pairs take the tiles in the order the chunks arrive (own rows first, read from the shard
+// itself, then the ring backwards); before the first load of a peer chunk's rows the producer warp waits
+// (system-scope acquire, bounded) until the counter shows all arrivals of this call.  Counters only grow: call
 // number s (1, 2, ...) expects kPushCtas * s arrivals, so nothing is reset between calls; the caller orders calls
 // with a barrier, since a rank may not overwrite a peer's gather buffer while the peer still reads it.  A push CTA
 // never waits for anything remote, and all CTAs of the grid are resident at once (one per SM), so ranks cannot
@@ -74,9 +75,13 @@ struct Args {
 
 constexpr int kPushPairs = 2, kPushCtas = 2 * kPushPairs;
 constexpr int kPushPiece = 32768;  // bytes per bulk copy of the push CTAs (one operand stage)
+constexpr int kPushDepth = 4;      // loads a push CTA keeps in flight
+static_assert(kPushDepth < kStages, "a push CTA needs a buffer for the store in flight");
 
 struct OutMaps {
-  CUtensorMap dest[8];  // MODE 2: rank d's receive buffer [world * R, N]; otherwise dest[0] is c
+  // MODE 2: rank d's receive buffer [world * R, N]; otherwise dest[0] is c.  MODE 1: dest[1] maps this rank's shard
+  // of a (an operand, not an output: the slot is free there).
+  CUtensorMap dest[8];
 };
 
 __device__ __forceinline__ void mma_pair_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -212,30 +217,49 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int q = (pair - num_pairs) * 2 + int(rank);
       const int64_t chunk_bytes = int64_t(g.rows_local / g.splits) * g.k_bytes;
       const int64_t part0 = (chunk_bytes / 16 * q / kPushCtas) * 16, part1 = (chunk_bytes / 16 * (q + 1) / kPushCtas) * 16;
-      uint32_t it = 0;
+      uint32_t it = 0;  // pieces requested so far, over the whole kernel: buffer it % kStages, phase (it / kStages) & 1
       bool ok = true;
-      for (int c = 0; c < g.splits && ok; ++c) {
-        const int64_t src_off = int64_t(c) * chunk_bytes;
-        for (int step = 0; step < g.world && ok; ++step) {
-          const int d = (g.rank + step) % g.world;  // own buffer first, then the ring
-          uint8_t* dst = g.gather[d] + int64_t(g.rank) * g.rows_local * g.k_bytes + src_off;
-          for (int64_t off = part0; off < part1; off += kPushPiece, ++it) {
+      // bytes [part0, part1) of `src` to `dst`: kPushDepth loads stay in flight, a piece's store follows its load
+      auto copy_part = [&](const uint8_t* src, uint8_t* dst) {
+        const int pieces = int((part1 - part0 + kPushPiece - 1) / kPushPiece);
+        const uint32_t base = it;
+        for (int i = 0; i < pieces + kPushDepth && ok; ++i) {
+          if (i < pieces) {
+            const int64_t off = part0 + int64_t(i) * kPushPiece;
             const uint32_t bytes = uint32_t(min(int64_t(kPushPiece), part1 - off));
-            const int s = it % kStages;
-            // the store that last read this buffer has finished reading: at most kStages - 1 groups stay in flight
-            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStages - 1) : "memory");
+            const int s = (base + i) % kStages;
+            // the store that last read this buffer (kStages pieces ago) has finished reading it: stores leave in
+            // order, kPushDepth of the later ones have not been issued yet
+            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStages - kPushDepth - 1) : "memory");
             const uint32_t bar = smem_u32(&full_bar[s]);
             mbar_arrive_expect_tx(bar, bytes);
-            bulk_load(smem_u32(smem + s * kStageBytes), g.shard + src_off + off, bytes, bar);
-            if (!mbar_wait(bar, (it / kStages) & 1, abort_flag)) { ok = false; break; }
+            bulk_load(smem_u32(smem + s * kStageBytes), src + off, bytes, bar);
+          }
+          if (i >= kPushDepth) {
+            const int j = i - kPushDepth;
+            const int64_t off = part0 + int64_t(j) * kPushPiece;
+            const uint32_t bytes = uint32_t(min(int64_t(kPushPiece), part1 - off));
+            const int s = (base + j) % kStages;
+            if (!mbar_wait(smem_u32(&full_bar[s]), ((base + j) / kStages) & 1, abort_flag)) { ok = false; break; }
             bulk_store(dst + off, smem_u32(smem + s * kStageBytes), bytes);
             bulk_commit_group();
           }
-          bulk_wait_group0();  // the writes themselves, not only the reads of shared memory
+        }
+        it = base + pieces;
+        bulk_wait_group0();  // the writes themselves, not only the reads of shared memory
+      };
+      const int64_t my_rows_off = int64_t(g.rank) * g.rows_local * g.k_bytes;
+      for (int c = 0; c < g.splits && ok; ++c) {
+        for (int step = 1; step < g.world && ok; ++step) {
+          const int d = (g.rank + step) % g.world;  // the ring, the next rank first
+          copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[d] + my_rows_off + int64_t(c) * chunk_bytes);
           __threadfence_system();
           if (ok) red_release_sys_add(g.progress[d] + g.rank * g.splits + c, 1u);
         }
       }
+      // this rank's own copy of its rows comes last: its tiles read the shard itself
+      for (int c = 0; c < g.splits && ok; ++c)
+        copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[g.rank] + my_rows_off + int64_t(c) * chunk_bytes);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
@@ -251,7 +275,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // rows of chunk (source rank, split): wait until every push CTA of the source has delivered its part
         const int rows_chunk = g.rows_local / g.splits;
         const int chunk = (m_blk * kTile) / rows_chunk;  // = source * splits + split
-        if (chunk != seen_chunk) {
+        if (chunk / g.splits != g.rank && chunk != seen_chunk) {
           const uint32_t* counter = g.progress[g.rank] + chunk;
           const long long t0 = clock64();
           while (int32_t(ld_acquire_sys(counter) - g.arrivals) < 0) {
@@ -274,7 +298,10 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);  // always the leader's barrier
         if (elect_one()) {
           if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * kStageBytes);
-          tma_load_2d_pair(smem_u32(st), &tmap_a, kb * 128, a_row, bar);
+          if (MODE == 1 && a_row / g.rows_local == g.rank)  // own rows: straight from the shard
+            tma_load_2d_pair(smem_u32(st), &omaps.dest[1], kb * 128, a_row - g.rank * g.rows_local, bar);
+          else
+            tma_load_2d_pair(smem_u32(st), &tmap_a, kb * 128, a_row, bar);
           tma_load_2d_pair(smem_u32(st + kHalfBytes), &tmap_b, kb * 128, b_row, bar);
         }
         __syncwarp();
@@ -584,6 +611,7 @@ extern "C" int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, vo
   OutMaps om{};
   if (!make_byte_map(&ta, gather_ptrs[rank], m, 2 * k, 2 * k) || !make_byte_map(&tb, b, n, 2 * k, 2 * ldb)) return HB200_ERR_CUDA;
   if (!make_output_map16(&om.dest[0], c, m, n, ldc, is_bf16 != 0)) return HB200_ERR_CUDA;
+  if (!make_byte_map(&om.dest[1], a_shard, rows_local, 2 * k, 2 * k)) return HB200_ERR_CUDA;
   g.out = c;
   g.ldc = ldc;
   g.scale_a = one;

@@ -1,8 +1,8 @@
 """Dense bf16 / fp16 GEMM on CTA pairs, all-gather + matmul and matmul + reduce-scatter as single kernels.
 
-With one rank the fused kernels still run their whole machinery (the push CTAs copy the shard into the gather
-buffer and count arrivals, the compute CTAs wait on the counters; the reduce-scatter stores into slot 0 and reduces
-one slot), inside one launch.  The run over real peer mappings needs two GPUs and is skipped otherwise.
+With one rank the fused kernels still run inside one launch: the push CTAs copy the shard into the gather buffer
+while the compute CTAs work on it; the reduce-scatter stores into slot 0 and reduces one slot.  The arrival counters
+and the waits on them need a peer: that run, over real peer mappings, needs two GPUs and is skipped otherwise.
 """
 
 from __future__ import annotations
@@ -59,12 +59,12 @@ def test_dense_matmul_rejects_what_it_does_not_take():
 
 
 @pytest.mark.parametrize("splits", [1, 2, 4])
-def test_all_gather_matmul_with_one_rank_counts_arrivals(splits):
+def test_all_gather_matmul_with_one_rank(splits):
     rows, k, n = 1024, 512, 768
     fm = D.FusedMatmulCollectives(torch.device(DEV, torch.cuda.current_device()))
     g = torch.Generator().manual_seed(splits)
     b = (torch.randn(n, k, generator=g) / k**0.5).to(torch.bfloat16).to(DEV).t()
-    for step in range(3):  # the counters keep growing from call to call
+    for step in range(3):
         a = torch.randn(rows, k, generator=g).to(torch.bfloat16).to(DEV)
         gathered, c = fm.all_gather_matmul(a, b, splits_per_rank=splits)
         assert status_ok()

@@ -266,3 +266,34 @@ def test_prefill_is_deterministic_and_replays_from_a_graph():
     assert device_status_ok()
     assert not torch.equal(c, first)
     check(c, a, b, sa, sb, None)
+
+
+def test_a_chain_of_calls_whose_tokens_the_kernel_before_wrote():
+    """Every call's tokens are written by the kernel just before it on the stream, and the next call reuses the
+    shared workspace (partial sums, arrival counters) at once; eagerly and replayed from a graph."""
+    m, k, n = 16, 4096, 24576  # stream-K: partial sums and arrival counters in the shared workspace
+    a, b, g = random_case(m, k, n, seed=91)
+    sa = (torch.rand(m, 1, generator=g) + 0.5).to(DEV)
+    sb = (torch.rand(n, generator=g) + 0.5).to(DEV)
+    srcs = [random_case(m, k, 16, seed=92 + i)[0] for i in range(6)]
+    outs = [torch.empty(m, n, dtype=torch.bfloat16, device=DEV) for _ in srcs]
+    torch.cuda.synchronize()
+    for src, c in zip(srcs, outs):
+        a.copy_(src)            # a kernel that writes the tokens ...
+        hb.scaled_mm(c, a, b, sa, sb)  # ... directly followed by their consumer
+    assert device_status_ok()
+    for src, c in zip(srcs, outs):
+        check(c, src, b, sa, sb, None)
+    # the same chain replayed from a graph
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for src, c in zip(srcs, outs):
+            a.copy_(src)
+            hb.scaled_mm(c, a, b, sa, sb)
+    firsts = [c.clone() for c in outs]
+    for c in outs:
+        c.fill_(float("nan"))
+    graph.replay()
+    assert device_status_ok()
+    for c, first in zip(outs, firsts):
+        assert torch.equal(c, first)
