@@ -752,6 +752,21 @@ def wl_scaled_mm(args, dev, rank, world, timer):
             torch._scaled_mm(a, b, scale_a=sa, scale_b=sb, bias=bias, out_dtype=torch.bfloat16)
 
     library_ms = timer.run(graphed(library_step)[0], args.steps, args.warmup)
+    # a prefill-sized call (8192 tokens: the CTA-pair kernel), two launches per step; timed region 3
+    pm, pk, pn = SCALED_MM_PREFILL[-1]
+    pa = (torch.randn(pm, pk, device=dev, generator=g) / math.sqrt(pk)).to(torch.float8_e4m3fn)
+    pb = (torch.randn(pn, pk, device=dev, generator=g) / math.sqrt(pk)).to(torch.float8_e4m3fn).t()
+    psa, psb = torch.rand(pm, 1, device=dev, generator=g) + 0.5, torch.rand(pn, device=dev, generator=g) + 0.5
+    pc = torch.empty(pm, pn, dtype=torch.bfloat16, device=dev)
+
+    def two_prefill():
+        hb.scaled_mm(pc, pa, pb, psa, psb)
+        hb.scaled_mm(pc, pa, pb, psa, psb)
+
+    prefill_ms = timer.run(graphed(two_prefill)[0], max(5, args.steps // 4), 3) / 2
+    prefill = {"shape": f"{pm}x{pk}x{pn}", "us": prefill_ms * 1e3, "TFLOPs": 2.0 * pm * pn * pk / (prefill_ms * 1e-3) / 1e12,
+               "traffic": ncu_traffic(f"scaled_mm_prefill_{pm}x{pk}x{pn}")}
+    del pa, pb, pc
     per_shape = {}
     for (k, n), cs in zip(SCALED_MM_KN, cases):
         def ours8(cs=cs):
@@ -785,7 +800,8 @@ def wl_scaled_mm(args, dev, rank, world, timer):
                 e2e_value=world * nbytes / (e2e_ms * 1e-3) / 1e12, e2e_ms=e2e_ms,
                 h2d=sum(h.numel() for h in host_a), d2h=sum(h.numel() * 2 for h in host_c), launches=len(cases),
                 roofline=roof, parity=parity,
-                extra={"library_ms_per_step": library_ms, "shapes_back_to_back": per_shape}, dtype="e4m3 operands, fp32 accumulate, bf16 out",
+                extra={"library_ms_per_step": library_ms, "shapes_back_to_back": per_shape, "prefill": prefill},
+                dtype="e4m3 operands, fp32 accumulate, bf16 out",
                 config={"workload": "scaled_mm", "tokens": m, "kn_shapes": len(SCALED_MM_KN),
                         "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
 

@@ -73,7 +73,7 @@ struct Args {
   int rows_per_dest;     // R: rows [d R, d R + R) of the product belong to rank d
 };
 
-constexpr int kPushPairs = 2, kPushCtas = 2 * kPushPairs;
+constexpr int kPushPairs = 4, kPushCtas = 2 * kPushPairs;
 constexpr int kPushPiece = 32768;  // bytes per bulk copy of the push CTAs (one operand stage)
 constexpr int kPushDepth = 4;      // loads a push CTA keeps in flight
 static_assert(kPushDepth < kStages, "a push CTA needs a buffer for the store in flight");
@@ -493,7 +493,7 @@ void fill_shape(Args& g, int64_t m, int64_t n, int64_t k_bytes) {
   g.k_bytes = int(k_bytes);
   g.m_tiles = int((m + kTile - 1) / kTile);
   g.n_tiles = int((n + kTile - 1) / kTile);
-  g.band = 8;
+  g.band = 16;
 }
 
 }  // namespace dense_pair

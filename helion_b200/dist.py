@@ -136,7 +136,7 @@ class FusedMatmulCollectives:
     ``helion_matmul_reduce_scatter`` (examples/distributed/matmul_reduce_scatter.py:118-140).
 
     The reference gathers with the copy engine on a second stream and lets a Triton matmul wait on progress
-    flags; here the GEMM kernel itself carries four CTAs that push the local shard to every rank and count
+    flags; here the GEMM kernel itself carries eight CTAs that push the local shard to every rank and count
     arrivals on the destination, while its other CTAs take the row tiles in arrival order.  For the
     reduce-scatter the GEMM's epilogue stores every tile into the owner's receive buffer; a barrier kernel and
     a slot reduction (rank order, fp32) follow.  Symmetric buffers are allocated on first use per shape.

@@ -428,10 +428,10 @@ int hb200_dense_matmul(const void* a, const void* b, void* c, int64_t m, int64_t
  * c [world * rows_local, N] = gathered a . b^T.  a_shard: this rank's rows [rows_local, K], contiguous.
  * gather_ptrs[i] / progress_ptrs[i]: rank i's gather buffer [world * rows_local, K] (contiguous) and its arrival
  * counters (uint32 [world * splits], zero before the first call, never reset), as mapped into this process
- * (symmetric memory); entry `rank` is this rank's own.  Four CTAs of the kernel copy the shard, in `splits` chunks,
+ * (symmetric memory); entry `rank` is this rank's own.  Eight CTAs of the kernel copy the shard, in `splits` chunks,
  * into every rank's buffer and count arrivals on the destination; the other CTAs take the row tiles in arrival
  * order and wait (bounded, system-scope acquire) for a chunk's counter before its first load.  call_number counts
- * the calls on this buffer set from 1: a chunk has landed when its counter reads 4 * call_number.  All ranks call
+ * the calls on this buffer set from 1: a chunk has landed when its counter reads 8 * call_number.  All ranks call
  * with the same shapes and call_number; the caller puts a barrier between calls (a rank must not overwrite a peer's
  * buffer while the peer still reads it).  (rows_local / splits) % 256 == 0, K % 8 == 0, N >= 256, ldc % 8 == 0. */
 int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, void* const* progress_ptrs, const void* b, void* c,
