@@ -393,8 +393,8 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int j = 0; j < 32; ++j) {
           const float v = is_int ? __int2float_rn(int(r[h][j])) : __uint_as_float(r[h][j]);
           const float sb = __shfl_sync(0xffffffffu, sb_l[h], j);
-          o[j] = cast_out<OutT>(sb * (sa * v));
-          if (bias != nullptr) o[j] = cast_out<OutT>(widen(o[j]) + __shfl_sync(0xffffffffu, bias_l[h], j));
+          o[j] = cast_out<OutT>(__fmul_rn(sb, __fmul_rn(sa, v)));  // no contraction with the bias add below
+          if (bias != nullptr) o[j] = cast_out<OutT>(__fadd_rn(widen(o[j]), __shfl_sync(0xffffffffu, bias_l[h], j)));
         }
         if constexpr (sizeof(OutT) == 2) {
           // a box of 32 rows x 32 columns (64 bytes per row, 64-byte swizzle) through this warp's staging buffer

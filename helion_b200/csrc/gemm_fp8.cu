@@ -333,8 +333,8 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           for (int j = 0; j < 16; ++j) {
             const int m_idx = m0 + c0 + j;
             const float sa = g.scale_a_per_row ? (m_idx < g.m ? __ldg(g.scale_a + m_idx) : 0.f) : sa_all;
-            OutT o = from_float<OutT>(sb * (sa * wide(v[j], is_int)));
-            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
+            OutT o = from_float<OutT>(__fmul_rn(sb, __fmul_rn(sa, wide(v[j], is_int))));
+            if (bias) o = from_float<OutT>(__fadd_rn(as_float(o), bias_n));
             turn[j * 32 + lane] = o;
           }
           __syncwarp();
@@ -356,8 +356,8 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           const int m_idx = m0 + c0 + j;
           if (m_idx < g.m) {
             const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : sa_all;
-            OutT o = from_float<OutT>(sb * (sa * wide(v[j], is_int)));
-            if (bias) o = from_float<OutT>(as_float(o) + bias_n);
+            OutT o = from_float<OutT>(__fmul_rn(sb, __fmul_rn(sa, wide(v[j], is_int))));
+            if (bias) o = from_float<OutT>(__fadd_rn(as_float(o), bias_n));
             out[int64_t(m_idx) * g.ldc + n_idx] = o;
           }
         }
@@ -483,8 +483,8 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         const int m_idx = c_m0 + i * CLUSTER;
         if (m_idx < g.m) {
           const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : c_sa_all;
-          OutT o = from_float<OutT>(c_sb * (sa * wide(v, format == 2)));
-          if (bias) o = from_float<OutT>(as_float(o) + c_bias);
+          OutT o = from_float<OutT>(__fmul_rn(c_sb, __fmul_rn(sa, wide(v, format == 2))));
+          if (bias) o = from_float<OutT>(__fadd_rn(as_float(o), c_bias));
           out[int64_t(m_idx) * g.ldc] = o;
         }
       }
