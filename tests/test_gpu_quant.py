@@ -194,6 +194,24 @@ def test_nvfp4_quantiser_tie_cases():
     assert count_diff(codes, co) == 0 and count_diff(scales, so) == 0
 
 
+def test_nvfp4_quantiser_code_rule_on_every_bf16_value_up_to_six():
+    """Every bf16 value in [-6, 6] (both zeros, denormals, every tie and its neighbours), fifteen per block beside
+    a 6.0 that pins the block's decoded scale to one: the codes are the oracle's.  Blocks that hold a tie or -0.0
+    take the kernel's slow path group by group, all others the hardware conversion."""
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16)
+    every = bits.view(torch.bfloat16)
+    vals = every[torch.isfinite(every.float()) & (every.float().abs() <= 6.0)]
+    pad = (-vals.numel()) % (15 * 8)  # whole rows of eight blocks; the filler repeats the first values
+    vals = torch.cat([vals, vals[:pad]])
+    x = torch.cat([vals.reshape(-1, 15), torch.full((vals.numel() // 15, 1), 6.0, dtype=torch.bfloat16)], dim=1)
+    x = x.reshape(-1, 8 * 16).contiguous()  # eight blocks per row
+    g = torch.tensor(1.0 / 448.0)
+    codes, scales, _ = hb.nvfp4_quantize(x.to(DEV), g.to(DEV))
+    co, so, _ = O.nvfp4_quantize(x, g)
+    assert count_diff(scales, so) == 0
+    assert count_diff(codes, co) == 0
+
+
 # ------------------------------------------------------------------ sibling producers
 def run_dyn(x, ub=None):
     t, h = x.shape
