@@ -136,7 +136,8 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
 // shared memory (distributed shared memory: remote stores, nothing waits on them), and after one cluster
 // barrier every owner adds up its columns from local shared memory in rank order.  No workspace, no counters,
 // no trip through L2.
-template <typename OutT, int CLUSTER>  // CLUSTER: CTAs per tile (2, 4 or 8) in the cluster form, 0 otherwise
+// CLUSTER: CTAs per tile (2, 4 or 8) in the cluster form, 0 otherwise.  INT8: int8 operands (format 2), int32 accumulation.
+template <typename OutT, int CLUSTER, bool INT8>
 __global__ void __launch_bounds__(kFp8Threads, 1)
 fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                      const Fp8Args g, const int format) {
@@ -191,13 +192,26 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   };
   const int acc_stride = g.cols < 32 ? 32 : g.cols;
 
-  // one stage of (tile, K block): the stage's barrier is told the bytes, both boxes are requested
-  auto issue = [&](int s, int tile, int kb) {
+  // one stage of (tile, K block): the stage's barrier is told the bytes, both boxes are requested.  The weights do
+  // not depend on the kernel before this one on the stream, the tokens may: `part` 1 requests the weights only
+  // (and arms the barrier for both), 2 the tokens only, 3 both.
+  auto issue = [&](int s, int tile, int kb, int part) {
     const uint32_t bar = smem_u32(&full_bar[s]);
     uint8_t* st = smem + s * g.stage_bytes;
-    mbar_arrive_expect_tx(bar, uint32_t(kFp8WBytes + g.cols * 128));
-    tma_load_2d(smem_u32(st), &tmap_w, kb * 128, (tile / g.m_chunks) * 128, bar);
-    tma_load_2d(smem_u32(st + kFp8WBytes), &tmap_x, kb * 128, (tile % g.m_chunks) * g.cols, bar);
+    if (part & 1) {
+      mbar_arrive_expect_tx(bar, uint32_t(kFp8WBytes + g.cols * 128));
+      tma_load_2d(smem_u32(st), &tmap_w, kb * 128, (tile / g.m_chunks) * 128, bar);
+    }
+    if (part & 2) tma_load_2d(smem_u32(st + kFp8WBytes), &tmap_x, kb * 128, (tile % g.m_chunks) * g.cols, bar);
+  };
+  // the first ring of loads, requested before the main loop
+  auto first_ring = [&](int part) {
+    int it = 0;
+    for (int i = 0; i < work_count && it < stages; ++i) {
+      int tile, kb0, kb1;
+      work(i, tile, kb0, kb1);
+      for (int kb = kb0; kb < kb1 && it < stages; ++kb, ++it) issue(it, tile, kb, part);
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -211,13 +225,9 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
     *abort_flag = 0;
     fence_barrier_init();
-    // The ring is empty: its first round of loads goes out now, while tensor memory is still being set up.
-    int it = 0;
-    for (int i = 0; i < work_count && it < stages; ++i) {
-      int tile, kb0, kb1;
-      work(i, tile, kb0, kb1);
-      for (int kb = kb0; kb < kb1 && it < stages; ++kb, ++it) issue(it, tile, kb);
-    }
+    // The ring is empty: the weights of its first round are requested now, while tensor memory is still being set
+    // up and (when this kernel was launched as a programmatic dependent) while the kernel before it still runs.
+    first_ring(1);
   }
   // two accumulators of acc_stride columns; the allocation is a power of two of at least 32 columns
   uint32_t tmem_cols = 32;
@@ -230,6 +240,13 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: kernels queued behind this one may be scheduled from now on (every CTA of this
+  // grid is resident once all have got here, so they only take what this grid frees), and everything below that
+  // touches memory another kernel may have written, or writes memory another kernel may still read, waits for the
+  // kernel before this one to complete.  Both are no-ops in an ordinary launch.
+  if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) first_ring(2);  // the tokens of the first round
   // CLUSTER: a CTA's shared memory may be written by its peers only once it runs.  Everybody arrives here;
   // the wait for the others sits in front of the first remote store, behind the whole main loop.
   bool peers_running = false;
@@ -255,12 +272,12 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         if (it < uint32_t(stages)) continue;  // requested during set-up
         const int s = it % stages;
         if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        if (elect_one()) issue(s, tile, kb);
+        if (elect_one()) issue(s, tile, kb, 3);
         __syncwarp();
       }
     }
   } else if (warp == 1) {
-    const bool is_int = format == 2;
+    constexpr bool is_int = INT8;
     const uint32_t idesc = is_int ? make_idesc_i8(128, g.cols) : make_idesc_f8(128, g.cols, format);
     uint32_t it = 0, sc = 0;
     bool ok = true;
@@ -296,7 +313,7 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
   } else {
     const int quarter = warp & 3;
-    const bool is_int = format == 2;
+    constexpr bool is_int = INT8;
     const int r_in = quarter * 32 + lane;  // weight row inside the tile = accumulator lane
     OutT* out = static_cast<OutT*>(g.out);
     const OutT* bias = static_cast<const OutT*>(g.bias);
@@ -479,11 +496,11 @@ fp8_scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         for (int q = 0; q < CLUSTER; ++q) t[q] = mine[(q * per + i) * 128];
         float v = t[0];
 #pragma unroll
-        for (int q = 1; q < CLUSTER; ++q) v = add_acc(v, t[q], format == 2);  // rank order = ascending K: a fixed summation order
+        for (int q = 1; q < CLUSTER; ++q) v = add_acc(v, t[q], INT8);  // rank order = ascending K: a fixed summation order
         const int m_idx = c_m0 + i * CLUSTER;
         if (m_idx < g.m) {
           const float sa = g.scale_a_per_row ? __ldg(g.scale_a + m_idx) : c_sa_all;
-          OutT o = from_float<OutT>(__fmul_rn(c_sb, __fmul_rn(sa, wide(v, format == 2))));
+          OutT o = from_float<OutT>(__fmul_rn(c_sb, __fmul_rn(sa, wide(v, INT8))));
           if (bias) o = from_float<OutT>(__fadd_rn(as_float(o), c_bias));
           out[int64_t(m_idx) * g.ldc] = o;
         }
@@ -526,8 +543,8 @@ int max_active_clusters(int size) {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || size < 1 || size > 8) return 0;
   std::lock_guard<std::mutex> lock(mu);
   if (cached[dev][size] == 0) {
-    auto kernel = size == 8 ? fp8_scaled_mm_kernel<__nv_bfloat16, 8>
-                  : size == 4 ? fp8_scaled_mm_kernel<__nv_bfloat16, 4> : fp8_scaled_mm_kernel<__nv_bfloat16, 2>;
+    auto kernel = size == 8 ? fp8_scaled_mm_kernel<__nv_bfloat16, 8, false>
+                  : size == 4 ? fp8_scaled_mm_kernel<__nv_bfloat16, 4, false> : fp8_scaled_mm_kernel<__nv_bfloat16, 2, false>;
     const size_t smem = 200 * 1024;
     int n = 0;
     cudaLaunchConfig_t cfg = {};
@@ -609,12 +626,12 @@ int device_sms() {
   return sms > 0 ? sms : 148;
 }
 
-template <typename OutT>
-int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
-               cudaStream_t s) {
+template <typename OutT, bool INT8>
+int launch_fp8_kind(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
+                    cudaStream_t s) {
   if (p.cluster) {
-    auto kernel = p.cluster == 8 ? fp8_scaled_mm_kernel<OutT, 8>
-                  : p.cluster == 4 ? fp8_scaled_mm_kernel<OutT, 4> : fp8_scaled_mm_kernel<OutT, 2>;
+    auto kernel = p.cluster == 8 ? fp8_scaled_mm_kernel<OutT, 8, INT8>
+                  : p.cluster == 4 ? fp8_scaled_mm_kernel<OutT, 4, INT8> : fp8_scaled_mm_kernel<OutT, 2, INT8>;
     const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + size_t(p.cols) * 512 + 1024;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
@@ -622,21 +639,42 @@ int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, c
     cfg.blockDim = dim3(kFp8Threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = unsigned(p.cluster);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     if (cudaLaunchKernelEx(&cfg, kernel, tw, tx, g, format) != cudaSuccess) return HB200_ERR_CUDA;
     return HB200_OK;
   }
-  auto kernel = fp8_scaled_mm_kernel<OutT, 0>;
+  // launched as a programmatic dependent of whatever precedes it on the stream: resident early, its first weights
+  // on their way, waiting (griddepcontrol.wait) for that kernel's completion before anything else
+  auto kernel = fp8_scaled_mm_kernel<OutT, 0, INT8>;
   const size_t smem = size_t(p.stages) * p.stage_bytes + 256 + 4 * 2048 + 1024;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return HB200_ERR_CUDA;
-  kernel<<<p.grid, kFp8Threads, smem, s>>>(tw, tx, g, format);
-  return launch_status();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(p.grid), 1, 1);
+  cfg.blockDim = dim3(kFp8Threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, tw, tx, g, format) != cudaSuccess) return HB200_ERR_CUDA;
+  return HB200_OK;
+}
+
+template <typename OutT>
+int launch_fp8(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Args& g, const Fp8Plan& p, int format,
+               cudaStream_t s) {
+  return format == 2 ? launch_fp8_kind<OutT, true>(tw, tx, g, p, format, s)
+                     : launch_fp8_kind<OutT, false>(tw, tx, g, p, format, s);
 }
 
 }  // namespace
