@@ -66,7 +66,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_bf16in_rs": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, c_float, _P],
     "hb200_tp_reduce_partials": [_P, _P, _I64, _I64, _I64, _I64, _P],
     "hb200_dense_matmul": [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, c_int, _P],
-    "hb200_ag_matmul": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, ctypes.c_uint32, c_int, _P],
+    "hb200_ag_matmul": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, ctypes.c_uint32, c_int, c_int, _P],
     "hb200_matmul_rs": [_P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, c_int, _P],
     "hb200_reduce_slots": [_P, _P, _I64, _I64, _I64, _I64, c_int, _P],
     "hb200_nvfp4_gemv_tc_workspace_bytes": [_I64, _I64, _I64, _I64],

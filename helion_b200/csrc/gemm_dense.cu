@@ -13,17 +13,18 @@
 // neither CTA exits while its peer may still touch its shared memory or barriers.
 //
 // MODE 1, all-gather + matmul (examples/distributed/all_gather_matmul.py:36-141): every rank holds rows_local rows
-// of a; c = gathered a . b.  The last kPushPairs CTA pairs of the grid do not compute: they copy this rank's shard,
-// chunk by chunk, into every peer's gather buffer (bulk loads into shared memory, several in flight, each followed
-// by a bulk store to peer memory; peers in ring order) and, when a chunk has landed, add one arrival per push CTA to
-// that chunk's progress counter on the destination (a system-scope release reduction); the local copy of the shard
-// comes last.  The compute pairs take the tiles in the order the chunks arrive (own rows first, read from the shard
-// itself, then the ring backwards); before the first load of a peer chunk's rows the producer warp waits
-// (system-scope acquire, bounded) until the counter shows all arrivals of this call.  Counters only grow: call
-// number s (1, 2, ...) expects kPushCtas * s arrivals, so nothing is reset between calls; the caller orders calls
-// with a barrier, since a rank may not overwrite a peer's gather buffer while the peer still reads it.  A push CTA
-// never waits for anything remote, and all CTAs of the grid are resident at once (one per SM), so ranks cannot
-// deadlock one another.
+// of a; c = gathered a . b.  The two warps of every CTA that have no role in the GEMM do the gather: each copies its
+// slice of every chunk of this rank's shard into every peer's gather buffer (16-byte loads from local memory, 16-byte
+// stores to peer memory, several in flight per lane; peers in ring order) and, when its stores of a chunk to a
+// destination are done, adds one arrival to that chunk's progress counter there (a system-scope release
+// reduction); the local copy of the shard comes last.  Spread over all SMs the copy needs no SM of its own and is
+// not held back by what a single SM can keep in flight towards a peer.  The GEMM takes the tiles in the order the
+// chunks arrive (own rows first, read from the shard itself, then the ring backwards); before the first load of a
+// peer chunk's rows the producer warp waits (system-scope acquire, bounded) until the counter shows all arrivals of
+// this call.  Counters only grow: call number s (1, 2, ...) expects s arrivals from every pushing warp, so nothing is
+// reset between calls; the caller orders calls with a barrier, since a rank may not overwrite a peer's gather buffer
+// while the peer still reads it.  A pushing warp never waits for anything remote, and all CTAs of the grid are
+// resident at once (one per SM), so ranks cannot deadlock one another.
 //
 // MODE 2, matmul + reduce-scatter (examples/distributed/matmul_reduce_scatter.py:37-115): every rank holds a K
 // shard; the tile rows [d R, d R + R) of its partial product, rounded to the output type as the reference rounds
@@ -68,15 +69,13 @@ struct Args {
   uint8_t* gather[8];    // every rank's gather buffer [world * rows_local, k_bytes], contiguous, as mapped here
   uint32_t* progress[8]; // every rank's arrival counters [world * splits]
   int rank, world, splits, rows_local;
-  uint32_t arrivals;     // what a counter shows once a chunk of this call has landed: kPushCtas * call number
+  uint32_t arrivals;     // what a counter shows once a chunk of this call has landed
+  int push;              // the kernel's own warps do the gather (else somebody else fills the buffer and the counters)
   // MODE 2 (matmul + reduce-scatter)
   int rows_per_dest;     // R: rows [d R, d R + R) of the product belong to rank d
 };
 
-constexpr int kPushPairs = 4, kPushCtas = 2 * kPushPairs;
-constexpr int kPushPiece = 32768;  // bytes per bulk copy of the push CTAs (one operand stage)
-constexpr int kPushDepth = 4;      // loads a push CTA keeps in flight
-static_assert(kPushDepth < kStages, "a push CTA needs a buffer for the store in flight");
+constexpr int kPushUnroll = 8;  // 16-byte loads a lane of a pushing warp keeps in flight
 
 struct OutMaps {
   // MODE 2: rank d's receive buffer [world * R, N]; otherwise dest[0] is c.  MODE 1: dest[1] maps this rank's shard
@@ -179,10 +178,9 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1;
-  const int num_pairs = (gridDim.x >> 1) - (MODE == 1 ? kPushPairs : 0);  // pairs that compute
-  const bool pusher = MODE == 1 && pair >= num_pairs;
+  const int num_pairs = gridDim.x >> 1;
   const int num_kb = (g.k_bytes + 127) / 128;
-  const int num_tiles = pusher ? 0 : g.m_tiles * g.n_tiles;
+  const int num_tiles = g.m_tiles * g.n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -208,60 +206,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (pusher) {
-    // ------------------------------------------------------------ all-gather push (one thread per CTA)
-    // Push CTA q of kPushCtas copies bytes [q, q + 1) / kPushCtas of every chunk of the shard to every rank, through
-    // the operand ring's shared memory: a bulk load per piece, then a bulk store to the destination.  When its
-    // part of a chunk has landed on a destination (the stores' writes are complete) it adds one arrival there.
-    if (threadIdx.x == 0) {
-      const int q = (pair - num_pairs) * 2 + int(rank);
-      const int64_t chunk_bytes = int64_t(g.rows_local / g.splits) * g.k_bytes;
-      const int64_t part0 = (chunk_bytes / 16 * q / kPushCtas) * 16, part1 = (chunk_bytes / 16 * (q + 1) / kPushCtas) * 16;
-      uint32_t it = 0;  // pieces requested so far, over the whole kernel: buffer it % kStages, phase (it / kStages) & 1
-      bool ok = true;
-      // bytes [part0, part1) of `src` to `dst`: kPushDepth loads stay in flight, a piece's store follows its load
-      auto copy_part = [&](const uint8_t* src, uint8_t* dst) {
-        const int pieces = int((part1 - part0 + kPushPiece - 1) / kPushPiece);
-        const uint32_t base = it;
-        for (int i = 0; i < pieces + kPushDepth && ok; ++i) {
-          if (i < pieces) {
-            const int64_t off = part0 + int64_t(i) * kPushPiece;
-            const uint32_t bytes = uint32_t(min(int64_t(kPushPiece), part1 - off));
-            const int s = (base + i) % kStages;
-            // the store that last read this buffer (kStages pieces ago) has finished reading it: stores leave in
-            // order, kPushDepth of the later ones have not been issued yet
-            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStages - kPushDepth - 1) : "memory");
-            const uint32_t bar = smem_u32(&full_bar[s]);
-            mbar_arrive_expect_tx(bar, bytes);
-            bulk_load(smem_u32(smem + s * kStageBytes), src + off, bytes, bar);
-          }
-          if (i >= kPushDepth) {
-            const int j = i - kPushDepth;
-            const int64_t off = part0 + int64_t(j) * kPushPiece;
-            const uint32_t bytes = uint32_t(min(int64_t(kPushPiece), part1 - off));
-            const int s = (base + j) % kStages;
-            if (!mbar_wait(smem_u32(&full_bar[s]), ((base + j) / kStages) & 1, abort_flag)) { ok = false; break; }
-            bulk_store(dst + off, smem_u32(smem + s * kStageBytes), bytes);
-            bulk_commit_group();
-          }
-        }
-        it = base + pieces;
-        bulk_wait_group0();  // the writes themselves, not only the reads of shared memory
-      };
-      const int64_t my_rows_off = int64_t(g.rank) * g.rows_local * g.k_bytes;
-      for (int c = 0; c < g.splits && ok; ++c) {
-        for (int step = 1; step < g.world && ok; ++step) {
-          const int d = (g.rank + step) % g.world;  // the ring, the next rank first
-          copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[d] + my_rows_off + int64_t(c) * chunk_bytes);
-          __threadfence_system();
-          if (ok) red_release_sys_add(g.progress[d] + g.rank * g.splits + c, 1u);
-        }
-      }
-      // this rank's own copy of its rows comes last: its tiles read the shard itself
-      for (int c = 0; c < g.splits && ok; ++c)
-        copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[g.rank] + my_rows_off + int64_t(c) * chunk_bytes);
-    }
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
     uint32_t it = 0;
     bool ok = true;
@@ -309,7 +254,7 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer (leader only)
-    if (leader && !pusher) {
+    if (leader) {
       const bool is_int = format == 2, is_f16 = format >= 3;
       // fp32 (or int32) accumulator at bits 4-5, operand formats at bits 7-9 and 10-12 (kind::f8f6f4: 0 e4m3, 1 e5m2;
       // kind::i8: 1 signed; kind::f16: 0 fp16, 1 bf16), N >> 3 at bit 17, M >> 4 at bit 24
@@ -347,7 +292,45 @@ dense_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         __syncwarp();
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ all-gather push (warps 2 and 3 of every CTA)
+    if (MODE == 1 && g.push) {
+      const int pw = int(blockIdx.x) * 2 + (warp - 2), n_pw = int(gridDim.x) * 2;
+      const int64_t chunk_bytes = int64_t(g.rows_local / g.splits) * g.k_bytes;  // a multiple of 16
+      const int64_t part0 = (chunk_bytes / 16 * pw / n_pw) * 16, part1 = (chunk_bytes / 16 * (pw + 1) / n_pw) * 16;
+      auto copy_part = [&](const uint8_t* src, uint8_t* dst) {
+        for (int64_t off = part0 + lane * 16; off < part1; off += 32 * 16 * kPushUnroll) {
+          uint4 v[kPushUnroll];
+#pragma unroll
+          for (int u = 0; u < kPushUnroll; ++u) {
+            const int64_t o = off + int64_t(u) * 32 * 16;
+            if (o < part1)
+              asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + o));
+          }
+#pragma unroll
+          for (int u = 0; u < kPushUnroll; ++u) {
+            const int64_t o = off + int64_t(u) * 32 * 16;
+            if (o < part1)
+              asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + o), "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w) : "memory");
+          }
+        }
+      };
+      const int64_t my_rows_off = int64_t(g.rank) * g.rows_local * g.k_bytes;
+      for (int c = 0; c < g.splits; ++c) {
+        for (int step = 1; step < g.world; ++step) {
+          const int d = (g.rank + step) % g.world;  // the ring, the next rank first
+          copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[d] + my_rows_off + int64_t(c) * chunk_bytes);
+          __threadfence_system();  // every lane's stores, before the arrival that lane 0 publishes
+          __syncwarp();
+          if (lane == 0) red_release_sys_add(g.progress[d] + g.rank * g.splits + c, 1u);
+        }
+      }
+      // this rank's own copy of its rows comes last: its tiles read the shard itself
+      for (int c = 0; c < g.splits; ++c)
+        copy_part(g.shard + int64_t(c) * chunk_bytes, g.gather[g.rank] + my_rows_off + int64_t(c) * chunk_bytes);
+    }
+  } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     // Sixteen warps: warp w reads lane quarter w % 4 (the only one it may) and the 64 columns [(w - 4) / 4 * 64, +64)
     // into registers with two loads, hands the accumulator back, then scales, casts, adds the bias and stores.
@@ -581,7 +564,7 @@ extern "C" int hb200_dense_matmul(const void* a, const void* b, void* c, int64_t
 
 extern "C" int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, void* const* progress_ptrs, const void* b,
                                void* c, int64_t rows_local, int64_t n, int64_t k, int64_t ldb, int64_t ldc, int64_t world,
-                               int64_t rank, int64_t splits, uint32_t call_number, int is_bf16, void* stream) {
+                               int64_t rank, int64_t splits, uint32_t call_number, int push, int is_bf16, void* stream) {
   using namespace hb200;
   using namespace hb200::dense_pair;
   if (!a_shard || !gather_ptrs || !progress_ptrs || !b || !c) return HB200_ERR_INVALID_ARGUMENT;
@@ -596,9 +579,9 @@ extern "C" int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, vo
   const int64_t m = rows_local * world;
   if (m > 0x3fffff00 || n > 0x3fffff00 || k > 0x3fffff00 || world * splits > 4096) return HB200_ERR_UNSUPPORTED;
   const int sms = device_sms();
-  if (sms / 2 <= kPushPairs) return HB200_ERR_UNSUPPORTED;
   Args g{};
   for (int i = 0; i < world; ++i) {
+    if (!push && i != rank) continue;  // only this rank's own buffer and counters are touched
     if (!gather_ptrs[i] || !progress_ptrs[i] || reinterpret_cast<uintptr_t>(gather_ptrs[i]) % 16 ||
         reinterpret_cast<uintptr_t>(progress_ptrs[i]) % 4)
       return HB200_ERR_INVALID_ARGUMENT;
@@ -622,13 +605,16 @@ extern "C" int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, vo
   g.world = int(world);
   g.splits = int(splits);
   g.rows_local = int(rows_local);
-  g.arrivals = uint32_t(kPushCtas) * call_number;
   const int tiles = g.m_tiles * g.n_tiles;
-  const int compute = tiles < sms / 2 - kPushPairs ? tiles : sms / 2 - kPushPairs;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  g.push = push != 0;
+  // pushed by the kernels: two pushing warps in each of the 2 * pairs CTAs, on every rank alike, one arrival each per
+  // call; filled from outside: whoever fills a chunk then writes the call number into its counter
+  g.arrivals = push ? uint32_t(4 * pairs) * call_number : call_number;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int format = is_bf16 ? 4 : 3;
-  if (is_bf16) return launch_kernel<__nv_bfloat16, 1>(ta, tb, om, g, format, compute + kPushPairs, s);
-  return launch_kernel<__half, 1>(ta, tb, om, g, format, compute + kPushPairs, s);
+  if (is_bf16) return launch_kernel<__nv_bfloat16, 1>(ta, tb, om, g, format, pairs, s);
+  return launch_kernel<__half, 1>(ta, tb, om, g, format, pairs, s);
 }
 
 extern "C" int hb200_matmul_rs(const void* a, const void* b, void* const* recv_ptrs, int64_t m, int64_t n, int64_t k,

@@ -424,19 +424,25 @@ int hb200_tp_reduce_partials(const void* partials_f32, void* out_bf16, int64_t w
 int hb200_dense_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int64_t lda,
                        int64_t ldb, int64_t ldc, int is_bf16, void* stream);
 
-/* All-gather + matmul in one kernel (helion_all_gather_matmul, examples/distributed/all_gather_matmul.py:145-196):
+/* All-gather + matmul (helion_all_gather_matmul, examples/distributed/all_gather_matmul.py:145-196):
  * c [world * rows_local, N] = gathered a . b^T.  a_shard: this rank's rows [rows_local, K], contiguous.
- * gather_ptrs[i] / progress_ptrs[i]: rank i's gather buffer [world * rows_local, K] (contiguous) and its arrival
+ * gather_ptrs[i] / progress_ptrs[i]: rank i's gather buffer [world * rows_local, K] (contiguous) and its progress
  * counters (uint32 [world * splits], zero before the first call, never reset), as mapped into this process
- * (symmetric memory); entry `rank` is this rank's own.  Eight CTAs of the kernel copy the shard, in `splits` chunks,
- * into every rank's buffer and count arrivals on the destination; the other CTAs take the row tiles in arrival
- * order and wait (bounded, system-scope acquire) for a chunk's counter before its first load.  call_number counts
- * the calls on this buffer set from 1: a chunk has landed when its counter reads 8 * call_number.  All ranks call
- * with the same shapes and call_number; the caller puts a barrier between calls (a rank must not overwrite a peer's
- * buffer while the peer still reads it).  (rows_local / splits) % 256 == 0, K % 8 == 0, N >= 256, ldc % 8 == 0. */
+ * (symmetric memory); entry `rank` is this rank's own.  The GEMM takes the row tiles in arrival order (own rows
+ * first, read from a_shard itself) and waits (bounded, system-scope acquire) for a chunk's counter before the first
+ * load of its rows.  call_number counts the calls on this buffer set from 1.  Two ways to fill the buffers:
+ *  - push != 0, one kernel does everything: the two warps of every CTA that have no role in the GEMM copy this
+ *    rank's shard, in `splits` chunks, into every peer's buffer (stores to peer memory only) and add one arrival per
+ *    warp to the chunk's counter there; a chunk has landed when its counter reads (pushing warps) * call_number.
+ *    All ranks call with the same shapes and call_number.
+ *  - push == 0, the reference's structure: somebody else (copy engines on another stream) fills this rank's buffer
+ *    chunk by chunk and, after a chunk, writes call_number into its counter (e.g. a stream memory write); only
+ *    entry `rank` of the two pointer arrays is read.
+ * Either way the caller puts a barrier between calls (a rank must not overwrite a buffer that is still being
+ * read).  (rows_local / splits) % 256 == 0, K % 8 == 0, N >= 256, ldc % 8 == 0. */
 int hb200_ag_matmul(const void* a_shard, void* const* gather_ptrs, void* const* progress_ptrs, const void* b, void* c,
                     int64_t rows_local, int64_t n, int64_t k, int64_t ldb, int64_t ldc, int64_t world, int64_t rank,
-                    int64_t splits, uint32_t call_number, int is_bf16, void* stream);
+                    int64_t splits, uint32_t call_number, int push, int is_bf16, void* stream);
 
 /* Matmul + reduce-scatter, first half (matmul_reduce_scatter_kernel, examples/distributed/matmul_reduce_scatter.py:
  * 37-115): a [M, K_local] . b^T (b K-major [N, K_local]) is this rank's partial product; the epilogue rounds it to the

@@ -108,10 +108,11 @@ def _two_rank_worker(rank: int, world: int, port: int, result):
         rows, k, n = 1024, 2048, 1536
         g = torch.Generator().manual_seed(31)
         b = (torch.randn(n, k, generator=g) / k**0.5).to(torch.bfloat16).to(dev).t()
-        for step in range(3):
+        for step in range(6):
             full = torch.randn(world * rows, k, generator=g).to(torch.bfloat16).to(dev)
             shard = full[rank * rows : (rank + 1) * rows].contiguous()
-            gathered, c = fm.all_gather_matmul(shard, b, splits_per_rank=2)
+            # the copy engines pull the shards on a second stream, or the GEMM's own warps push them
+            gathered, c = fm.all_gather_matmul(shard, b, splits_per_rank=2, gather=("copy_engine", "kernel")[step % 2])
             torch.cuda.synchronize()
             ok &= bool(torch.equal(gathered, full))
             ok &= bool(torch.equal(c, D.dense_matmul(full, b)))
