@@ -20,6 +20,7 @@ from .layouts import swizzle_fp8_scales
 from .layouts import swizzled_scale_numel
 from .layouts import swizzled_scale_offsets
 from .layouts import unswizzle_fp8_scales
+from .ops import HostPipelinedMatmul
 from .ops import nvfp4_gemv_bf16in
 from .ops import nvfp4_gemv_bf16in_batched
 from .ops import nvfp4_gemv_fp4in

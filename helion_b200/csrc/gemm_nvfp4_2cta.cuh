@@ -81,6 +81,8 @@ struct PairArgs {
   float* row_amax;
 };
 
+constexpr int kBand = 32;  // row tiles per band of the dense tile order (8192 rows: 16384 x 8192 x 8192 went from 450 to 385 us)
+
 struct PairTile {
   int m_blk, n_blk, group;
   bool valid;
@@ -96,8 +98,13 @@ __device__ __forceinline__ PairTile decode_pair_tile(const PairArgs& g, int tile
     t.group = ti.x;
     t.valid = ti.x >= 0 && ti.y > 0;
   } else {
-    t.m_blk = tile % g.m_tiles;
-    t.n_blk = tile / g.m_tiles;
+    // bands of kBand row tiles; inside a band the row tile runs fastest, then the column tile: the 74 pairs that work
+    // at the same time share a few row tiles of A and a few column tiles of B, which stay in L2
+    const int per_band = kBand * g.n_tiles;
+    const int b = tile / per_band, r = tile - b * per_band;
+    const int rows_here = min(kBand, g.m_tiles - b * kBand);
+    t.n_blk = r / rows_here;
+    t.m_blk = b * kBand + (r - t.n_blk * rows_here);
     t.group = 0;
     t.valid = true;
   }

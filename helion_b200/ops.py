@@ -599,6 +599,62 @@ def nvfp4_scaled_matmul(
     )
 
 
+class HostPipelinedMatmul:
+    """``host_out = (quantise(host_a) @ W^T) * alpha`` for activations that live in pinned host memory: the rows are
+    cut into chunks, and the host-to-device copy of chunk i + 1, the quantiser and NVFP4 GEMM of chunk i and the
+    device-to-host copy of chunk i - 1 run at the same time on three streams (PCIe is full duplex, so the two copies
+    overlap each other as well as the kernels).  Every output row is what ``nvfp4_quantize`` + ``nvfp4_scaled_matmul``
+    give for the whole matrix, bit for bit: rows are independent and the tensor-wide activation scale is given.
+
+    ``weight_packed [N, K/2]`` / ``weight_scale`` are device tensors as for ``nvfp4_scaled_matmul``; ``a_global_scale``
+    a one-element fp32 device tensor (the activation tensor's ``amax / (6 * 448)``); ``alpha`` the product of both
+    global scales.  Buffers and streams are made once for a shape.  No counterpart in the reference (its operators
+    take device tensors)."""
+
+    def __init__(self, weight_packed: Tensor, weight_scale: Tensor, a_global_scale: Tensor, alpha: float, rows: int,
+                 chunks: int = 4):
+        _require_cuda(weight_packed, weight_scale, a_global_scale)
+        if rows % chunks or (rows // chunks) % 256:
+            raise ValueError("rows must split into chunks that are multiples of 256 rows")
+        dev = weight_packed.device
+        self.w, self.ws, self.ga, self.alpha = weight_packed, weight_scale, a_global_scale, float(alpha)
+        self.rows, self.chunks, self.chunk = rows, chunks, rows // chunks
+        self.k = weight_packed.shape[1] * 2
+        self.a_buf = [torch.empty(self.chunk, self.k, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.copy_in = torch.cuda.Stream(device=dev)
+        self.copy_out = torch.cuda.Stream(device=dev)
+        self.a_free = [torch.cuda.Event() for _ in range(2)]
+
+    def __call__(self, host_a: Tensor, host_out: Tensor) -> None:
+        """Enqueues the whole pipeline; on return the current stream waits for the last copy to the host."""
+        if host_a.shape != (self.rows, self.k) or host_a.dtype is not torch.bfloat16 or not host_a.is_pinned():
+            raise ValueError("host_a must be a pinned bfloat16 [rows, K] tensor")
+        if host_out.shape[0] != self.rows or not host_out.is_pinned():
+            raise ValueError("host_out must be a pinned [rows, N] tensor")
+        main = torch.cuda.current_stream(self.w.device)
+        self.copy_in.wait_stream(main)
+        self.copy_out.wait_stream(main)
+        for i in range(self.chunks):
+            buf, lo = self.a_buf[i % 2], i * self.chunk
+            with torch.cuda.stream(self.copy_in):
+                if i >= 2:
+                    self.copy_in.wait_event(self.a_free[i % 2])  # the quantiser of chunk i - 2 has read this buffer
+                buf.copy_(host_a[lo : lo + self.chunk], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(self.copy_in)
+            main.wait_event(arrived)
+            codes, scales, _ = nvfp4_quantize(buf, self.ga)
+            self.a_free[i % 2].record(main)
+            y = nvfp4_scaled_matmul(codes, self.w.t(), scales, self.ws, host_out.dtype, alpha=self.alpha)
+            done = torch.cuda.Event()
+            done.record(main)
+            y.record_stream(self.copy_out)
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(done)
+                host_out[lo : lo + self.chunk].copy_(y, non_blocking=True)
+        main.wait_stream(self.copy_out)
+
+
 def nvfp4_w4a4_matmul(
     A_packed: Tensor, B_packed: Tensor, act_scale: Tensor, weight_scale: Tensor, alpha: float = 1.0  # noqa: N803
 ) -> Tensor:

@@ -105,3 +105,30 @@ def test_b_layout_variants_and_errors():
         hb.nvfp4_scaled_matmul(ad, bd[:, :32].t(), sad, sbd)
     with pytest.raises(ValueError, match="scale_b must contain"):
         hb.nvfp4_scaled_matmul(ad, bd.t(), sad, sbd[:-1])
+
+
+@pytest.mark.parametrize("chunks", [1, 2, 4])
+def test_host_pipelined_matmul_equals_the_resident_path(chunks):
+    """Activations in pinned host memory, rows in chunks over three streams: the same bits as quantising and
+    multiplying the whole matrix on the device; two calls in a row reuse the buffers."""
+    m, n, k = 1024, 512, 1024
+    g = torch.Generator().manual_seed(21)
+    w = torch.randn(n, k, generator=g) * 0.02
+    wp, ws, wg = O.nvfp4_quantize(w)
+    wp, ws = wp.to(DEV), ws.to(DEV)
+    pipe = None
+    for call in range(2):
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        ga = (a.float().abs().amax() / (6.0 * 448.0)).reshape(1).to(DEV)
+        alpha = float(ga) * float(wg)
+        pipe = hb.HostPipelinedMatmul(wp, ws, ga, alpha, m, chunks=chunks)  # scales change with the activations
+        host_a, host_out = a.pin_memory(), torch.full((m, n), float("nan"), dtype=torch.bfloat16).pin_memory()
+        pipe(host_a, host_out)
+        torch.cuda.synchronize()
+        codes, scales, _ = hb.nvfp4_quantize(a.to(DEV), ga)
+        want = hb.nvfp4_scaled_matmul(codes, wp.t(), scales, ws, alpha=alpha)
+        assert torch.equal(host_out.to(DEV), want)
+    with pytest.raises(ValueError):
+        hb.HostPipelinedMatmul(wp, ws, ga, alpha, m, chunks=8)  # 128-row chunks
+    with pytest.raises(ValueError):
+        pipe(a, host_out)  # not pinned
