@@ -96,14 +96,29 @@ def column_parallel_matmul(a_packed: Tensor, scale_a: Tensor, b_local: Tensor, s
 
 
 # ------------------------------------------------------------------ fused matmul + collective
-def dense_matmul(a: Tensor, b: Tensor, out: Tensor | None = None) -> Tensor:
-    """``a [M, K] @ b [K, N]`` in bf16 or fp16 on CTA pairs (256 x 256 tiles, fp32 accumulate); the one-GPU form of
-    the two fused kernels below.  ``b`` is taken K-major (``b.stride(0) == 1``, the weight stored ``[N, K]``);
-    anything else is copied into that layout first."""
+@torch.library.custom_op("helion_b200::dense_matmul_out", mutates_args=("out",))
+def _dense_matmul_op(a: Tensor, b_nk: Tensor, out: Tensor) -> None:
     from . import _lib
     from .ops import _require_cuda
 
-    _require_cuda(a, b)
+    _require_cuda(a, b_nk, out)
+    m, k = a.shape
+    n = b_nk.shape[0]
+    with torch.cuda.device(a.device):
+        _lib.call("hb200_dense_matmul", a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), m, n, k, a.stride(0),
+                  b_nk.stride(0), out.stride(0), int(a.dtype is torch.bfloat16),
+                  torch.cuda.current_stream(a.device).cuda_stream)
+
+
+@_dense_matmul_op.register_fake
+def _(a, b_nk, out):
+    return None
+
+
+def dense_matmul(a: Tensor, b: Tensor, out: Tensor | None = None) -> Tensor:
+    """``a [M, K] @ b [K, N]`` in bf16 or fp16 on CTA pairs (256 x 256 tiles, fp32 accumulate); the one-GPU form of
+    the two fused kernels below (``torch.ops.helion_b200.dense_matmul_out`` on the K-major operands).  ``b`` is taken
+    K-major (``b.stride(0) == 1``, the weight stored ``[N, K]``); anything else is copied into that layout first."""
     if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
         raise TypeError("dense_matmul takes bfloat16 or float16 operands of one type")
     m, k = a.shape
@@ -111,23 +126,26 @@ def dense_matmul(a: Tensor, b: Tensor, out: Tensor | None = None) -> Tensor:
         raise ValueError(f"b {tuple(b.shape)} does not match a {tuple(a.shape)}")
     n = b.shape[1]
     b_nk = _k_major(b)
-    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+    if a.stride(1) != 1 or a.stride(0) % 8 or _misaligned(a):
         a = a.contiguous()
     if out is None:
         out = torch.empty(m, n, dtype=a.dtype, device=a.device)
-    with torch.cuda.device(a.device):
-        _lib.call("hb200_dense_matmul", a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), m, n, k, a.stride(0),
-                  b_nk.stride(0), out.stride(0), int(a.dtype is torch.bfloat16),
-                  torch.cuda.current_stream(a.device).cuda_stream)
+    _dense_matmul_op(a, b_nk, out)
     return out
 
 
 def _k_major(b: Tensor) -> Tensor:
     """``b [K, N]`` -> its ``[N, K]`` storage with unit stride along K (a view when ``b`` already is K-major)."""
     b_nk = b.t()
-    if b_nk.stride(1) != 1 or b_nk.stride(0) % 8 or b_nk.data_ptr() % 16:
+    if b_nk.stride(1) != 1 or b_nk.stride(0) % 8 or _misaligned(b_nk):
         b_nk = b_nk.contiguous()
     return b_nk
+
+
+def _misaligned(t: Tensor) -> bool:
+    """Whether ``t`` starts off a 16-byte boundary (from the storage offset: no data pointer is read, so that shapes
+    trace under fake tensors; allocations themselves are at least 256-byte aligned)."""
+    return (t.storage_offset() * t.element_size()) % 16 != 0
 
 
 class FusedMatmulCollectives:

@@ -179,6 +179,11 @@ def test_grouped_and_moe_ops_registered_with_fake_impls():
                                   torch.empty(8, 256 * 8, dtype=torch.float8_e4m3fn, **cuda), torch.empty(8, **cuda))
         y = M.nvfp4_moe(x, logits, 2, gu, dn)
         assert y.shape == (64, 256) and y.dtype is torch.bfloat16 and y.device.type == "cuda"
+        from helion_b200 import dist as D
+
+        assert hasattr(torch.ops.helion_b200, "dense_matmul_out")
+        y = D.dense_matmul(torch.empty(512, 128, dtype=torch.bfloat16, **cuda), torch.empty(384, 128, dtype=torch.bfloat16, **cuda).t())
+        assert y.shape == (512, 384) and y.dtype is torch.bfloat16
 
 
 def test_product_modules_have_no_cpu_path():
