@@ -82,6 +82,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_tc_counter_bytes": [],
     "hb200_set_wait_budget_cycles": [_I64],
     "hb200_selftest_bounded_wait": [_P],
+    "hb200_selftest_exact_reciprocal": [_P, _P],
     "hb200_build_worklist_tiles": [_P, _I64, _I64, _P, _I64, _P],
     "hb200_build_split_tiles": [_P, c_int, _I64, _I64, _I64, _P, _I64, _P],
     "hb200_nvfp4_quantize_scatter": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P],

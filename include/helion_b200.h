@@ -523,6 +523,13 @@ int hb200_set_wait_budget_cycles(int64_t cycles);
  * HB200_ERR_DEVICE_TIMEOUT until reset.  Exercises the expiry path without a fault; shorten the budget first. */
 int hb200_selftest_bounded_wait(void* stream);
 
+/* Self-test of the short exact reciprocal and division the quant producers use where the divisor's range is
+ * known (no reference counterpart).  `mismatches` points at three 64-bit device counters: [0] counts the fp32
+ * divisors in [2^-100, 2^125], all of which are tried, whose short reciprocal differs from the IEEE one; [1] the
+ * quotients of the one-correction-step division that differ from the IEEE quotient among four numerators per
+ * divisor (|x| >= 2^-100); [2] the same for two correction steps.  All read 0 when the short forms are exact. */
+int hb200_selftest_exact_reciprocal(unsigned long long* mismatches, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -58,6 +58,28 @@ def test_group_quant_other_dtypes():
         assert count_diff(s, so) == 0 and count_diff(q, qo) == 0
 
 
+def test_group_quant_with_tiny_eps_and_tiny_groups_or_other_limits():
+    """Scales below 2^-60 (tiny eps, tiny values: the kernel moves such a group up by 2^64 before its short
+    division) and limits other than the format's own (the kernel then clamps explicitly)."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(32, 1024, generator=g)
+    x[:16] *= 1e-30
+    x[16:24] *= 1e-36
+    x[8, :128] = 0.0
+    x[8, 5] = 1e-38
+    for dt in (torch.bfloat16, torch.float32):
+        xs = x.to(dt)
+        q, s = run_group(xs, 128, False, eps=1e-44)
+        qo, so = O.per_token_group_fp8_quant(xs, 128, 1e-44, -448.0, 448.0, False)
+        assert count_diff(s, so) == 0 and count_diff(q, qo) == 0
+    xs = (x[24:] * 3).to(torch.bfloat16)
+    q = torch.zeros(8, 1024, device=DEV).to(FP8)
+    s = torch.zeros(8, 8, device=DEV)
+    hb.per_token_group_fp8_quant(xs.to(DEV), q, s, 128, 1e-10, -200.0, 240.0, False)
+    qo, so = O.per_token_group_fp8_quant(xs, 128, 1e-10, -200.0, 240.0, False)
+    assert count_diff(s, so) == 0 and count_diff(q, qo) == 0
+
+
 # ---------------------------------------------------------------- silu_and_mul_per_block_quant
 def run_silu(x, gs, ub=None, int8=False):
     t, two_i = x.shape
@@ -452,3 +474,35 @@ def test_silu_scales_may_be_a_transposed_view():
     hb.silu_and_mul_per_block_quant(q, x, s_t, 128, None, True)
     qd, sd = O.silu_and_mul_per_block_quant(x, 128)
     assert count_diff(q, qd) == 0 and torch.equal(s_t, sd)
+
+
+
+def test_short_reciprocal_and_division_are_exact_on_their_whole_range():
+    """The producers replace the general reciprocal / division by a two-FMA Newton step and a one-step exact
+    quotient where the divisor is known to lie in [2^-100, 2^125]: every fp32 divisor of that range gives the IEEE
+    reciprocal, and four numerators per divisor (7.6e9 pairs) the IEEE quotient."""
+    from helion_b200 import _lib
+
+    bad = torch.full((3,), -1, dtype=torch.int64, device=DEV)
+    _lib.call("hb200_selftest_exact_reciprocal", bad.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert bad.tolist() == [0, 0, 0], f"reciprocals / one-step / two-step quotients that differ: {bad.tolist()}"
+
+
+def test_silu_producers_on_extreme_gate_values():
+    """Gate values beyond +-86 (where 1 + exp(-a) leaves the short reciprocal's range), denormal-sized values and
+    zeros of both signs take the general path or the exact corner of the short one, and still equal torch on the
+    device bit for bit.  (The up values beside them are small so that no product overflows into a NaN, whose fp8
+    sign bit is nobody's contract.)"""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(8, 2 * 256, generator=g).to(torch.bfloat16)
+    special = torch.tensor([-86.0, -87.0, -88.5, -100.0, -3e38, 86.0, 90.0, 3e38, 0.0, -0.0, 1e-30, -1e-30, 1e-38, -1e-38,
+                            -85.5, 85.5], dtype=torch.bfloat16)
+    for r in range(8):
+        x[r, r * 16 : r * 16 + 16] = special  # one group with specials per row, the other groups plain
+        x[r, 256 + r * 16 : 256 + r * 16 + 16] = 0.001
+    check_silu(x, 128)
+    check_silu(x, 64)
+    scale = torch.tensor([0.5], device=DEV)
+    x[0, 3] = float("inf")  # silu(inf) = inf: saturates to 448
+    got = hb.silu_mul_fp8(x.to(DEV), scale)
+    assert torch.equal(got.view(torch.uint8), _silu_mul_fp8_on_device(x.to(DEV), scale).view(torch.uint8))
