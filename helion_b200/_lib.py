@@ -40,6 +40,7 @@ SIGNATURES: dict[str, list] = {
     "hb200_nvfp4_gemv_bf16in_mma": [_P, _P, _P, _P, _I64, _I64, _I64, c_float, _P],
     "hb200_nvfp4_gemv_fp4in": [_P, _P, _P, _P, _P, _I64, _I64, c_float, _P],
     "hb200_silu_and_mul_per_block_quant": [_P, _P, _P, _I64, _I64, _I64, _I64, c_int, _P, c_int, _P],
+    "hb200_silu_and_mul_per_block_quant_typed": [_P, _P, _P, _I64, _I64, _I64, _I64, c_int, _P, c_int, c_int, _P],
     "hb200_rms_norm_dynamic_per_token_quant": [_P, _P, _P, _P, _I64, _I64, c_float, _P, _P, c_int, c_int, _P],
     "hb200_per_token_group_fp8_quant": [_P, _P, _P, _I64, _I64, c_int, c_float, c_float, c_float, c_int, c_int, _P],
     "hb200_nvfp4_quantize": [_P, _P, _P, _P, _I64, _I64, _I64, c_int, _P],

@@ -243,9 +243,10 @@ def _silu_mul_quant_op(out: Tensor, input: Tensor, scales: Tensor, group_size: i
     tokens, two_i = input.shape
     with torch.cuda.device(input.device):
         _lib.call(
-            "hb200_silu_and_mul_per_block_quant",
+            "hb200_silu_and_mul_per_block_quant_typed",
             out.data_ptr(), input.data_ptr(), scales.data_ptr(), tokens, two_i // 2,
-            input.stride(0), out.stride(0), group_size, _ptr(scale_ub), int(out.dtype == torch.int8), _stream(),
+            input.stride(0), out.stride(0), group_size, _ptr(scale_ub), int(out.dtype == torch.int8),
+            {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[input.dtype], _stream(),
         )
 
 
@@ -743,8 +744,8 @@ def silu_and_mul_per_block_quant(
     assert group_size in [64, 128]
     assert input.stride()[-1] == 1
     assert out.stride()[-1] == 1
-    if input.dtype is not torch.bfloat16:
-        raise TypeError(f"input must be torch.bfloat16, got {input.dtype}")  # (the reference also takes fp16 / fp32)
+    if input.dtype not in (torch.bfloat16, torch.float16, torch.float32):  # the reference converts any to fp32
+        raise TypeError(f"input must be bfloat16, float16 or float32, got {input.dtype}")
     if scales.is_contiguous():
         _silu_mul_quant_op(out, input, scales, group_size, scale_ub)
     else:

@@ -80,6 +80,11 @@ int hb200_nvfp4_gemv_fp4in(const void* weight_packed, const void* x_packed, cons
 int hb200_silu_and_mul_per_block_quant(void* out, const void* input, void* scales, int64_t tokens,
                                        int64_t inter, int64_t in_stride, int64_t out_stride, int group,
                                        const float* scale_ub, int out_is_int8, void* stream);
+/* The same for an input of another float type, as the reference converts any to fp32 first
+ * (silu_and_mul_per_block_quant.py:99-107): in_dtype 0 = bf16, 1 = fp16, 2 = fp32. */
+int hb200_silu_and_mul_per_block_quant_typed(void* out, const void* input, void* scales, int64_t tokens,
+                                             int64_t inter, int64_t in_stride, int64_t out_stride, int group,
+                                             const float* scale_ub, int out_is_int8, int in_dtype, void* stream);
 
 /* Replaces rms_norm_dynamic_per_token_quant
  * (pretuned_kernels/rms_norm_dynamic_per_token_quant/rms_norm_dynamic_per_token_quant.py:40-128).

@@ -122,6 +122,14 @@ def test_silu_bit_exact(t, i, gs):
     check_silu(x, gs)
 
 
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32])
+def test_silu_other_input_types(dt):
+    """The reference converts any float input to fp32 first (silu_and_mul_per_block_quant.py:99-107)."""
+    x = torch.randn(33, 2 * 1024, generator=torch.Generator().manual_seed(6)).to(dt)
+    check_silu(x, 128)
+    check_silu(x, 64, torch.tensor(0.75))
+
+
 def test_silu_strided_input_and_int8():
     x = torch.randn(16, 2 * 256 + 64, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
     xv = x.to(DEV)[:, : 2 * 256]  # row stride 576
