@@ -693,6 +693,47 @@ def wl_quant(args, dev, rank, world, timer):
     b = 2 * t * h + t * h + 4 * t
     ops["dynamic_per_token_scaled_fp8_quant_16384x7168"] = {"us": tm * 1e3, "GBps": b / (tm * 1e-3) / 1e9}
 
+    # The reference gates these kernels on their speed-up over the best of torch eager and torch.compile
+    # (test/test_pretuned_kernels.py:325-346, H100 figures only).  torch eager, the modules' own torch expressions
+    # written out here, is timed beside each operator on this device at the same size (its fp32 temporaries take a
+    # few GB).
+    fp8 = torch.float8_e4m3fn
+    te, scale_up = t, 1.0
+
+    def eager_rms():
+        xf = x[:te].float()
+        xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16) * w
+        sc = (xn.float().abs().amax(-1, keepdim=True) * (1.0 / 448.0)).clamp(min=1.0 / (448.0 * 512.0))
+        return (xn.float() / sc).clamp(-448.0, 448.0).to(fp8), sc
+
+    def eager_group():
+        xg = x[:te].float().reshape(te, h // 128, 128)
+        sc = xg.abs().amax(-1, keepdim=True).clamp(min=1e-10) / 448.0
+        return (xg / sc).clamp(-448.0, 448.0).to(fp8), sc
+
+    xs_e = torch.randn(te, 2 * i, device=dev, dtype=torch.bfloat16)
+
+    def eager_silu():
+        a, bb = xs_e[:, :i].float(), xs_e[:, i:].float()
+        y = (a * torch.sigmoid(a) * bb).reshape(te, i // 128, 128)
+        sc = (y.abs().amax(-1) * (1.0 / 448.0)).clamp(min=1.0 / (448.0 * 512.0))
+        return (y / sc[:, :, None]).clamp(-448.0, 448.0).to(fp8), sc
+
+    def eager_dyn():
+        xf = x[:te].float()
+        sc = (xf.abs().amax(-1, keepdim=True) * (1.0 / 448.0)).clamp(min=1.0 / (448.0 * 512.0))
+        return (xf * (1.0 / sc)).clamp(-448.0, 448.0).to(fp8), sc
+
+    eager = {}
+    for name, fn, ours_us in (("rms_norm_dynamic_per_token_quant_16384x7168", eager_rms, ms * 1e3),
+                              ("per_token_group_fp8_quant_16384x7168", eager_group, None),
+                              ("silu_and_mul_per_block_quant_16384x18432", eager_silu, None),
+                              ("dynamic_per_token_scaled_fp8_quant_16384x7168", eager_dyn, None)):
+        tm = timer.run(graphed(fn)[0], 5, 2) * 1e3 * scale_up
+        ours = ours_us if ours_us is not None else ops[name]["us"]
+        eager[name] = {"torch_eager_us": tm, "ours_us": ours, "speedup": tm / ours}
+    del xs_e
+
     host_q = torch.empty(t, h, dtype=torch.uint8).pin_memory()
 
     def e2e_step():
@@ -708,7 +749,7 @@ def wl_quant(args, dev, rank, world, timer):
             "frac": ach / peaks["hbm_gbs"], "traffic": ncu_traffic("rms_norm_16384x7168")}
     return dict(value=world * nbytes / (ms * 1e-3) / 1e12, unit="TB/s", ms=ms, e2e_value=world * nbytes / (e2e_ms * 1e-3) / 1e12,
                 e2e_ms=e2e_ms, h2d=host_x.numel() * 2, d2h=host_q.numel(), launches=1, roofline=roof,
-                parity=parity, extra={"ops": ops}, dtype="fp32 arithmetic, bf16 in, e4m3 out",
+                parity=parity, extra={"ops": ops, "vs_torch_eager": eager}, dtype="fp32 arithmetic, bf16 in, e4m3 out",
                 config={"workload": "quant", "op": "rms_norm_dynamic_per_token_quant", "tokens": t, "hidden": h,
                         "parallelism": "replicas only" if world > 1 else "single", "l2": "flushed between steps"})
 
